@@ -1,0 +1,171 @@
+/*
+ * ratchet_cuda.h — C ABI of the sm_100a CUDA device for ratchet-core's tensor-op hot path.
+ *
+ * ratchet has no FFI surface of its own: a device is an arm of three internal Rust enums/traits
+ * (Device, Storage, and the per-op resolve path).  Every entry point below names the reference
+ * interface it stands in for, by path inside the reference repository.  A Rust `-sys` crate binds
+ * these symbols one to one; the Python package binds the same symbols with ctypes.
+ *
+ * Conventions
+ *   - Every call returns an rcu_status; nothing aborts or throws across this boundary.  A
+ *     human-readable message for the last failing call on a device is kept per device
+ *     (rcu_last_error).
+ *   - One CUDA stream per rcu_device.  All launches and copies are asynchronous on that stream;
+ *     only rcu_d2h and rcu_sync block.  Calls on one handle must be serialised by the caller
+ *     (the reference drives one device from one thread at a time); distinct handles are independent.
+ *   - Tensors are contiguous, row-major, rank <= 4, described by a caller-owned POD (rcu_tensor).
+ *     Ops never allocate their output: the caller passes `dst` (ratchet-core/src/tensor.rs:817-821).
+ *   - A quantised tensor is ONE buffer holding ratchet's segments back to back, each padded to
+ *     256 bytes (ratchet-core/src/dtype/blocks.rs:69-82,124-148); `shape` is the logical shape.
+ *   - There is no CPU fallback: an unsupported combination returns RCU_ERR_UNSUPPORTED.
+ */
+#ifndef RATCHET_CUDA_H
+#define RATCHET_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RCU_MAX_RANK 4
+#define RCU_MAX_CONCAT 8 /* ratchet-core/src/ops/concat.rs:120-124 */
+
+typedef enum {
+    RCU_OK = 0,
+    RCU_ERR_INVALID_ARG = 1, /* InvariantError / OpGuards panics in the reference (op.rs:217-228) */
+    RCU_ERR_UNSUPPORTED = 2, /* dtype/shape combination with no kernel (InvariantError::UnsupportedDType) */
+    RCU_ERR_OOM = 3,         /* DeviceError / allocator failure */
+    RCU_ERR_CUDA = 4,        /* CUDA runtime error */
+    RCU_ERR_NCCL = 5,
+    RCU_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up */
+    RCU_ERR_BOUNDS = 7,      /* index outside a tensor (e.g. gather id) */
+    RCU_ERR_INPLACE = 8      /* OperationError::InplaceError (ops/concat.rs:35-37) */
+} rcu_status;
+
+/* ratchet-core/src/dtype/mod.rs:11-23 */
+typedef enum {
+    RCU_F32 = 0,
+    RCU_F16 = 1,
+    RCU_BF16 = 2,
+    RCU_I32 = 3,
+    RCU_U32 = 4,
+    RCU_Q8_0F = 5, /* int8 x32 blocks, f32 scale */
+    RCU_Q8_0H = 6, /* int8 x32 blocks, f16 scale */
+    RCU_Q4_KF = 7, /* GGUF Q4_K super-blocks, f32 d/dmin */
+    RCU_Q4_KH = 8  /* GGUF Q4_K super-blocks, f16 d/dmin */
+} rcu_dtype;
+
+/* ops/binary.rs:19-45, ops/unary.rs:23-60, ops/norm/mod.rs:18-60 */
+typedef enum { RCU_ADD = 0, RCU_SUB = 1, RCU_MUL = 2, RCU_DIV = 3 } rcu_binary_op;
+typedef enum {
+    RCU_GELU = 0, RCU_TANH = 1, RCU_EXP = 2, RCU_LOG = 3, RCU_SIN = 4, RCU_COS = 5, RCU_ABS = 6, RCU_SQRT = 7,
+    RCU_RELU = 8, RCU_FLOOR = 9, RCU_CEIL = 10, RCU_NEG = 11, RCU_SILU = 12, RCU_SIGMOID = 13
+} rcu_unary_op;
+typedef enum { RCU_LAYER_NORM = 0, RCU_RMS_NORM = 1, RCU_GROUP_NORM = 2 } rcu_norm_kind;
+typedef enum { RCU_REDUCE_SUM = 0, RCU_REDUCE_MAX = 1, RCU_REDUCE_MEAN = 2 } rcu_reduce_kind;
+
+/* StorageView + storage pointer of a resolved tensor (ratchet-core/src/tensor.rs:131-151). */
+typedef struct {
+    int32_t dt;                    /* rcu_dtype */
+    uint32_t rank;                 /* 1..RCU_MAX_RANK */
+    uint64_t shape[RCU_MAX_RANK];  /* row-major, contiguous */
+    void* data;                    /* device pointer */
+} rcu_tensor;
+
+typedef struct rcu_device rcu_device;
+
+/* ------------------------------------------------------------------ device (device.rs:25-93) */
+/* Device::request_device(DeviceRequest::GPU): open CUDA device `ordinal` with its own stream. */
+rcu_status rcu_device_create(int ordinal, rcu_device** out);
+/* Same, but every launch goes to the caller's cudaStream_t (e.g. the stream of a host framework). */
+rcu_status rcu_device_create_on_stream(int ordinal, void* cuda_stream, rcu_device** out);
+void rcu_device_destroy(rcu_device* dev);
+const char* rcu_last_error(rcu_device* dev);
+/* Number of kernels this handle has launched since creation (profiling aid, gpu/profiler.rs). */
+uint64_t rcu_launch_count(rcu_device* dev);
+int rcu_sm_count(rcu_device* dev);
+
+/* ------------------------------------------------------------------ storage (storage/gpu_buffer.rs) */
+/* BufferAllocator / BufferPool: pooled device memory (gpu/pools/buffer_pool.rs:80-94 rounds sizes
+ * up to 4 B with a 16 B minimum; this pool rounds to 256 B size classes and caches freed blocks). */
+rcu_status rcu_alloc(rcu_device* dev, uint64_t nbytes, void** dptr);
+rcu_status rcu_free(rcu_device* dev, void* dptr);
+/* Return cached blocks to the driver (WgpuDevice::begin_pass garbage collection analogue). */
+rcu_status rcu_pool_trim(rcu_device* dev);
+/* bytes currently handed out / bytes held by the pool (allocator.rs:330-337 logs the same) */
+void rcu_pool_stats(rcu_device* dev, uint64_t* in_use, uint64_t* reserved);
+/* GPUBuffer::from_bytes (storage/gpu_buffer.rs:49-60) and to_cpu (200-218). d2h blocks. */
+rcu_status rcu_h2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
+rcu_status rcu_d2h(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
+rcu_status rcu_d2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
+rcu_status rcu_memset(rcu_device* dev, void* dst, int value, uint64_t nbytes);
+/* device.poll(Wait) (tensor.rs:856) */
+rcu_status rcu_sync(rcu_device* dev);
+
+/* ------------------------------------------------------------------ layouts (dtype/blocks.rs) */
+/* DType::segments total: bytes of the single buffer that holds `numel` elements of `dt`. */
+uint64_t rcu_dtype_nbytes(int32_t dt, uint64_t numel);
+/* Byte offsets of the segments: Q8_0 -> {qs, d}; Q4_K -> {qs, scales, dmin, d}; returns count. */
+int rcu_dtype_segments(int32_t dt, uint64_t numel, uint64_t offsets[4]);
+/* DType::activation_dt (dtype/mod.rs:97-105) */
+int32_t rcu_activation_dtype(int32_t dt);
+
+/* ------------------------------------------------------------------ ops */
+/* dequantize (quant.rs:132-164) on the device: bit-exact with the CPU routine. src is Q8_0F/H or
+ * Q4_KF/H, dst is F32 (…F) or F16 (…H) of the same shape. */
+rcu_status rcu_dequantize(rcu_device* dev, const rcu_tensor* src, rcu_tensor* dst);
+
+/* Matmul (ops/matmul/mod.rs:381-545; Tensor::gemm tensor.rs:409-419).  dst dtype = rhs dtype.
+ * Allowed (lhs, rhs) pairs: (F32,F32) (F16,F16) (Q8_0F,F32) (Q8_0H,F16) (Q4_KF,F32) (Q4_KH,F16)
+ * as in check_dtypes (mod.rs:518-534), plus (Q8_0F,F16): f32 block scales with f16 activations.
+ * bias (nullable) is a vector over dst's last dimension, in the rhs dtype. */
+rcu_status rcu_matmul(rcu_device* dev, const rcu_tensor* lhs, const rcu_tensor* rhs, const rcu_tensor* bias,
+                      int trans_lhs, int trans_rhs, int trans_dst, rcu_tensor* dst);
+/* Matmul::compute_dst_shape (mod.rs:392-466): fills dst->rank/shape/dt, touches no memory. */
+rcu_status rcu_matmul_dst_shape(const rcu_tensor* lhs, const rcu_tensor* rhs, int trans_lhs, int trans_rhs,
+                                int trans_dst, rcu_tensor* dst);
+
+/* Binary (ops/binary.rs): same-shape operands, or `b` broadcastable to `a`'s shape (the reference
+ * materialises the broadcast first, tensor.rs:252-278; here it is folded into the kernel).
+ * dst may alias a (in-place, binary.rs:130-132). */
+rcu_status rcu_binary(rcu_device* dev, int op, const rcu_tensor* a, const rcu_tensor* b, rcu_tensor* dst);
+/* Unary (ops/unary.rs); dst may alias x. */
+rcu_status rcu_unary(rcu_device* dev, int op, const rcu_tensor* x, rcu_tensor* dst);
+/* Cast (ops/cast.rs; cpu/mod.rs:127-156: f32<->f16, f32<->bf16 convert, f32<->i32/u32 reinterpret). */
+rcu_status rcu_cast(rcu_device* dev, const rcu_tensor* x, rcu_tensor* dst);
+/* Norm (ops/norm/mod.rs): LayerNorm / RMSNorm over the last dimension; bias nullable;
+ * GroupNorm takes x [B,C,L] with `groups`. */
+rcu_status rcu_norm(rcu_device* dev, int kind, const rcu_tensor* x, const rcu_tensor* scale, const rcu_tensor* bias,
+                    float eps, uint32_t groups, rcu_tensor* dst);
+/* Softmax (ops/softmax.rs) over `dim`, which must be the last dimension; dst may alias x. */
+rcu_status rcu_softmax(rcu_device* dev, const rcu_tensor* x, uint32_t dim, rcu_tensor* dst);
+/* Row reduction over the last dimension (the reduce step shared by Norm and Softmax; cpu/norm.rs:72-89). */
+rcu_status rcu_reduce(rcu_device* dev, int kind, const rcu_tensor* x, rcu_tensor* dst);
+/* RoPE (ops/rope.rs): x [B,H,S,D], rotates the first `dim` features; dst may alias x. */
+rcu_status rcu_rope(rcu_device* dev, const rcu_tensor* x, uint32_t dim, float base, uint32_t offset, rcu_tensor* dst);
+/* Concat (ops/concat.rs): n <= 8 inputs along `dim`. */
+rcu_status rcu_concat(rcu_device* dev, const rcu_tensor* const* inputs, uint32_t n, uint32_t dim, rcu_tensor* dst);
+/* IndexSelect (ops/select.rs): src rank 2 (float or Q8_0), ids rank-1 I32; Q8_0 tables are
+ * dequantised while gathering into the activation dtype. An id outside the table sets RCU_ERR_BOUNDS
+ * on the next rcu_sync/rcu_d2h (the row is clamped, select.rs:157). */
+rcu_status rcu_index_select(rcu_device* dev, const rcu_tensor* src, const rcu_tensor* ids, uint32_t dim, rcu_tensor* dst);
+/* Reindex (ops/reindex/{permute,slice,broadcast}.rs) */
+rcu_status rcu_permute(rcu_device* dev, const rcu_tensor* src, const uint32_t* perm, rcu_tensor* dst);
+rcu_status rcu_slice(rcu_device* dev, const rcu_tensor* src, const uint64_t* start, const uint64_t* stop, rcu_tensor* dst);
+rcu_status rcu_broadcast(rcu_device* dev, const rcu_tensor* src, rcu_tensor* dst);
+/* Cache (ops/cache.rs): cache[..., offset:offset+s, ...] = src along `dim`, and
+ * dst = cache[..., :offset+s, ...].  When dst->data is NULL only the append happens and the
+ * caller reads the prefix of `cache` directly (valid for dim <= 1 leading size-1 dims, or when the
+ * consumer takes a row stride). */
+rcu_status rcu_cache(rcu_device* dev, rcu_tensor* cache, const rcu_tensor* src, uint32_t dim, uint32_t offset, rcu_tensor* dst);
+/* IndexWrite (ops/index_write.rs): dst[start + i] = src[i]. */
+rcu_status rcu_index_write(rcu_device* dev, rcu_tensor* dst, const rcu_tensor* src, const uint64_t* start);
+/* Conv (ops/conv.rs): conv1d with kernel size 3; x [B,Cin,L], w [Cout,Cin,3], bias [Cout]. */
+rcu_status rcu_conv1d(rcu_device* dev, const rcu_tensor* x, const rcu_tensor* w, const rcu_tensor* bias,
+                      uint32_t stride, uint32_t padding, rcu_tensor* dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RATCHET_CUDA_H */

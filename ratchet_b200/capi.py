@@ -1,0 +1,144 @@
+"""ctypes binding of ``libratchet_cuda.so`` — one Python function per C-ABI symbol of
+``include/ratchet_cuda.h`` plus the small amount of glue needed to describe tensors.
+
+There is no fallback: importing works without a GPU (so symbol tables can be checked), but every
+compute call needs the library and a B200, and raises :class:`RatchetCudaError` otherwise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libratchet_cuda.so")
+
+RCU_MAX_RANK = 4
+
+# rcu_status
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_BOUNDS, ERR_INPLACE = range(9)
+_STATUS_NAMES = ["RCU_OK", "RCU_ERR_INVALID_ARG", "RCU_ERR_UNSUPPORTED", "RCU_ERR_OOM", "RCU_ERR_CUDA", "RCU_ERR_NCCL",
+                 "RCU_ERR_TIMEOUT", "RCU_ERR_BOUNDS", "RCU_ERR_INPLACE"]
+
+# rcu_dtype (ratchet-core/src/dtype/mod.rs:11-23)
+F32, F16, BF16, I32, U32, Q8_0F, Q8_0H, Q4_KF, Q4_KH = range(9)
+DTYPE_NAMES = ["F32", "F16", "BF16", "I32", "U32", "Q8_0F", "Q8_0H", "Q4_KF", "Q4_KH"]
+_NP_OF = {F32: np.float32, F16: np.float16, BF16: np.uint16, I32: np.int32, U32: np.uint32}
+_DT_OF_NP = {np.dtype(np.float32): F32, np.dtype(np.float16): F16, np.dtype(np.int32): I32, np.dtype(np.uint32): U32}
+
+BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+UNARY_OPS = {"gelu": 0, "tanh": 1, "exp": 2, "log": 3, "sin": 4, "cos": 5, "abs": 6, "sqrt": 7, "relu": 8, "floor": 9,
+             "ceil": 10, "neg": 11, "silu": 12, "sigmoid": 13}
+LAYER_NORM, RMS_NORM, GROUP_NORM = 0, 1, 2
+REDUCE_SUM, REDUCE_MAX, REDUCE_MEAN = 0, 1, 2
+
+
+class RatchetCudaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        name = _STATUS_NAMES[status] if 0 <= status < len(_STATUS_NAMES) else str(status)
+        super().__init__(f"{name}: {message}")
+        self.status = status
+
+
+class rcu_tensor(C.Structure):
+    _fields_ = [("dt", C.c_int32), ("rank", C.c_uint32), ("shape", C.c_uint64 * RCU_MAX_RANK), ("data", C.c_void_p)]
+
+
+_T = C.POINTER(rcu_tensor)
+_DEV = C.c_void_p
+_u64p = C.POINTER(C.c_uint64)
+_u32p = C.POINTER(C.c_uint32)
+
+# symbol -> (restype, argtypes); the keys are exactly the functions declared in include/ratchet_cuda.h
+SIGNATURES = {
+    "rcu_device_create": (C.c_int, [C.c_int, C.POINTER(_DEV)]),
+    "rcu_device_create_on_stream": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(_DEV)]),
+    "rcu_device_destroy": (None, [_DEV]),
+    "rcu_last_error": (C.c_char_p, [_DEV]),
+    "rcu_launch_count": (C.c_uint64, [_DEV]),
+    "rcu_sm_count": (C.c_int, [_DEV]),
+    "rcu_alloc": (C.c_int, [_DEV, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "rcu_free": (C.c_int, [_DEV, C.c_void_p]),
+    "rcu_pool_trim": (C.c_int, [_DEV]),
+    "rcu_pool_stats": (None, [_DEV, _u64p, _u64p]),
+    "rcu_h2d": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "rcu_d2h": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "rcu_d2d": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "rcu_memset": (C.c_int, [_DEV, C.c_void_p, C.c_int, C.c_uint64]),
+    "rcu_sync": (C.c_int, [_DEV]),
+    "rcu_dtype_nbytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
+    "rcu_dtype_segments": (C.c_int, [C.c_int32, C.c_uint64, _u64p]),
+    "rcu_activation_dtype": (C.c_int32, [C.c_int32]),
+    "rcu_dequantize": (C.c_int, [_DEV, _T, _T]),
+    "rcu_matmul": (C.c_int, [_DEV, _T, _T, _T, C.c_int, C.c_int, C.c_int, _T]),
+    "rcu_matmul_dst_shape": (C.c_int, [_T, _T, C.c_int, C.c_int, C.c_int, _T]),
+    "rcu_binary": (C.c_int, [_DEV, C.c_int, _T, _T, _T]),
+    "rcu_unary": (C.c_int, [_DEV, C.c_int, _T, _T]),
+    "rcu_cast": (C.c_int, [_DEV, _T, _T]),
+    "rcu_norm": (C.c_int, [_DEV, C.c_int, _T, _T, _T, C.c_float, C.c_uint32, _T]),
+    "rcu_softmax": (C.c_int, [_DEV, _T, C.c_uint32, _T]),
+    "rcu_reduce": (C.c_int, [_DEV, C.c_int, _T, _T]),
+    "rcu_rope": (C.c_int, [_DEV, _T, C.c_uint32, C.c_float, C.c_uint32, _T]),
+    "rcu_concat": (C.c_int, [_DEV, C.POINTER(_T), C.c_uint32, C.c_uint32, _T]),
+    "rcu_index_select": (C.c_int, [_DEV, _T, _T, C.c_uint32, _T]),
+    "rcu_permute": (C.c_int, [_DEV, _T, _u32p, _T]),
+    "rcu_slice": (C.c_int, [_DEV, _T, _u64p, _u64p, _T]),
+    "rcu_broadcast": (C.c_int, [_DEV, _T, _T]),
+    "rcu_cache": (C.c_int, [_DEV, _T, _T, C.c_uint32, C.c_uint32, _T]),
+    "rcu_index_write": (C.c_int, [_DEV, _T, _T, _u64p]),
+    "rcu_conv1d": (C.c_int, [_DEV, _T, _T, _T, C.c_uint32, C.c_uint32, _T]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the shared library (built in-tree by ``ratchet_b200._build``). Fails loudly if absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RatchetCudaError(ERR_CUDA, f"{LIB_PATH} is missing: run `python -m ratchet_b200._build` "
+                                             "(there is no CPU fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError here = the library does not export a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def dtype_nbytes(dt: int, numel: int) -> int:
+    return lib().rcu_dtype_nbytes(dt, numel)
+
+
+def dtype_segments(dt: int, numel: int):
+    off = (C.c_uint64 * 4)()
+    n = lib().rcu_dtype_segments(dt, numel, off)
+    return [off[i] for i in range(n)]
+
+
+def activation_dtype(dt: int) -> int:
+    return lib().rcu_activation_dtype(dt)
+
+
+def np_dtype(dt: int):
+    return _NP_OF[dt]
+
+
+def dt_of_numpy(a: np.ndarray) -> int:
+    return _DT_OF_NP[a.dtype]
+
+
+def describe(dt: int, shape, ptr: int) -> rcu_tensor:
+    shape = tuple(int(s) for s in shape)
+    if not 1 <= len(shape) <= RCU_MAX_RANK:
+        raise RatchetCudaError(ERR_INVALID_ARG, f"rank {len(shape)} is outside 1..{RCU_MAX_RANK}")
+    t = rcu_tensor()
+    t.dt = dt
+    t.rank = len(shape)
+    for i, s in enumerate(shape):
+        t.shape[i] = s
+    t.data = ptr
+    return t

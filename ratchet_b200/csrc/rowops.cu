@@ -1,0 +1,313 @@
+// Row-wise reductions: LayerNorm / RMSNorm / GroupNorm, Softmax and the standalone row reduce.
+//
+// Stand in for ratchet-core's layer_norm / rms_norm / group_norm WGSL kernels
+// (ops/norm/mod.rs:112-245), softmax (ops/softmax.rs:55-180) and the reduce step both contain.
+// Formulas follow the CPU device (the parity target): LayerNorm uses var = E[x^2] - E[x]^2 and
+// y = (x - mu) * (1/sqrt(var + eps)) * gamma (+ beta) (cpu/norm.rs:91-147); RMSNorm
+// y = x * (1/sqrt(mean(x^2) + eps)) * gamma (cpu/norm.rs:185-213).  Softmax subtracts the row
+// maximum (the CPU device does not, cpu/softmax.rs:21-42; the results agree to f32 rounding and
+// the maximum keeps large logits finite).
+//
+// Each row is read from HBM once, kept in registers, reduced with warp shuffles (plus one
+// shared-memory hop across the warps of a CTA for long rows) and written once.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxPerLane = 32;     // warp-per-row path: N <= 1024
+constexpr int kCtaThreads = 256;
+constexpr int kMaxPerThread = 32;   // CTA-per-row path keeps N <= 8192 in registers
+
+struct SumOp { __device__ static float id() { return 0.f; } __device__ static float f(float a, float b) { return a + b; } };
+struct MaxOp { __device__ static float id() { return -INFINITY; } __device__ static float f(float a, float b) { return fmaxf(a, b); } };
+
+template <class Op> __device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = Op::f(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// reduce across the CTA; every thread gets the result. `scratch` holds 32 floats.
+template <class Op> __device__ __forceinline__ float cta_reduce(float v, float* scratch) {
+    v = warp_reduce<Op>(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();  // scratch may still be read from a previous reduction
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = lane < (blockDim.x >> 5) ? scratch[lane] : Op::id();
+    return warp_reduce<Op>(r);
+}
+
+enum { MODE_LN = 0, MODE_RMS = 1, MODE_SOFTMAX = 2 };
+
+// One row per "group" of threads. WARP=true: group = warp (blockDim = 32 x rows_per_cta);
+// WARP=false: group = whole CTA.
+template <class T, int MODE, bool WARP, int PER>
+__global__ void __launch_bounds__(kCtaThreads)
+row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
+           size_t rows, int N, float eps) {
+    __shared__ float scratch[32];
+    const int gsize = WARP ? 32 : blockDim.x;
+    const int gid = WARP ? (threadIdx.x & 31) : threadIdx.x;
+    const size_t groups_per_cta = WARP ? (blockDim.x >> 5) : 1;
+    const size_t gidx = WARP ? (threadIdx.x >> 5) : 0;
+    for (size_t row = (size_t)blockIdx.x * groups_per_cta + gidx; row < rows; row += (size_t)gridDim.x * groups_per_cta) {
+        // WARP=false: all threads of the CTA iterate together (row depends only on blockIdx)
+        const T* xr = x + row * (size_t)N;
+        T* orow = out + row * (size_t)N;
+        float v[PER];
+        float s = 0.f, s2 = 0.f, mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = gid + i * gsize;
+            if (j < N) {
+                v[i] = to_f32<T>(xr[j]);
+                if (MODE == MODE_SOFTMAX) mx = fmaxf(mx, v[i]);
+                else { s += v[i]; s2 += rnd<T>(v[i] * v[i]); }
+            } else {
+                v[i] = 0.f;
+            }
+        }
+        if (MODE == MODE_SOFTMAX) {
+            mx = WARP ? warp_reduce<MaxOp>(mx) : cta_reduce<MaxOp>(mx, scratch);
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int j = gid + i * gsize;
+                if (j < N) { v[i] = rnd<T>(expf(v[i] - mx)); sum += v[i]; }
+            }
+            sum = WARP ? warp_reduce<SumOp>(sum) : cta_reduce<SumOp>(sum, scratch);
+            sum = rnd<T>(sum);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int j = gid + i * gsize;
+                if (j < N) orow[j] = from_f32<T>(v[i] / sum);
+            }
+        } else {
+            const float nf = rnd<T>((float)N);
+            const float e = rnd<T>(eps);
+            if (MODE == MODE_LN) {
+                s = WARP ? warp_reduce<SumOp>(s) : cta_reduce<SumOp>(s, scratch);
+                s2 = WARP ? warp_reduce<SumOp>(s2) : cta_reduce<SumOp>(s2, scratch);
+                const float mu = rnd<T>(rnd<T>(s) / nf);
+                const float ex2 = rnd<T>(rnd<T>(s2) / nf);
+                const float var = rnd<T>(ex2 - rnd<T>(mu * mu));
+                const float rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(var + e))));
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    const int j = gid + i * gsize;
+                    if (j < N) {
+                        float y = rnd<T>(rnd<T>(v[i] - mu) * rstd);
+                        y = rnd<T>(y * to_f32<T>(gamma[j]));
+                        if (beta) y = rnd<T>(y + to_f32<T>(beta[j]));
+                        orow[j] = from_f32<T>(y);
+                    }
+                }
+            } else {
+                s2 = WARP ? warp_reduce<SumOp>(s2) : cta_reduce<SumOp>(s2, scratch);
+                const float ms = rnd<T>(rnd<T>(s2) / nf);
+                const float rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(ms + e))));
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    const int j = gid + i * gsize;
+                    if (j < N) orow[j] = from_f32<T>(rnd<T>(rnd<T>(v[i] * rstd) * to_f32<T>(gamma[j])));
+                }
+            }
+        }
+    }
+}
+
+// Rows too long for the register-resident kernels: three passes over a row that stays in L2.
+template <class T, int MODE>
+__global__ void __launch_bounds__(kCtaThreads)
+row_kernel_long(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
+                size_t rows, int N, float eps) {
+    __shared__ float scratch[32];
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * (size_t)N;
+        T* orow = out + row * (size_t)N;
+        float s = 0.f, s2 = 0.f, mx = -INFINITY;
+        for (int j = threadIdx.x; j < N; j += blockDim.x) {
+            const float v = to_f32<T>(xr[j]);
+            mx = fmaxf(mx, v); s += v; s2 += rnd<T>(v * v);
+        }
+        if (MODE == MODE_SOFTMAX) {
+            mx = cta_reduce<MaxOp>(mx, scratch);
+            float sum = 0.f;
+            for (int j = threadIdx.x; j < N; j += blockDim.x) sum += rnd<T>(expf(to_f32<T>(xr[j]) - mx));
+            sum = rnd<T>(cta_reduce<SumOp>(sum, scratch));
+            for (int j = threadIdx.x; j < N; j += blockDim.x) orow[j] = from_f32<T>(rnd<T>(expf(to_f32<T>(xr[j]) - mx)) / sum);
+        } else {
+            const float nf = rnd<T>((float)N), e = rnd<T>(eps);
+            s = cta_reduce<SumOp>(s, scratch);
+            s2 = cta_reduce<SumOp>(s2, scratch);
+            const float mu = MODE == MODE_LN ? rnd<T>(rnd<T>(s) / nf) : 0.f;
+            const float ex2 = rnd<T>(rnd<T>(s2) / nf);
+            const float var = MODE == MODE_LN ? rnd<T>(ex2 - rnd<T>(mu * mu)) : ex2;
+            const float rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(var + e))));
+            for (int j = threadIdx.x; j < N; j += blockDim.x) {
+                float y = rnd<T>(rnd<T>(to_f32<T>(xr[j]) - mu) * rstd);
+                y = rnd<T>(y * to_f32<T>(gamma[j]));
+                if (MODE == MODE_LN && beta) y = rnd<T>(y + to_f32<T>(beta[j]));
+                orow[j] = from_f32<T>(y);
+            }
+        }
+    }
+}
+
+template <class T, int MODE>
+rcu_status launch_rows(rcu_device* dev, const void* x, const void* gamma, const void* beta, void* out, size_t rows, int N, float eps) {
+    const T* xp = (const T*)x; const T* gp = (const T*)gamma; const T* bp = (const T*)beta; T* op = (T*)out;
+    const int cap = dev->sm_count * 8;
+    if (N <= 32 * kMaxPerLane) {
+        const int warps = 8;
+        const int grid = (int)std::min<size_t>((rows + warps - 1) / warps, (size_t)cap);
+#define RCU_ROW_WARP(P) row_kernel<T, MODE, true, P><<<grid, warps * 32, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps)
+        if (N <= 32 * 4) RCU_ROW_WARP(4);
+        else if (N <= 32 * 8) RCU_ROW_WARP(8);
+        else if (N <= 32 * 16) RCU_ROW_WARP(16);
+        else RCU_ROW_WARP(32);
+#undef RCU_ROW_WARP
+    } else if (N <= kCtaThreads * kMaxPerThread) {
+        const int grid = (int)std::min<size_t>(rows, (size_t)cap);
+#define RCU_ROW_CTA(P) row_kernel<T, MODE, false, P><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps)
+        if (N <= kCtaThreads * 8) RCU_ROW_CTA(8);
+        else if (N <= kCtaThreads * 16) RCU_ROW_CTA(16);
+        else RCU_ROW_CTA(32);
+#undef RCU_ROW_CTA
+    } else {
+        const int grid = (int)std::min<size_t>(rows, (size_t)cap);
+        row_kernel_long<T, MODE><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);
+    }
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
+template <int MODE>
+rcu_status dispatch_rows(rcu_device* dev, int dt, const void* x, const void* gamma, const void* beta, void* out, size_t rows, int N, float eps) {
+    switch (dt) {
+        case RCU_F32: return launch_rows<float, MODE>(dev, x, gamma, beta, out, rows, N, eps);
+        case RCU_F16: return launch_rows<__half, MODE>(dev, x, gamma, beta, out, rows, N, eps);
+        case RCU_BF16: return launch_rows<__nv_bfloat16, MODE>(dev, x, gamma, beta, out, rows, N, eps);
+    }
+    return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "row op: dtype %d", dt);
+}
+
+// GroupNorm (ops/norm/groupnorm.rs): x [B,C,L]; statistics over each group of C/groups channels
+// times L positions; y = (x - mu) * rsqrt(var + eps) * gamma[c] + beta[c].
+template <class T>
+__global__ void __launch_bounds__(kCtaThreads)
+group_norm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
+                  int C, int L, int groups, float eps) {
+    __shared__ float scratch[32];
+    const int cpg = C / groups;
+    const size_t base = (size_t)blockIdx.x * cpg * L;   // blockIdx.x = b * groups + g
+    const int g = blockIdx.x % groups;
+    const size_t n = (size_t)cpg * L;
+    float s = 0.f, s2 = 0.f;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32<T>(x[base + i]); s += v; s2 += v * v; }
+    s = cta_reduce<SumOp>(s, scratch);
+    s2 = cta_reduce<SumOp>(s2, scratch);
+    const float mu = s / (float)n;
+    const float var = s2 / (float)n - mu * mu;
+    const float rstd = rsqrtf(var + eps);
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const int c = g * cpg + (int)(i / L);
+        float y = (to_f32<T>(x[base + i]) - mu) * rstd * to_f32<T>(gamma[c]);
+        if (beta) y += to_f32<T>(beta[c]);
+        out[base + i] = from_f32<T>(y);
+    }
+}
+
+template <class T, int KIND>
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int N) {
+    const int lane = threadIdx.x & 31;
+    const size_t wpc = blockDim.x >> 5;
+    for (size_t row = (size_t)blockIdx.x * wpc + (threadIdx.x >> 5); row < rows; row += (size_t)gridDim.x * wpc) {
+        const T* xr = x + row * (size_t)N;
+        float acc = KIND == RCU_REDUCE_MAX ? -INFINITY : 0.f;
+        for (int j = lane; j < N; j += 32) {
+            const float v = to_f32<T>(xr[j]);
+            acc = KIND == RCU_REDUCE_MAX ? fmaxf(acc, v) : acc + v;
+        }
+        acc = KIND == RCU_REDUCE_MAX ? warp_reduce<MaxOp>(acc) : warp_reduce<SumOp>(acc);
+        if (KIND == RCU_REDUCE_MEAN) acc = rnd<T>(acc) / rnd<T>((float)N);   // cpu/norm.rs:72-89
+        if (lane == 0) out[row] = from_f32<T>(acc);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+rcu_status rcu_norm(rcu_device* dev, int kind, const rcu_tensor* x, const rcu_tensor* scale, const rcu_tensor* bias, float eps,
+                    uint32_t groups, rcu_tensor* dst) {
+    if (!dev) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(dev, t_valid(x) && t_valid(scale) && t_valid(dst), "norm: invalid tensor descriptor");
+    RCU_REQUIRE(dev, x->dt == scale->dt, "norm: DTypeMismatch expected %d, actual %d (scale)", x->dt, scale->dt);  // cpu/norm.rs:35-41
+    RCU_REQUIRE(dev, !bias || bias->dt == x->dt, "norm: DTypeMismatch (bias)");
+    RCU_REQUIRE(dev, dst->dt == x->dt && t_numel(dst) == t_numel(x), "norm: dst must match x");
+    DevGuard g(dev->ordinal);
+    const uint64_t N = x->shape[x->rank - 1];
+    if (kind == RCU_GROUP_NORM) {
+        RCU_REQUIRE(dev, x->rank == 3 && groups > 0 && x->shape[1] % groups == 0, "group_norm: x must be [B,C,L] with C %% groups == 0");
+        RCU_REQUIRE(dev, t_numel(scale) == x->shape[1] && (!bias || t_numel(bias) == x->shape[1]), "group_norm: scale/bias must have C elements");
+        const int grid = (int)(x->shape[0] * groups);
+        const void* bp = bias ? bias->data : nullptr;
+        switch (x->dt) {
+            case RCU_F32: group_norm_kernel<float><<<grid, kCtaThreads, 0, dev->stream>>>((const float*)x->data, (const float*)scale->data, (const float*)bp, (float*)dst->data, (int)x->shape[1], (int)x->shape[2], (int)groups, eps); break;
+            case RCU_F16: group_norm_kernel<__half><<<grid, kCtaThreads, 0, dev->stream>>>((const __half*)x->data, (const __half*)scale->data, (const __half*)bp, (__half*)dst->data, (int)x->shape[1], (int)x->shape[2], (int)groups, eps); break;
+            default: return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "group_norm: dtype %d", x->dt);
+        }
+        RCU_LAUNCH_CHECK(dev);
+        return RCU_OK;
+    }
+    RCU_REQUIRE(dev, kind == RCU_LAYER_NORM || kind == RCU_RMS_NORM, "norm: unknown kind %d", kind);
+    RCU_REQUIRE(dev, t_numel(scale) == N && (!bias || t_numel(bias) == N), "norm: scale/bias must have %llu elements", (unsigned long long)N);
+    RCU_REQUIRE(dev, N <= 0x7fffffffull && N > 0, "norm: bad row length");
+    const size_t rows = t_numel(x) / N;
+    const void* bp = (bias && kind == RCU_LAYER_NORM) ? bias->data : nullptr;
+    if (kind == RCU_LAYER_NORM) return dispatch_rows<MODE_LN>(dev, x->dt, x->data, scale->data, bp, dst->data, rows, (int)N, eps);
+    return dispatch_rows<MODE_RMS>(dev, x->dt, x->data, scale->data, nullptr, dst->data, rows, (int)N, eps);
+}
+
+rcu_status rcu_softmax(rcu_device* dev, const rcu_tensor* x, uint32_t dim, rcu_tensor* dst) {
+    if (!dev) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(dev, t_valid(x) && t_valid(dst), "softmax: invalid tensor descriptor");
+    RCU_REQUIRE(dev, dim == x->rank - 1, "softmax: only the last dimension is supported (dim=%u, rank=%u)", dim, x->rank);
+    RCU_REQUIRE(dev, dst->dt == x->dt && t_numel(dst) == t_numel(x), "softmax: dst must match x");
+    DevGuard g(dev->ordinal);
+    const uint64_t N = x->shape[dim];
+    RCU_REQUIRE(dev, N <= 0x7fffffffull && N > 0, "softmax: bad row length");
+    return dispatch_rows<MODE_SOFTMAX>(dev, x->dt, x->data, nullptr, nullptr, dst->data, t_numel(x) / N, (int)N, 0.f);
+}
+
+rcu_status rcu_reduce(rcu_device* dev, int kind, const rcu_tensor* x, rcu_tensor* dst) {
+    if (!dev) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(dev, t_valid(x) && t_valid(dst), "reduce: invalid tensor descriptor");
+    const uint64_t N = x->shape[x->rank - 1];
+    const size_t rows = t_numel(x) / N;
+    RCU_REQUIRE(dev, dst->dt == x->dt && t_numel(dst) == rows, "reduce: dst must hold one element per row");
+    RCU_REQUIRE(dev, kind >= RCU_REDUCE_SUM && kind <= RCU_REDUCE_MEAN, "reduce: unknown kind %d", kind);
+    DevGuard g(dev->ordinal);
+    const int grid = (int)std::min<size_t>((rows + 7) / 8, (size_t)dev->sm_count * 8);
+#define RCU_RED(T, K) reduce_rows_kernel<T, K><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (T*)dst->data, rows, (int)N)
+#define RCU_RED_T(T)                                       \
+    switch (kind) {                                        \
+        case RCU_REDUCE_SUM: RCU_RED(T, RCU_REDUCE_SUM); break; \
+        case RCU_REDUCE_MAX: RCU_RED(T, RCU_REDUCE_MAX); break; \
+        default: RCU_RED(T, RCU_REDUCE_MEAN); break;       \
+    }
+    switch (x->dt) {
+        case RCU_F32: RCU_RED_T(float) break;
+        case RCU_F16: RCU_RED_T(__half) break;
+        case RCU_BF16: RCU_RED_T(__nv_bfloat16) break;
+        default: return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "reduce: dtype %d", x->dt);
+    }
+#undef RCU_RED_T
+#undef RCU_RED
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
+}  // extern "C"
