@@ -47,47 +47,65 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and clock-event (throttle) reasons through NVML every few milliseconds on a
+    background thread while the timed region runs (read-only queries; nothing is set)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index = index
-        self.samples = []
-        self.proc = None
+        self.period = period_s
+        self.samples = []   # (sm_mhz, reasons_bitmask)
+        self.max_mhz = None
+        self._stop = threading.Event()
         self.thread = None
+        self.nvml = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            # honour CUDA_VISIBLE_DEVICES: map the CUDA ordinal to the NVML device by UUID
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 6:
-                self.samples.append(parts)
+    def _run(self):
+        nv = self.nvml
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                self.samples.append((float(mhz), int(reasons)))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
-    def stop(self):
-        if self.proc is None:
+    def mark(self):
+        """Index of the next sample: brackets the timed region inside the sample list."""
+        return len(self.samples)
+
+    def stop(self, lo=0, hi=None):
+        if self.nvml is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(self.samples)}
+        self._stop.set()
+        self.thread.join(timeout=2)
+        nv = self.nvml
+        window = self.samples[lo:hi] or self.samples
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        reasons = [n for n, bit in names.items() if any(r & bit for _, r in window)]
+        sm = [m for m, _ in window]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(window)}
 
 
 def make_weights(N, K, seed):
@@ -188,7 +206,7 @@ def run_ours(args):
     stream = torch.cuda.current_stream()
     dev = Device(local_rank, stream=stream.cuda_stream)
 
-    K, N = K_HEAD, N_HEAD
+    K, N = K_HEAD, (args.rows or N_HEAD)
     n_local = N // world
     wq = make_weights(n_local, K, seed=1000 + rank)
     dw = dev.from_quantized(wq, capi.Q8_0F, (n_local, K))
@@ -228,11 +246,13 @@ def run_ours(args):
     launches0 = dev.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    mark0 = sampler.mark()
     ev0.record(stream)
     for _ in range(args.steps):
         step()
     ev1.record(stream)
     barrier()
+    mark1 = sampler.mark()
     ms = ev0.elapsed_time(ev1)
     launches = dev.launches - launches0
     # kernel-only duration of the GEMV (no collective), for the roofline of the dominant kernel
@@ -252,7 +272,7 @@ def run_ours(args):
         step_e2e()
     barrier()
     e2e_s = (time.perf_counter() - t0) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(mark0, max(mark1, mark0 + 1)) if rank == 0 else None
 
     t = torch.tensor([ms, kernel_ms, e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -280,7 +300,7 @@ def run_ours(args):
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "gemv_q8_kernel",
                          "kernel_ms": kernel_ms, "bytes_per_launch": local_bytes, "traffic": None},
         }
-        if world == 1:
+        if world == 1 and not args.rows:
             line["cpu_baseline"] = cpu_baseline_sample(K, N)
         print(json.dumps(line))
     dev.close()
@@ -291,9 +311,12 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=0,
+                    help="profiling aid: run the same GEMV with this many rows instead of 65536 (no CPU baseline); "
+                         "8192 rows = 134 MB of weights, still larger than L2, small enough for an ncu capture")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
