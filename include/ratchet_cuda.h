@@ -165,6 +165,58 @@ rcu_status rcu_index_write(rcu_device* dev, rcu_tensor* dst, const rcu_tensor* s
 rcu_status rcu_conv1d(rcu_device* dev, const rcu_tensor* x, const rcu_tensor* w, const rcu_tensor* bias,
                       uint32_t stride, uint32_t padding, rcu_tensor* dst);
 
+/* ------------------------------------------------------------------ lazy tensor graph (tensor.rs)
+ * rcu_lazy is ratchet-core's `Tensor` (tensor.rs:45-47): a reference-counted node of a lazy DAG.
+ * Builders validate their arguments and compute the output view exactly when the reference's
+ * builder methods do (tensor.rs:294-510); nothing runs on the device until rcu_lazy_resolve
+ * (Tensor::resolve, tensor.rs:861-863), which walks the graph in the reference's execution order
+ * (tensor.rs:696-740), plans buffers by liveness with greedy-by-size sharing and in-place leasing
+ * (gpu/buffer_allocator/allocator.rs:141-340) and launches one kernel per node on the device's
+ * stream.  A handle owns one reference; rcu_lazy_release drops it (Drop for Tensor).  Builders
+ * retain their sources, so a source handle may be released right after building on it — which is
+ * what lets an op run in place (tensor.rs:823-824: only when the op is the source's sole owner). */
+typedef struct rcu_lazy rcu_lazy;
+
+/* Tensor::from_data / from_quantized: copy host bytes into a new pooled device buffer (resolved leaf). */
+rcu_status rcu_lazy_from_host(rcu_device* dev, int32_t dt, uint32_t rank, const uint64_t* shape, const void* host,
+                              uint64_t nbytes, rcu_lazy** out);
+/* Tensor::zeros */
+rcu_status rcu_lazy_zeros(rcu_device* dev, int32_t dt, uint32_t rank, const uint64_t* shape, rcu_lazy** out);
+/* A resolved leaf over device memory the caller owns (never freed by the library). */
+rcu_status rcu_lazy_wrap(rcu_device* dev, const rcu_tensor* t, rcu_lazy** out);
+void rcu_lazy_retain(rcu_lazy* t);
+void rcu_lazy_release(rcu_lazy* t);
+/* shape / dtype / device pointer (NULL until resolved); returns 1 if resolved (Tensor::resolved). */
+int rcu_lazy_info(const rcu_lazy* t, rcu_tensor* out);
+/* Arc::strong_count of the node (handles + consumers). */
+uint32_t rcu_lazy_strong_count(const rcu_lazy* t);
+
+rcu_status rcu_lazy_binary(int op, rcu_lazy* a, rcu_lazy* b, rcu_lazy** out);
+rcu_status rcu_lazy_unary(int op, rcu_lazy* x, rcu_lazy** out);
+rcu_status rcu_lazy_cast(rcu_lazy* x, int32_t dt, rcu_lazy** out);
+rcu_status rcu_lazy_norm(int kind, rcu_lazy* x, rcu_lazy* scale, rcu_lazy* bias, float eps, uint32_t groups, rcu_lazy** out);
+rcu_status rcu_lazy_softmax(rcu_lazy* x, uint32_t dim, rcu_lazy** out);
+rcu_status rcu_lazy_rope(rcu_lazy* x, uint32_t dim, float base, uint32_t offset, rcu_lazy** out);
+rcu_status rcu_lazy_matmul(rcu_lazy* lhs, rcu_lazy* rhs, rcu_lazy* bias, int trans_lhs, int trans_rhs, int trans_dst, rcu_lazy** out);
+rcu_status rcu_lazy_conv1d(rcu_lazy* x, rcu_lazy* w, rcu_lazy* bias, uint32_t stride, uint32_t padding, rcu_lazy** out);
+rcu_status rcu_lazy_view(rcu_lazy* x, uint32_t rank, const uint64_t* shape, rcu_lazy** out);
+rcu_status rcu_lazy_slice(rcu_lazy* x, const uint64_t* start, const uint64_t* stop, rcu_lazy** out);
+rcu_status rcu_lazy_permute(rcu_lazy* x, const uint32_t* perm, rcu_lazy** out);
+rcu_status rcu_lazy_broadcast(rcu_lazy* x, uint32_t rank, const uint64_t* shape, rcu_lazy** out);
+rcu_status rcu_lazy_concat(rcu_lazy* const* inputs, uint32_t n, uint32_t dim, rcu_lazy** out);
+rcu_status rcu_lazy_index_select(rcu_lazy* src, rcu_lazy* ids, uint32_t dim, rcu_lazy** out);
+rcu_status rcu_lazy_cache(rcu_lazy* cache, rcu_lazy* src, uint32_t dim, uint32_t offset, rcu_lazy** out);
+rcu_status rcu_lazy_index_write(rcu_lazy* dst, rcu_lazy* src, const uint64_t* start, rcu_lazy** out);
+
+/* Tensor::resolve: run every unresolved node `t` depends on.  Asynchronous on the device stream. */
+rcu_status rcu_lazy_resolve(rcu_lazy* t);
+/* Tensor::to(Device::CPU): resolve if needed, copy to host, block. */
+rcu_status rcu_lazy_to_host(rcu_lazy* t, void* host, uint64_t nbytes);
+/* Counters of the last resolve on this device: nodes visited, kernels launched, ops run in place,
+ * bytes of distinct buffers planned vs bytes if every node had its own (allocator.rs:330-337). */
+typedef struct { uint32_t nodes, launched, inplace, buffers; uint64_t planned_bytes, naive_bytes; } rcu_resolve_stats;
+void rcu_last_resolve_stats(rcu_device* dev, rcu_resolve_stats* out);
+
 #ifdef __cplusplus
 }
 #endif

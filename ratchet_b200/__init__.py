@@ -8,5 +8,6 @@ or a B200 is missing.
 from . import capi
 from .capi import RatchetCudaError
 from .device import Buffer, Device
+from .tensor import Tensor, last_resolve_stats
 
-__all__ = ["capi", "Buffer", "Device", "RatchetCudaError"]
+__all__ = ["capi", "Buffer", "Device", "RatchetCudaError", "Tensor", "last_resolve_stats"]

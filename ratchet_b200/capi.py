@@ -45,8 +45,14 @@ class rcu_tensor(C.Structure):
     _fields_ = [("dt", C.c_int32), ("rank", C.c_uint32), ("shape", C.c_uint64 * RCU_MAX_RANK), ("data", C.c_void_p)]
 
 
+class rcu_resolve_stats(C.Structure):
+    _fields_ = [("nodes", C.c_uint32), ("launched", C.c_uint32), ("inplace", C.c_uint32), ("buffers", C.c_uint32),
+                ("planned_bytes", C.c_uint64), ("naive_bytes", C.c_uint64)]
+
+
 _T = C.POINTER(rcu_tensor)
 _DEV = C.c_void_p
+_LZ = C.c_void_p
 _u64p = C.POINTER(C.c_uint64)
 _u32p = C.POINTER(C.c_uint32)
 
@@ -88,6 +94,33 @@ SIGNATURES = {
     "rcu_cache": (C.c_int, [_DEV, _T, _T, C.c_uint32, C.c_uint32, _T]),
     "rcu_index_write": (C.c_int, [_DEV, _T, _T, _u64p]),
     "rcu_conv1d": (C.c_int, [_DEV, _T, _T, _T, C.c_uint32, C.c_uint32, _T]),
+    # lazy tensor graph
+    "rcu_lazy_from_host": (C.c_int, [_DEV, C.c_int32, C.c_uint32, _u64p, C.c_void_p, C.c_uint64, C.POINTER(_LZ)]),
+    "rcu_lazy_zeros": (C.c_int, [_DEV, C.c_int32, C.c_uint32, _u64p, C.POINTER(_LZ)]),
+    "rcu_lazy_wrap": (C.c_int, [_DEV, _T, C.POINTER(_LZ)]),
+    "rcu_lazy_retain": (None, [_LZ]),
+    "rcu_lazy_release": (None, [_LZ]),
+    "rcu_lazy_info": (C.c_int, [_LZ, _T]),
+    "rcu_lazy_strong_count": (C.c_uint32, [_LZ]),
+    "rcu_lazy_binary": (C.c_int, [C.c_int, _LZ, _LZ, C.POINTER(_LZ)]),
+    "rcu_lazy_unary": (C.c_int, [C.c_int, _LZ, C.POINTER(_LZ)]),
+    "rcu_lazy_cast": (C.c_int, [_LZ, C.c_int32, C.POINTER(_LZ)]),
+    "rcu_lazy_norm": (C.c_int, [C.c_int, _LZ, _LZ, _LZ, C.c_float, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_softmax": (C.c_int, [_LZ, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_rope": (C.c_int, [_LZ, C.c_uint32, C.c_float, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_matmul": (C.c_int, [_LZ, _LZ, _LZ, C.c_int, C.c_int, C.c_int, C.POINTER(_LZ)]),
+    "rcu_lazy_conv1d": (C.c_int, [_LZ, _LZ, _LZ, C.c_uint32, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_view": (C.c_int, [_LZ, C.c_uint32, _u64p, C.POINTER(_LZ)]),
+    "rcu_lazy_slice": (C.c_int, [_LZ, _u64p, _u64p, C.POINTER(_LZ)]),
+    "rcu_lazy_permute": (C.c_int, [_LZ, _u32p, C.POINTER(_LZ)]),
+    "rcu_lazy_broadcast": (C.c_int, [_LZ, C.c_uint32, _u64p, C.POINTER(_LZ)]),
+    "rcu_lazy_concat": (C.c_int, [C.POINTER(_LZ), C.c_uint32, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_index_select": (C.c_int, [_LZ, _LZ, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_cache": (C.c_int, [_LZ, _LZ, C.c_uint32, C.c_uint32, C.POINTER(_LZ)]),
+    "rcu_lazy_index_write": (C.c_int, [_LZ, _LZ, _u64p, C.POINTER(_LZ)]),
+    "rcu_lazy_resolve": (C.c_int, [_LZ]),
+    "rcu_lazy_to_host": (C.c_int, [_LZ, C.c_void_p, C.c_uint64]),
+    "rcu_last_resolve_stats": (None, [_DEV, C.POINTER(rcu_resolve_stats)]),
 }
 
 _lib = None

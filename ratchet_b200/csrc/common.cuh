@@ -39,6 +39,7 @@ struct rcu_device {
     rcu_pool pool;
     int* d_status = nullptr;     // device-side status word: bounds / timeout flags raised by kernels
     int* h_status = nullptr;     // pinned host mirror
+    rcu_resolve_stats last_resolve = {};   // counters of the last lazy-graph resolve (graph.cu)
     void* comm = nullptr;        // communicator state, owned by comm.cu
     // per-device resources created lazily by individual ops; run at rcu_device_destroy
     std::vector<std::pair<void (*)(void*), void*>> cleanup;
