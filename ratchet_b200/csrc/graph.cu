@@ -37,6 +37,9 @@ struct Storage {
     void* ptr;
     uint64_t nbytes;
     bool owned;
+    Storage(rcu_device* d, void* p, uint64_t n, bool o) : dev(d), ptr(p), nbytes(n), owned(o) {}
+    Storage(const Storage&) = delete;              // exactly one owner returns the block to the pool
+    Storage& operator=(const Storage&) = delete;
     ~Storage() {
         if (owned && ptr) rcu_free(dev, ptr);
     }
@@ -332,7 +335,7 @@ rcu_status resolve(rcu_lazy* out) {
             void* ptr = nullptr;
             st = rcu_alloc(dev, p.size, &ptr);
             if (st != RCU_OK) return st;
-            objects.push_back(Object{p.size, std::make_shared<Storage>(Storage{dev, ptr, p.size, true}), {}, p.exclusive});
+            objects.push_back(Object{p.size, std::make_shared<Storage>(dev, ptr, p.size, true), {}, p.exclusive});
             planned += p.size;
             best = (int)objects.size() - 1;
         }
@@ -382,7 +385,7 @@ rcu_status rcu_lazy_from_host(rcu_device* dev, int32_t dt, uint32_t rank, const 
     void* ptr = nullptr;
     rcu_status st = rcu_alloc(dev, need, &ptr);
     if (st != RCU_OK) { delete n; return st; }
-    n->storage = std::make_shared<Storage>(Storage{dev, ptr, need, true});
+    n->storage = std::make_shared<Storage>(dev, ptr, need, true);
     if (host) {
         if (nbytes > need) nbytes = need;
         st = rcu_h2d(dev, ptr, host, nbytes);
@@ -403,7 +406,7 @@ rcu_status rcu_lazy_zeros(rcu_device* dev, int32_t dt, uint32_t rank, const uint
 rcu_status rcu_lazy_wrap(rcu_device* dev, const rcu_tensor* t, rcu_lazy** out) {
     if (!dev || !out || !t_valid(t)) return RCU_ERR_INVALID_ARG;
     rcu_lazy* n = new_node(dev, K_CONST, t->dt, t->rank, t->shape, {});
-    n->storage = std::make_shared<Storage>(Storage{dev, t->data, n->nbytes(), false});
+    n->storage = std::make_shared<Storage>(dev, t->data, n->nbytes(), false);
     *out = n;
     return RCU_OK;
 }
