@@ -189,6 +189,143 @@ def cpu_baseline_sample(K, N):
             "sample": f"{rows} of {N} rows, {reps} repetitions (~10 s)"}
 
 
+# DRAM bytes per weight row of the headline GEMV (K=16384), from the ncu capture summarised in
+# profiles/gemv_q8_kernel_K16384_N8192.md: (dram__bytes_read.sum + dram__bytes_write.sum) / rows.
+GEMV_TRAFFIC_PER_ROW_BYTES = (151.047936e6 + 3.8e6) / 8192
+
+SWEEP_SHAPES = [(3072, 3072), (3072, 16384), (8192, 3072)]   # (K, N) of the decode sweep below the headline shape
+
+
+def _time_loop(torch, stream, fn, iters):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream.synchronize()
+    e0.record(stream)
+    for i in range(iters):
+        fn(i)
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def gemv_sweep(dev, torch, stream):
+    """The smaller (K,N) pairs of the GEMV sweep.  They fit in L2 (126 MB), so each is timed twice:
+    'cold' rotates through enough distinct weight copies to exceed 2x L2 between reuses, 'warm'
+    re-reads one copy (L2 resident)."""
+    from ratchet_b200 import capi
+    peak, _ = measured_peak()
+    out = []
+    for K, N in SWEEP_SHAPES:
+        wq = make_weights(N, K, seed=K + N)
+        copies = max(2, int(300e6 // wq.nbytes) + 1)
+        bufs = [dev.from_quantized(wq, capi.Q8_0F, (N, K)) for _ in range(copies)]
+        x = dev.from_numpy(np.random.Generator(np.random.PCG64(3)).standard_normal((1, K)).astype(np.float16))
+        y = dev.empty(capi.F16, (1, N))
+        run = lambda i: dev.matmul(bufs[i % copies], x, None, False, True, True, out=y)
+        for i in range(copies):
+            run(i)
+        cold_ms = _time_loop(torch, stream, run, copies * 10)
+        warm_ms = _time_loop(torch, stream, lambda i: run(0), 200)
+        b = gemv_bytes(N, K)
+        out.append({"K": K, "N": N, "bytes": b, "cold_us": cold_ms * 1e3, "cold_gbs": b / cold_ms / 1e6, "cold_frac_of_measured": b / cold_ms / 1e6 / peak,
+                    "warm_us": warm_ms * 1e3, "warm_gbs": b / warm_ms / 1e6, "weight_copies_rotated": copies})
+        for bf in bufs:
+            bf.free()
+    return out
+
+
+PHI3 = dict(n_layers=32, d=3072, n_heads=32, head_dim=96, ffn=8192, vocab=32064, max_cache=4096, kv_prior=1024)
+
+
+def _q8h_weights(N, K, seed):
+    """Q8_0H buffer (f16 scales) with random int8 codes and scales of N(0,0.02)-like magnitude.  Built
+    directly in the quantised domain: the decode benchmark needs the bytes, not a float original."""
+    from ratchet_b200 import capi
+    rng = np.random.Generator(np.random.PCG64(seed))
+    buf = np.zeros(capi.dtype_nbytes(capi.Q8_0H, N * K), np.uint8)
+    uniq = min(N, 1024)
+    q = rng.integers(-127, 128, (uniq, K), dtype=np.int8)
+    d = (np.abs(rng.standard_normal((uniq, K // 32))) * 0.0004 + 0.0003).astype(np.float16)
+    qs = buf[: N * K].view(np.int8).reshape(N, K)
+    off = capi.dtype_segments(capi.Q8_0H, N * K)[1]
+    ds = buf[off: off + (N * K // 32) * 2].view(np.float16).reshape(N, K // 32)
+    for r0 in range(0, N, uniq):
+        r1 = min(N, r0 + uniq)
+        qs[r0:r1] = q[: r1 - r0]
+        ds[r0:r1] = d[: r1 - r0]
+    return buf
+
+
+def phi3_decode_bytes(c):
+    """Algorithmic HBM bytes of one decode step: Q8_0H weights (1 + 2/32 bytes per element) of every
+    Linear + one embedding row, K and V rows of the populated cache, negligible activations."""
+    d, ffn, V, L = c["d"], c["ffn"], c["vocab"], c["n_layers"]
+    w_elems = L * (3 * d * d + d * d + 2 * ffn * d + d * ffn) + V * d
+    kv = L * 2 * c["n_heads"] * (c["kv_prior"] + 1) * c["head_dim"] * 2
+    return int(w_elems * (1 + 2 / 32)) + kv + d * (1 + 2 / 32)
+
+
+def phi3_decode_bench(dev, torch, stream, steps, warmup):
+    """Phi-3-mini decode step (32 layers, hidden 3072, 32 heads x 96, MLP 8192, vocab 32064, Q8_0H
+    weights, 1024 prior KV positions of N(0,1) f16, batch 1) through the fused decode engine."""
+    from ratchet_b200 import capi
+    from ratchet_b200.decoder import Decoder, DecoderConfig, DecoderLayer
+    c = PHI3
+    d, H, hd, ffn, V = c["d"], c["n_heads"], c["head_dim"], c["ffn"], c["vocab"]
+    rng = np.random.Generator(np.random.PCG64(11))
+    host = {"qkv": _q8h_weights(3 * d, d, 1), "o": _q8h_weights(d, d, 2), "up": _q8h_weights(2 * ffn, d, 3), "down": _q8h_weights(d, ffn, 4)}
+    kv_host = np.zeros((H, c["max_cache"], hd), np.float16)
+    kv_host[:, : c["kv_prior"]] = rng.standard_normal((H, c["kv_prior"], hd)).astype(np.float16)
+    ones = np.ones(d, np.float32)
+    layers = []
+    for _ in range(c["n_layers"]):   # every layer gets its own device copy: the step streams 32 distinct sets
+        layers.append(DecoderLayer(dev.from_numpy(ones), dev.from_quantized(host["qkv"], capi.Q8_0H, (3 * d, d)),
+                                   dev.from_quantized(host["o"], capi.Q8_0H, (d, d)), dev.from_numpy(ones),
+                                   dev.from_quantized(host["up"], capi.Q8_0H, (2 * ffn, d)), dev.from_quantized(host["down"], capi.Q8_0H, (d, ffn)),
+                                   dev.from_numpy(kv_host), dev.from_numpy(kv_host)))
+    emb = dev.from_quantized(_q8h_weights(V, d, 5), capi.Q8_0H, (V, d))
+    head = dev.from_quantized(_q8h_weights(V, d, 6), capi.Q8_0H, (V, d))
+    cfg = DecoderConfig(c["n_layers"], d, H, H, hd, ffn, V, c["max_cache"], hd, 10000.0, 1e-5, capi.Q8_0H)
+    dec = Decoder(dev, cfg, layers, emb, dev.from_numpy(ones), head)
+    tok_host = torch.tensor([int(rng.integers(0, V))], dtype=torch.int32).pin_memory()
+    tok_dev = torch.empty(1, dtype=torch.int32, device="cuda")
+    tok_dev.copy_(tok_host)
+    logits_host = torch.empty(V, dtype=torch.float16).pin_memory()
+    logits_dev = torch.empty(V, dtype=torch.float16, device="cuda")
+    import ctypes as C
+
+    def step(_i=0):
+        dec.position = c["kv_prior"]          # keep the workload fixed: 1024 prior positions every step
+        dev.check(dev._lib.rcu_decoder_step(dec._h, C.c_void_p(tok_dev.data_ptr()), C.c_void_p(logits_dev.data_ptr()), None))
+
+    def step_e2e(_i=0):
+        tok_dev.copy_(tok_host, non_blocking=True)     # ids up (phi3/generate.rs:95-96)
+        step()
+        logits_host.copy_(logits_dev, non_blocking=True)   # logits down, arg-max on the host (generate.rs:101-108)
+        stream.synchronize()
+        tok_host[0] = int(torch.argmax(logits_host.float()))
+
+    for _ in range(warmup):
+        step()
+    l0 = dev.launches
+    ms = _time_loop(torch, stream, step, steps)
+    launches = (dev.launches - l0) // steps
+    for _ in range(3):
+        step_e2e()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step_e2e()
+    e2e_s = (time.perf_counter() - t0) / steps
+    b = phi3_decode_bytes(c)
+    peak, kind = measured_peak()
+    res = {"metric": "phi3_mini_q8_0_decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "ms_per_token": ms,
+           "e2e_tokens_per_s": 1.0 / e2e_s, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": V * 2,
+           "kernels_per_token": int(launches), "algorithmic_bytes_per_token": b, "achieved_gbs": b / ms / 1e6,
+           "roofline_frac": b / ms / 1e6 / peak, "roofline_tokens_per_s": peak * 1e9 / b, "peak_kind": f"of {kind}",
+           "config": {"model": "phi-3-mini shape, random Q8_0H weights", **c, "steps": steps}}
+    dec.close()
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -285,6 +422,7 @@ def run_ours(args):
     local_bytes = gemv_bytes(n_local, K)
     achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
 
+    line = {}
     if rank == 0:
         line = {
             "metric": "q8_0_gemv_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -300,8 +438,17 @@ def run_ours(args):
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "gemv_q8_kernel",
                          "kernel_ms": kernel_ms, "bytes_per_launch": local_bytes, "traffic": None},
         }
+        line["roofline"]["traffic"] = GEMV_TRAFFIC_PER_ROW_BYTES * n_local
         if world == 1 and not args.rows:
             line["cpu_baseline"] = cpu_baseline_sample(K, N)
+    # release the GEMV weights before the other legs allocate theirs
+    del dw
+    extras = {}
+    if world == 1 and not args.rows and not args.no_extras:
+        extras["gemv_sweep"] = gemv_sweep(dev, torch, stream)
+        extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
+    if rank == 0:
+        line.update(extras)
         print(json.dumps(line))
     dev.close()
     if world > 1:
@@ -317,6 +464,7 @@ def main():
     ap.add_argument("--rows", type=int, default=0,
                     help="profiling aid: run the same GEMV with this many rows instead of 65536 (no CPU baseline); "
                          "8192 rows = 134 MB of weights, still larger than L2, small enough for an ncu capture")
+    ap.add_argument("--no-extras", action="store_true", help="skip the GEMV sweep and the Phi-3 decode leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

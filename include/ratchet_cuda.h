@@ -217,6 +217,56 @@ rcu_status rcu_lazy_to_host(rcu_lazy* t, void* host, uint64_t nbytes);
 typedef struct { uint32_t nodes, launched, inplace, buffers; uint64_t planned_bytes, naive_bytes; } rcu_resolve_stats;
 void rcu_last_resolve_stats(rcu_device* dev, rcu_resolve_stats* out);
 
+/* ------------------------------------------------------------------ fused decode step
+ * One decoder-only transformer step at sequence length 1 — the graph Phi3::schedule builds per
+ * token (ratchet-models/src/phi3/model.rs:134-156, attn.rs:88-159, mlp.rs:31-39) — executed as a
+ * fixed sequence of fused kernels replayed from a CUDA graph instead of ~43 kernels per layer:
+ *   embedding row gather (Q8_0 dequant) -> per layer { RMSNorm+qkv GEMV, RoPE + KV append +
+ *   split-KV attention, o GEMV + residual, RMSNorm + gate_up GEMV + SiLU gate, down GEMV + residual }
+ *   -> RMSNorm + lm_head GEMV (-> optional argmax).
+ * Weights are ratchet Q8_0 buffers (Q8_0H or Q8_0F), activations f16, norm scales f32, KV caches
+ * f16 [n_kv_heads, max_cache, head_dim] per layer as ratchet-nn allocates them (kv_cache.rs:11-18).
+ * All pointers are device memory owned by the caller and must outlive the decoder. */
+typedef struct rcu_decoder rcu_decoder;
+typedef struct {
+    uint32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn, vocab, max_cache, rope_dim;
+    float rope_base, rms_eps;
+    int32_t weight_dt; /* RCU_Q8_0H or RCU_Q8_0F */
+} rcu_decoder_config;
+typedef struct {
+    const void* attn_norm; /* f32 [d_model] */
+    const void* qkv;       /* Q8_0 [(n_heads + 2 n_kv_heads) * head_dim, d_model] */
+    const void* o;         /* Q8_0 [d_model, n_heads * head_dim] */
+    const void* ffn_norm;  /* f32 [d_model] */
+    const void* gate_up;   /* Q8_0 [2 ffn, d_model]: gate rows then up rows */
+    const void* down;      /* Q8_0 [d_model, ffn] */
+    void* k_cache;         /* f16 [n_kv_heads, max_cache, head_dim] */
+    void* v_cache;
+} rcu_decoder_layer;
+rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers,
+                              const void* tok_embd /* Q8_0 [vocab, d_model] */, const void* out_norm /* f32 [d_model] */,
+                              const void* lm_head /* Q8_0 [vocab, d_model] */, rcu_decoder** out);
+void rcu_decoder_destroy(rcu_decoder* dec);
+/* Number of KV entries already in the caches = position of the next token (KVCache::entries). */
+rcu_status rcu_decoder_set_position(rcu_decoder* dec, uint32_t position);
+uint32_t rcu_decoder_position(const rcu_decoder* dec);
+/* Run one step for the token id at `token_dev` (device int32). Writes f16 logits [vocab] to
+ * `logits_dev` and, when `argmax_dev` is not NULL, the arg-max token id (device int32) — which may
+ * be the same address as `token_dev` for greedy generation without a host round trip.  Advances the
+ * position by one (KVCache::update(1)).  Asynchronous on the device stream. */
+rcu_status rcu_decoder_step(rcu_decoder* dec, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev);
+/* Kernels per step of the captured graph (profiling aid). */
+uint32_t rcu_decoder_kernels_per_step(const rcu_decoder* dec);
+
+/* Decode attention for one layer, standalone (the kernel rcu_decoder_step uses): RoPE on q and k
+ * (ops/rope.rs), append k/v at `position` (ops/cache.rs), softmax(q.K^T * scale).V over
+ * position + 1 entries (phi3/attn.rs:142-157).  qkv is f16 [(n_heads + 2 n_kv_heads) * head_dim];
+ * out is f16 [n_heads * head_dim].  Split-KV partial results go through device scratch memory that
+ * the device handle allocates on first use. */
+rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void* v_cache, uint32_t n_heads,
+                           uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_cache, uint32_t rope_dim, float rope_base,
+                           uint32_t position, void* out);
+
 #ifdef __cplusplus
 }
 #endif

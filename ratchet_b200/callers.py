@@ -29,6 +29,12 @@ class Phi3SelfAttention:
         hdim = n_state // self.n_heads
         kv_x_hdim = self.n_kv_heads * hdim
         qkv = self.qkv.schedule(x)
+        return self.o.schedule(self.attend(qkv, batch, q_len, n_state, mask, cache))
+
+    def attend(self, qkv, batch, q_len, n_state, mask=None, cache: Optional[KVEntry] = None):
+        """Everything between the fused qkv projection and the output projection (attn.rs:95-157)."""
+        hdim = n_state // self.n_heads
+        kv_x_hdim = self.n_kv_heads * hdim
         query_pos = self.n_heads * hdim
         key_pos = query_pos + kv_x_hdim
         value_pos = key_pos + kv_x_hdim
@@ -50,8 +56,7 @@ class Phi3SelfAttention:
             attn = attn.add(mask.cast(attn.dt()))
         w = attn.full().softmax(3).cast(v.dt())
         wv = w.matmul(v, False, False).permute([0, 2, 1, 3])
-        wv = wv.view([batch, q_len, n_state])
-        return self.o.schedule(wv)
+        return wv.view([batch, q_len, n_state])
 
 
 class Phi3MLP:

@@ -50,6 +50,17 @@ class rcu_resolve_stats(C.Structure):
                 ("planned_bytes", C.c_uint64), ("naive_bytes", C.c_uint64)]
 
 
+class rcu_decoder_config(C.Structure):
+    _fields_ = [("n_layers", C.c_uint32), ("d_model", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
+                ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32), ("max_cache", C.c_uint32),
+                ("rope_dim", C.c_uint32), ("rope_base", C.c_float), ("rms_eps", C.c_float), ("weight_dt", C.c_int32)]
+
+
+class rcu_decoder_layer(C.Structure):
+    _fields_ = [("attn_norm", C.c_void_p), ("qkv", C.c_void_p), ("o", C.c_void_p), ("ffn_norm", C.c_void_p),
+                ("gate_up", C.c_void_p), ("down", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
 _T = C.POINTER(rcu_tensor)
 _DEV = C.c_void_p
 _LZ = C.c_void_p
@@ -121,6 +132,16 @@ SIGNATURES = {
     "rcu_lazy_resolve": (C.c_int, [_LZ]),
     "rcu_lazy_to_host": (C.c_int, [_LZ, C.c_void_p, C.c_uint64]),
     "rcu_last_resolve_stats": (None, [_DEV, C.POINTER(rcu_resolve_stats)]),
+    # fused decode step
+    "rcu_decoder_create": (C.c_int, [_DEV, C.POINTER(rcu_decoder_config), C.POINTER(rcu_decoder_layer), C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.POINTER(C.c_void_p)]),
+    "rcu_decoder_destroy": (None, [C.c_void_p]),
+    "rcu_decoder_set_position": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "rcu_decoder_position": (C.c_uint32, [C.c_void_p]),
+    "rcu_decoder_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "rcu_decoder_kernels_per_step": (C.c_uint32, [C.c_void_p]),
+    "rcu_attn_decode": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                  C.c_uint32, C.c_float, C.c_uint32, C.c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,357 @@
+// Q8_0 GEMV kernel template shared by the Matmul entry point (plain prologue / epilogue) and the
+// decode engine (fused RMSNorm prologue, residual and SiLU-gate epilogues).
+//
+// y[N] = W[N,K] . x[K], W = ratchet Q8_0 segments (int8 qs row-major, one scale per 32 along K).
+// Takes the place of ratchet-core's subgroup_gemv / workgroup_gemv WGSL kernels
+// (ops/matmul/subgroup_gemv.rs:89-309, ops/matmul/workgroup_gemv.rs:221-371).
+//
+// The kernel is HBM-bound: every weight byte is read exactly once.  Layout of the work:
+//   * persistent CTAs (a multiple of the SM count), 8 warps each; the Prologue stages the activation
+//     vector once per CTA in shared memory (optionally normalising it on the way);
+//   * output units (a row, or a gate/up row pair) are dealt to warps as contiguous ranges balanced
+//     to one unit, so there is no tail wave;
+//   * a warp walks K in 512-element chunks, each lane owning 16 consecutive int8 (one 16-byte
+//     streaming load per row per chunk), ROWS rows at a time so that ROWS x UNROLL loads are in
+//     flight per lane and the activation registers are reused ROWS times;
+//   * int8 -> float conversion is exact, products are accumulated in f32, one f32 multiply by the
+//     block scale per 16 elements, warp-shuffle reduction at the end;
+//   * small N: KSPLIT warps share a unit range and split K, combined through shared memory.
+#pragma once
+#include "common.cuh"
+
+namespace gemvq8 {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// f32 += f16 * f16 (exact product, f32 accumulate); sm_100 mixed-precision fma.
+__device__ __forceinline__ float fma_mixed(uint16_t a, uint16_t b, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void split_h2(uint32_t v, uint16_t& lo, uint16_t& hi) {
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(v));
+}
+
+// four packed int8 -> two half2 holding the exact integer values:
+// byte ^ 0x80 placed in the mantissa of 1024.0h gives 1024 + (q + 128); subtract 1152.
+__device__ __forceinline__ void i8x4_to_h2x2(uint32_t w, uint32_t& h01, uint32_t& h23) {
+    const uint32_t t = w ^ 0x80808080u;
+    const uint32_t a = prmt(t, 0x64646464u, 0x4140u);
+    const uint32_t b = prmt(t, 0x64646464u, 0x4342u);
+    const __half2 k = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+    __half2 ha = __hsub2(*reinterpret_cast<const __half2*>(&a), k);
+    __half2 hb = __hsub2(*reinterpret_cast<const __half2*>(&b), k);
+    h01 = *reinterpret_cast<uint32_t*>(&ha);
+    h23 = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+// four packed int8 -> four exact floats: byte ^ 0x80 in the mantissa of 2^23, minus (2^23 + 128)
+__device__ __forceinline__ void i8x4_to_f32x4(uint32_t w, float q[4]) {
+    const uint32_t t = w ^ 0x80808080u;
+    q[0] = __uint_as_float(prmt(t, 0x4B000000u, 0x7440u)) - 8388736.f;
+    q[1] = __uint_as_float(prmt(t, 0x4B000000u, 0x7441u)) - 8388736.f;
+    q[2] = __uint_as_float(prmt(t, 0x4B000000u, 0x7442u)) - 8388736.f;
+    q[3] = __uint_as_float(prmt(t, 0x4B000000u, 0x7443u)) - 8388736.f;
+}
+
+// Dot of 16 int8 (one uint4) with 16 activations held in registers.
+// MODE 0: f16 activations stay packed, mixed-precision fma.  MODE 1: activations widened to f32
+// once per chunk (shared by all ROWS rows), int8 -> f32 through the mantissa trick, FFMA.
+template <class ActT, int MODE> struct Dot16;
+
+template <> struct Dot16<__half, 0> {
+    uint32_t x[8];
+    __device__ __forceinline__ void load(const __half* xs, int k) {
+        const uint4 a = *reinterpret_cast<const uint4*>(xs + k);
+        const uint4 b = *reinterpret_cast<const uint4*>(xs + k + 8);
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+    __device__ __forceinline__ float dot(const uint4& w) const {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t h01, h23;
+            i8x4_to_h2x2(ws[i], h01, h23);
+            uint16_t q0, q1, q2, q3, x0, x1, x2, x3;
+            split_h2(h01, q0, q1);
+            split_h2(h23, q2, q3);
+            split_h2(x[2 * i], x0, x1);
+            split_h2(x[2 * i + 1], x2, x3);
+            p0 = fma_mixed(q0, x0, p0);
+            p1 = fma_mixed(q1, x1, p1);
+            p0 = fma_mixed(q2, x2, p0);
+            p1 = fma_mixed(q3, x3, p1);
+        }
+        return p0 + p1;
+    }
+};
+
+template <class ActT> struct Dot16<ActT, 1> {
+    float x[16];
+    __device__ __forceinline__ void load(const ActT* xs, int k) {
+        if constexpr (sizeof(ActT) == 4) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(xs) + k + 4 * i);
+                x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+            }
+        } else {
+            const uint4 a = *reinterpret_cast<const uint4*>(xs + k);
+            const uint4 b = *reinterpret_cast<const uint4*>(xs + k + 8);
+            const uint32_t h[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+                x[2 * i] = f.x; x[2 * i + 1] = f.y;
+            }
+        }
+    }
+    __device__ __forceinline__ float dot(const uint4& w) const {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float q[4];
+            i8x4_to_f32x4(ws[i], q);
+            p0 = fmaf(q[0], x[4 * i], p0);
+            p1 = fmaf(q[1], x[4 * i + 1], p1);
+            p0 = fmaf(q[2], x[4 * i + 2], p0);
+            p1 = fmaf(q[3], x[4 * i + 3], p1);
+        }
+        return p0 + p1;
+    }
+};
+template <> struct Dot16<float, 0> : Dot16<float, 1> {};
+
+template <class ScaleT> __device__ __forceinline__ float ld_scale(const ScaleT* p);
+template <> __device__ __forceinline__ float ld_scale<float>(const float* p) { return __ldg(p); }
+template <> __device__ __forceinline__ float ld_scale<__half>(const __half* p) {
+    return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(p))));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prologues: stage x[K] into shared memory (all kThreads threads call; caller syncs afterwards).
+// `scratch` is kWarps floats of shared memory.
+// ------------------------------------------------------------------------------------------------
+template <class ActT> struct PlainPrologue {
+    const ActT* x;
+    __device__ __forceinline__ void stage(ActT* xs, int K, float* /*scratch*/) const {
+        const int vec = 16 / (int)sizeof(ActT);
+        const uint4* src = reinterpret_cast<const uint4*>(x);
+        uint4* dst = reinterpret_cast<uint4*>(xs);
+        for (int i = threadIdx.x; i < K / vec; i += kThreads) dst[i] = __ldg(src + i);
+    }
+};
+
+// RMSNorm as ratchet-nn schedules it (ratchet-nn/src/norm.rs:63-69): upcast to f32,
+// y = x * (1/sqrt(mean(x^2) + eps)) * gamma (cpu/norm.rs:185-213), cast back to the input dtype.
+struct RmsNormPrologueH {
+    const __half* x;
+    const float* gamma;
+    float eps;
+    __device__ __forceinline__ void stage(__half* xs, int K, float* scratch) const {
+        float s2 = 0.f;
+        for (int i = threadIdx.x; i < K; i += kThreads) {
+            const float v = __half2float(x[i]);
+            s2 = fmaf(v, v, s2);
+        }
+        s2 = warp_sum(s2);
+        if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = s2;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) tot += scratch[w];
+        const float rstd = 1.0f / sqrtf(tot / (float)K + eps);
+        for (int i = threadIdx.x; i < K; i += kThreads) xs[i] = __float2half_rn(__half2float(x[i]) * rstd * gamma[i]);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// Epilogues: called by lane 0 (or the combining lanes) with the finished f32 sums of one unit.
+// UNIT = rows per unit; row j of unit u is u + j * unit_stride.
+// ------------------------------------------------------------------------------------------------
+template <class ActT> struct PlainEpilogue {
+    static constexpr int UNIT = 1;
+    const ActT* bias;
+    ActT* y;
+    __device__ __forceinline__ void store(int u, const float* acc) const {
+        float s = acc[0];
+        if (bias) s += to_f32<ActT>(bias[u]);
+        y[u] = from_f32<ActT>(s);
+    }
+};
+
+// y = residual + Linear(x): the Linear output is rounded to f16 first, then added in f16
+// (phi3/model.rs:110-116: `residual.add(attn_output)` on f16 tensors).
+struct ResidualEpilogueH {
+    static constexpr int UNIT = 1;
+    const __half* residual;
+    __half* y;
+    __device__ __forceinline__ void store(int u, const float* acc) const {
+        const float lin = __half2float(__float2half_rn(acc[0]));
+        y[u] = __float2half_rn(lin + __half2float(residual[u]));
+    }
+};
+
+// Fused gate_up projection of phi3/mlp.rs:31-39: unit u pairs row u (gate) with row u + N/2 (up);
+// out[u] = up * f16(silu(f32(gate))), silu(x) = x / (1 + exp(-x)) (cpu/unary.rs:64).
+struct SiluGateEpilogueH {
+    static constexpr int UNIT = 2;
+    __half* y;
+    __device__ __forceinline__ void store(int u, const float* acc) const {
+        const float gate = __half2float(__float2half_rn(acc[0]));
+        const float up = __half2float(__float2half_rn(acc[1]));
+        const float act = __half2float(__float2half_rn(gate / (1.0f + expf(-gate))));
+        y[u] = __float2half_rn(up * act);
+    }
+};
+
+template <class ScaleT, class ActT, int KSPLIT, int UNROLL, int MODE, class Prologue, class Epilogue>
+__global__ void __launch_bounds__(kThreads)
+gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales, Prologue pro, Epilogue epi, int n_units,
+               int unit_stride, int K) {
+    constexpr int UNIT = Epilogue::UNIT;
+    constexpr int ROWS = 4;                     // weight rows in flight per warp iteration
+    constexpr int UPI = ROWS / UNIT;            // units per iteration
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    ActT* xs = reinterpret_cast<ActT*>(smem_raw);
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)K * sizeof(ActT));  // [kWarps][ROWS]
+
+    pro.stage(xs, K, red);
+    __syncthreads();
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    constexpr int RG = kWarps / KSPLIT;          // independent unit ranges per CTA
+    const int rg = warp / KSPLIT, ks = warp % KSPLIT;
+    const long long gw = (long long)blockIdx.x * RG + rg;
+    const long long W = (long long)gridDim.x * RG;
+    const int u_begin = (int)((gw * n_units) / W);
+    const int u_end = (int)(((gw + 1) * n_units) / W);
+    const int kblocks = K >> 5;
+    const int nchunks = (K + 511) >> 9;
+    const int kl = lane << 4;
+
+    for (int u0 = u_begin; u0 < u_end; u0 += UPI) {
+        float acc[ROWS];
+        const int8_t* wrow[ROWS];
+        const ScaleT* srow[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            acc[r] = 0.f;
+            const int u = min(u0 + r / UNIT, u_end - 1);     // duplicate the last unit; its result is dropped
+            const int row = u + (r % UNIT) * unit_stride;
+            wrow[r] = qs + (size_t)row * K;
+            srow[r] = scales + (size_t)row * kblocks;
+        }
+        for (int c0 = ks; c0 < nchunks; c0 += KSPLIT * UNROLL) {
+            uint4 w[UNROLL][ROWS];
+            float sc[UNROLL][ROWS];
+            bool live[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int k = ((c0 + u * KSPLIT) << 9) + kl;
+                live[u] = k < K;
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    if (live[u]) {
+                        w[u][r] = ld_stream_v4(wrow[r] + k);
+                        sc[u][r] = ld_scale<ScaleT>(srow[r] + (k >> 5));
+                    } else {
+                        w[u][r] = make_uint4(0x0, 0x0, 0x0, 0x0);
+                        sc[u][r] = 0.f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (!live[u]) continue;
+                const int k = ((c0 + u * KSPLIT) << 9) + kl;
+                Dot16<ActT, MODE> d16;
+                d16.load(xs, k);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(d16.dot(w[u][r]), sc[u][r], acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
+
+        if (KSPLIT > 1) {
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) red[warp * ROWS + r] = acc[r];
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(KSPLIT * 32) : "memory");
+            if (ks == 0 && lane < UPI) {
+                float s[UNIT];
+#pragma unroll
+                for (int j = 0; j < UNIT; ++j) {
+                    s[j] = 0.f;
+#pragma unroll
+                    for (int q = 0; q < KSPLIT; ++q) s[j] += red[(rg * KSPLIT + q) * ROWS + lane * UNIT + j];
+                }
+                if (u0 + lane < u_end) epi.store(u0 + lane, s);
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(KSPLIT * 32) : "memory");
+        } else if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < UPI; ++i)
+                if (u0 + i < u_end) epi.store(u0 + i, &acc[i * UNIT]);
+        }
+    }
+}
+
+struct Plan { int ksplit; int grid; };
+
+// Pick the K split and grid: enough warps in flight to cover HBM latency even when N is small.
+inline Plan plan(const rcu_device* dev, int n_units, int unit, int K, int ctas_per_sm = 3) {
+    Plan p;
+    const long long max_ctas = (long long)dev->sm_count * ctas_per_sm;
+    const int upi = 4 / unit;
+    const long long groups = (n_units + upi - 1) / upi;
+    const long long warps_wanted = max_ctas * kWarps;
+    int ksplit = 1;
+    while (ksplit < 8 && groups * ksplit * 2 <= warps_wanted && (K / (ksplit * 2)) >= 1024) ksplit *= 2;
+    p.ksplit = ksplit;
+    const long long ctas_needed = (groups * ksplit + kWarps - 1) / kWarps;
+    p.grid = (int)(ctas_needed < max_ctas ? (ctas_needed < 1 ? 1 : ctas_needed) : max_ctas);
+    return p;
+}
+
+template <class ScaleT, class ActT, int MODE, class Prologue, class Epilogue>
+rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const Prologue& pro, const Epilogue& epi, int N, int K) {
+    constexpr int UNROLL = 2;
+    constexpr int UNIT = Epilogue::UNIT;
+    const int n_units = N / UNIT;
+    const Plan p = plan(dev, n_units, UNIT, K);
+    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float);
+    if (smem > (size_t)dev->smem_optin) return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "gemv: K=%d does not fit the activation stage", K);
+#define RCU_GEMV_Q8_CASE(KS)                                                                                  \
+    case KS: {                                                                                                \
+        auto kern = gemv_q8_kernel<ScaleT, ActT, KS, UNROLL, MODE, Prologue, Epilogue>;                       \
+        if (smem > 48 * 1024) RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kern<<<p.grid, kThreads, smem, dev->stream>>>(qs, (const ScaleT*)scales, pro, epi, n_units, N / UNIT, K); \
+        break;                                                                                                \
+    }
+    switch (p.ksplit) {
+        RCU_GEMV_Q8_CASE(1)
+        RCU_GEMV_Q8_CASE(2)
+        RCU_GEMV_Q8_CASE(4)
+        RCU_GEMV_Q8_CASE(8)
+    }
+#undef RCU_GEMV_Q8_CASE
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
+}  // namespace gemvq8

@@ -51,23 +51,55 @@ def phi3_weights(seed, n_layers, d=3072, n_heads=32, ffn=8192, vocab=32064, quan
             "lm_head": _weight(g, (vocab, d), quant), "d": d, "n_heads": n_heads, "ffn": ffn, "vocab": vocab}
 
 
+def phi3_kv(W, kv_prior, act_np, max_cache=4096, kv_seed=5):
+    """Per layer (k_cache, v_cache) [1, H, max_cache, hd], zero except `kv_prior` N(0,1) positions."""
+    d, H = W["d"], W["n_heads"]
+    hd = d // H
+    g = rng(kv_seed)
+    out = []
+    for _ in W["layers"]:
+        kc = np.zeros((1, H, max_cache, hd), act_np)
+        vc = np.zeros((1, H, max_cache, hd), act_np)
+        kc[:, :, :kv_prior] = g.standard_normal((1, H, kv_prior, hd)).astype(act_np)
+        vc[:, :, :kv_prior] = g.standard_normal((1, H, kv_prior, hd)).astype(act_np)
+        out.append((kc, vc))
+    return out
+
+
+def phi3_decoder(dev, W, kv_prior, max_cache=4096, kv_seed=5):
+    """The fused decode engine over the same weights and caches as phi3_model (f16 activations)."""
+    from ratchet_b200 import capi
+    from ratchet_b200.decoder import Decoder, DecoderConfig, DecoderLayer
+    d, H = W["d"], W["n_heads"]
+    hd = d // H
+    kv = phi3_kv(W, kv_prior, np.float16, max_cache, kv_seed)
+    wdt = W["embd"][1]
+    q = lambda rd, shape: dev.from_quantized(rd[0], rd[1], shape)
+    layers = []
+    for li, lw in enumerate(W["layers"]):
+        layers.append(DecoderLayer(dev.from_numpy(lw["attn_norm"]), q(lw["qkv"], (3 * d, d)), q(lw["o"], (d, d)), dev.from_numpy(lw["ffn_norm"]),
+                                   q(lw["up"], (2 * W["ffn"], d)), q(lw["down"], (d, W["ffn"])),
+                                   dev.from_numpy(kv[li][0][0]), dev.from_numpy(kv[li][1][0])))
+    cfg = DecoderConfig(len(layers), d, H, H, hd, W["ffn"], W["vocab"], max_cache, hd, 10000.0, 1e-5, wdt)
+    dec = Decoder(dev, cfg, layers, q(W["embd"], (W["vocab"], d)), dev.from_numpy(W["ln_post"]), q(W["lm_head"], (W["vocab"], d)))
+    dec.position = kv_prior
+    return dec
+
+
 def phi3_model(T, dev, W, kv_prior, act_np, max_cache=4096, kv_seed=5):
     """Builds callers.Phi3 with a KV cache holding `kv_prior` N(0,1) positions (phi3/model.rs:160-202)."""
     d, H = W["d"], W["n_heads"]
     hd = d // H
-    g = rng(kv_seed)
+    kv = phi3_kv(W, kv_prior, act_np, max_cache, kv_seed)
     scale = T.from_data(np.array([1.0 / np.sqrt(np.float32(hd))], np.float32), device=dev)
     layers, entries = [], []
-    for lw in W["layers"]:
+    for li, lw in enumerate(W["layers"]):
         attn = callers.Phi3SelfAttention(nn.Linear(_wrap(T, dev, *lw["qkv"], (3 * d, d))), nn.Linear(_wrap(T, dev, *lw["o"], (d, d))),
                                          nn.RotaryEmbedding(hd, False, 10000.0, 1.0), H, H, scale)
         mlp = callers.Phi3MLP(nn.Linear(_wrap(T, dev, *lw["up"], (2 * W["ffn"], d))), nn.Linear(_wrap(T, dev, *lw["down"], (d, W["ffn"]))))
         layers.append(callers.Phi3DecoderLayer(nn.RMSNorm(T.from_data(lw["attn_norm"], device=dev), 1e-5), attn,
                                                nn.RMSNorm(T.from_data(lw["ffn_norm"], device=dev), 1e-5), mlp))
-        kc = np.zeros((1, H, max_cache, hd), act_np)
-        vc = np.zeros((1, H, max_cache, hd), act_np)
-        kc[:, :, :kv_prior] = g.standard_normal((1, H, kv_prior, hd)).astype(act_np)
-        vc[:, :, :kv_prior] = g.standard_normal((1, H, kv_prior, hd)).astype(act_np)
+        kc, vc = kv[li]
         entries.append(nn.KVEntry(T.from_data(kc, device=dev), T.from_data(vc, device=dev), kv_prior))
     model = callers.Phi3(nn.Embedding(_wrap(T, dev, *W["embd"], (W["vocab"], d))), layers,
                          nn.RMSNorm(T.from_data(W["ln_post"], device=dev), 1e-5),
