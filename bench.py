@@ -207,6 +207,25 @@ def _time_loop(torch, stream, fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
+def _time_graph(torch, stream, fn, iters, replays=5):
+    """Average device time of one call of `fn`, with `iters` calls captured into one CUDA graph so
+    that host launch overhead (several microseconds per call through Python) is out of the picture."""
+    g = torch.cuda.CUDAGraph()
+    stream.synchronize()
+    with torch.cuda.graph(g, stream=stream):
+        for i in range(iters):
+            fn(i)
+    g.replay()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(replays):
+        g.replay()
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / (replays * iters)
+
+
 def gemv_sweep(dev, torch, stream):
     """The smaller (K,N) pairs of the GEMV sweep.  They fit in L2 (126 MB), so each is timed twice:
     'cold' rotates through enough distinct weight copies to exceed 2x L2 between reuses, 'warm'
@@ -223,8 +242,8 @@ def gemv_sweep(dev, torch, stream):
         run = lambda i: dev.matmul(bufs[i % copies], x, None, False, True, True, out=y)
         for i in range(copies):
             run(i)
-        cold_ms = _time_loop(torch, stream, run, copies * 10)
-        warm_ms = _time_loop(torch, stream, lambda i: run(0), 200)
+        cold_ms = _time_graph(torch, stream, run, copies * 8)
+        warm_ms = _time_graph(torch, stream, lambda i: run(0), 100)
         b = gemv_bytes(N, K)
         out.append({"K": K, "N": N, "bytes": b, "cold_us": cold_ms * 1e3, "cold_gbs": b / cold_ms / 1e6, "cold_frac_of_measured": b / cold_ms / 1e6 / peak,
                     "warm_us": warm_ms * 1e3, "warm_gbs": b / warm_ms / 1e6, "weight_copies_rotated": copies})
@@ -340,7 +359,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    stream = torch.cuda.current_stream()
+    # a stream of our own: CUDA-graph capture (used by the decode engine) is not allowed on the legacy default stream
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     dev = Device(local_rank, stream=stream.cuda_stream)
 
     K, N = K_HEAD, (args.rows or N_HEAD)

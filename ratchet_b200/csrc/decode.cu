@@ -17,7 +17,7 @@
 #include <cmath>
 #include <cstdlib>
 
-#include "gemv_q8.cuh"
+#include "gemv_q8_bulk.cuh"
 
 namespace {
 
@@ -59,8 +59,9 @@ __device__ __forceinline__ void rope_into(const __half* in, const float* tab, in
         if (i < half) {
             const float x1 = __half2float(in[i]), x2 = __half2float(in[i + half]);
             const float c = tab[i], s = tab[half + i];
-            dst[i] = f16r(x1 * c - x2 * s);            // f32 rope, then `.cast(f16)` (attn.rs:118-130)
-            dst[i + half] = f16r(x1 * s + x2 * c);
+            // f32 rope with each product rounded (no fma contraction), then `.cast(f16)` (attn.rs:118-130)
+            dst[i] = f16r(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)));
+            dst[i + half] = f16r(__fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c)));
         } else if (i >= rope_dim) {
             dst[i] = __half2float(in[i]);
         }
@@ -75,6 +76,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     __shared__ float o_s[4][HD];
     __shared__ unsigned int ticket;
 
+    // everything this kernel reads was produced by kernels before it in the stream; the kernel after
+    // it may begin launching (it only prefetches weights until this one has finished)
+    gemvq8::pdl_launch_dependents();
+    gemvq8::pdl_wait();
     const int tid = threadIdx.x;
     const int h = blockIdx.y, s = blockIdx.x;
     const int group = p.H / p.Hkv;
@@ -216,14 +221,38 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     if (tid == 0) p.counters[h] = 0;                 // ready for the next launch
 }
 
-rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim) {
+__global__ void set_u32_kernel(uint32_t* p, uint32_t v);
+__global__ void argmax_advance_kernel(const __half* logits, int n, int32_t* out, uint32_t* d_pos);
+
+rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool overlap = false) {
     const int chunk_max = (p.max_cache + kSplits - 1) / kSplits;
     const size_t smem = (size_t)chunk_max * sizeof(float);
-    dim3 grid(kSplits, p.H);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kSplits, p.H);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    // Same shared-memory carve-out as the GEMVs around it: an SM that has to change its L1/shared split
+    // between consecutive kernels drains first, which costs microseconds per kernel in a decode step.
+    static bool carveout_set = false;
+    if (!carveout_set) {
+        cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(attn_decode_kernel<96>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(rope_table_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(set_u32_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carveout_set = true;
+    }
     switch (head_dim) {
-        case 64: attn_decode_kernel<64><<<grid, kAttnThreads, smem, dev->stream>>>(p); break;
-        case 96: attn_decode_kernel<96><<<grid, kAttnThreads, smem, dev->stream>>>(p); break;
-        case 128: attn_decode_kernel<128><<<grid, kAttnThreads, smem, dev->stream>>>(p); break;
+        case 64: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, p)); break;
+        case 96: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<96>, p)); break;
+        case 128: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, p)); break;
         default: return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "attn_decode: head_dim %d (supported: 64, 96, 128)", head_dim);
     }
     RCU_LAUNCH_CHECK(dev);
@@ -275,17 +304,31 @@ int q8_mode() {
     return mode;
 }
 
+// Programmatic dependent launch between the kernels of a step (RCU_NO_PDL=1 turns it off).
+bool pdl_enabled() {
+    static bool on = std::getenv("RCU_NO_PDL") == nullptr;
+    return on;
+}
+
 template <class Pro, class Epi>
 rcu_status gemv(rcu_device* dev, int weight_dt, const void* w, const Pro& pro, const Epi& epi, int N, int K) {
     const int8_t* qs = (const int8_t*)w;
     const void* sc = (const char*)w + align256((uint64_t)N * K);
     const int mode = q8_mode();
-    if (weight_dt == RCU_Q8_0H) {
-        if (mode == 1) return gemvq8::launch<__half, __half, 1>(dev, qs, sc, pro, epi, N, K);
-        return gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, N, K);
+    const bool ov = pdl_enabled();
+    static const int ctas = [] { const char* e = std::getenv("RCU_DECODE_CTAS"); const int n = e ? std::atoi(e) : 3; return n < 1 ? 1 : (n > 3 ? 3 : n); }();
+    // shared-memory ring fed by TMA tile copies: opt-in with RCU_GEMV_BULK=1 (the register kernel measures faster on cold weights)
+    static const bool bulk = std::getenv("RCU_GEMV_BULK") != nullptr;
+    if (bulk && gemvq8::bulk_eligible(qs, K, (size_t)dev->smem_optin, weight_dt == RCU_Q8_0H ? 2 : 4)) {
+        if (weight_dt == RCU_Q8_0H) return gemvq8::launch_bulk<__half>(dev, qs, sc, pro, epi, N, K, ov);
+        return gemvq8::launch_bulk<float>(dev, qs, sc, pro, epi, N, K, ov);
     }
-    if (mode == 1) return gemvq8::launch<float, __half, 1>(dev, qs, sc, pro, epi, N, K);
-    return gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, N, K);
+    if (weight_dt == RCU_Q8_0H) {
+        if (mode == 1) return gemvq8::launch<__half, __half, 1>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
+        return gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
+    }
+    if (mode == 1) return gemvq8::launch<float, __half, 1>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
+    return gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
 }
 
 // per-device scratch for the standalone attention entry point
@@ -367,7 +410,7 @@ rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_d
         if (st != RCU_OK) return st;
         AttnParams ap{d->qkv, (__half*)L.k_cache, (__half*)L.v_cache, H, Hkv, (int)c.max_cache, (int)c.rope_dim,
                       d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters, d->attn};
-        st = launch_attn(dev, ap, HD);
+        st = launch_attn(dev, ap, HD, pdl_enabled());
         if (st != RCU_OK) return st;
         st = gemv(dev, c.weight_dt, L.o, gemvq8::PlainPrologue<__half>{d->attn}, gemvq8::ResidualEpilogueH{d->x, d->x}, D, H * HD);
         if (st != RCU_OK) return st;
@@ -454,7 +497,8 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
     rcu_device* dev = d->dev;
     RCU_REQUIRE(dev, d->position < d->cfg.max_cache, "decoder: the KV cache is full (%u entries)", d->cfg.max_cache);
     DevGuard g(dev->ordinal);
-    const bool use_graph = std::getenv("RCU_NO_GRAPH") == nullptr;
+    // stream capture is not available on the legacy default stream: run the sequence eagerly there
+    const bool use_graph = std::getenv("RCU_NO_GRAPH") == nullptr && dev->stream != nullptr;
     rcu_status st = RCU_OK;
     if (!use_graph || d->steps == 0) {
         // first step runs eagerly: sets kernel attributes and counts the launches

@@ -7,7 +7,7 @@
 // transposed.
 #include <cstdlib>
 
-#include "gemv_q8.cuh"
+#include "gemv_q8_bulk.cuh"
 
 namespace {
 
@@ -130,12 +130,29 @@ int q8_mode() {
     return mode;
 }
 
+int q8_ctas_per_sm() {
+    static int v = [] {
+        const char* e = std::getenv("RCU_GEMV_CTAS");
+        const int n = e ? std::atoi(e) : 3;
+        return n < 1 ? 1 : (n > 3 ? 3 : n);
+    }();
+    return v;
+}
+
 template <class ScaleT, class ActT>
 rcu_status launch_q8(rcu_device* dev, const int8_t* qs, const void* scales, const void* x, const void* bias, void* y, int N, int K) {
     gemvq8::PlainPrologue<ActT> pro{(const ActT*)x};
     gemvq8::PlainEpilogue<ActT> epi{(const ActT*)bias, (ActT*)y};
-    if (q8_mode() == 1) return gemvq8::launch<ScaleT, ActT, 1>(dev, qs, scales, pro, epi, N, K);
-    return gemvq8::launch<ScaleT, ActT, 0>(dev, qs, scales, pro, epi, N, K);
+    if constexpr (sizeof(ActT) == 2) {
+        static const bool bulk = std::getenv("RCU_GEMV_BULK") != nullptr;   // TMA-ring variant: opt-in (the register kernel measures faster on cold weights)
+        if (bulk && gemvq8::bulk_eligible(qs, K, (size_t)dev->smem_optin, sizeof(ScaleT)))
+            return gemvq8::launch_bulk<ScaleT>(dev, qs, scales, pro, epi, N, K, false);
+    }
+    const int ctas = q8_ctas_per_sm();
+    // short streams (tens of MB) gain from the pre-loaded, double-buffered variant; long ones from occupancy
+    const bool pipe = (size_t)N * K < (size_t)128 << 20;
+    if (q8_mode() == 1) return gemvq8::launch<ScaleT, ActT, 1>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
+    return gemvq8::launch<ScaleT, ActT, 0>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
 }
 
 template <class T>

@@ -63,8 +63,9 @@ __device__ __forceinline__ void i8x4_to_f32x4(uint32_t w, float q[4]) {
 }
 
 // Dot of 16 int8 (one uint4) with 16 activations held in registers.
-// MODE 0: f16 activations stay packed, mixed-precision fma.  MODE 1: activations widened to f32
-// once per chunk (shared by all ROWS rows), int8 -> f32 through the mantissa trick, FFMA.
+// MODE 0: f16 activations stay packed, mixed-precision fma (measured faster on B200).  MODE 1:
+// activations widened to f32 once per chunk (shared by all ROWS rows), int8 -> f32 through the
+// mantissa trick, FFMA; the only mode for f32 activations.
 template <class ActT, int MODE> struct Dot16;
 
 template <> struct Dot16<__half, 0> {
@@ -132,7 +133,6 @@ template <class ActT> struct Dot16<ActT, 1> {
     }
 };
 template <> struct Dot16<float, 0> : Dot16<float, 1> {};
-
 template <class ScaleT> __device__ __forceinline__ float ld_scale(const ScaleT* p);
 template <> __device__ __forceinline__ float ld_scale<float>(const float* p) { return __ldg(p); }
 template <> __device__ __forceinline__ float ld_scale<__half>(const __half* p) {
@@ -149,7 +149,7 @@ template <class ActT> struct PlainPrologue {
         const int vec = 16 / (int)sizeof(ActT);
         const uint4* src = reinterpret_cast<const uint4*>(x);
         uint4* dst = reinterpret_cast<uint4*>(xs);
-        for (int i = threadIdx.x; i < K / vec; i += kThreads) dst[i] = __ldg(src + i);
+        for (int i = threadIdx.x; i < K / vec; i += kThreads) dst[i] = __ldcg(src + i);   // produced by the previous kernel: read at L2
     }
 };
 
@@ -160,19 +160,23 @@ struct RmsNormPrologueH {
     const float* gamma;
     float eps;
     __device__ __forceinline__ void stage(__half* xs, int K, float* scratch) const {
+        // one trip to L2: raw values are parked in shared memory while the sum of squares is reduced
         float s2 = 0.f;
         for (int i = threadIdx.x; i < K; i += kThreads) {
-            const float v = __half2float(x[i]);
+            const __half h = __ldcg(x + i);
+            xs[i] = h;
+            const float v = __half2float(h);
             s2 = fmaf(v, v, s2);
         }
         s2 = warp_sum(s2);
         if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = s2;
-        __syncthreads();
+        // the kThreads staging threads only (a kernel may run extra warps that do not stage)
+        asm volatile("bar.sync 15, %0;" ::"n"(kThreads) : "memory");
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) tot += scratch[w];
         const float rstd = 1.0f / sqrtf(tot / (float)K + eps);
-        for (int i = threadIdx.x; i < K; i += kThreads) xs[i] = __float2half_rn(__half2float(x[i]) * rstd * gamma[i]);
+        for (int i = threadIdx.x; i < K; i += kThreads) xs[i] = __float2half_rn(__half2float(xs[i]) * rstd * __ldg(gamma + i));
     }
 };
 
@@ -199,7 +203,7 @@ struct ResidualEpilogueH {
     __half* y;
     __device__ __forceinline__ void store(int u, const float* acc) const {
         const float lin = __half2float(__float2half_rn(acc[0]));
-        y[u] = __float2half_rn(lin + __half2float(residual[u]));
+        y[u] = __float2half_rn(lin + __half2float(__ldcg(residual + u)));
     }
 };
 
@@ -216,6 +220,9 @@ struct SiluGateEpilogueH {
     }
 };
 
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <class ScaleT, class ActT, int KSPLIT, int UNROLL, int MODE, class Prologue, class Epilogue>
 __global__ void __launch_bounds__(kThreads)
 gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales, Prologue pro, Epilogue epi, int n_units,
@@ -227,6 +234,9 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
     ActT* xs = reinterpret_cast<ActT*>(smem_raw);
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)K * sizeof(ActT));  // [kWarps][ROWS]
 
+    // nothing before this point touches data written by the previous kernel in the stream
+    pdl_launch_dependents();
+    pdl_wait();
     pro.stage(xs, K, red);
     __syncthreads();
 
@@ -311,6 +321,133 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
     }
 }
 
+// Variant for short kernels (the GEMVs of a decode step): two register slots of loads are put in
+// flight BEFORE the kernel waits for its predecessor and stages x, and refilled as they are consumed.
+// It needs 128 registers (two CTAs per SM); on long, cold streams the plain kernel above, with three
+// CTAs per SM, measures faster, on 10-60 MB weights this one does.
+
+// One pipeline slot: the weight vectors and block scales of UNROLL chunks x ROWS rows, in registers.
+template <int UNROLL, int ROWS> struct Slot {
+    uint4 w[UNROLL][ROWS];
+    float sc[UNROLL][ROWS];
+};
+
+template <class ScaleT, class ActT, int KSPLIT, int UNROLL, int MODE, class Prologue, class Epilogue>
+__global__ void __launch_bounds__(kThreads)
+gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales, Prologue pro, Epilogue epi, int n_units,
+               int unit_stride, int K) {
+    constexpr int UNIT = Epilogue::UNIT;
+    constexpr int ROWS = 4;                     // weight rows in flight per warp iteration
+    constexpr int UPI = ROWS / UNIT;            // units per iteration
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    ActT* xs = reinterpret_cast<ActT*>(smem_raw);
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)K * sizeof(ActT));  // [kWarps][ROWS]
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    constexpr int RG = kWarps / KSPLIT;          // independent unit ranges per CTA
+    const int rg = warp / KSPLIT, ks = warp % KSPLIT;
+    const long long gw = (long long)blockIdx.x * RG + rg;
+    const long long W = (long long)gridDim.x * RG;
+    const int u_begin = (int)((gw * n_units) / W);
+    const int u_end = (int)(((gw + 1) * n_units) / W);
+    const int kblocks = K >> 5;
+    const int nchunks = (K + 511) >> 9;
+    const int kl = lane << 4;
+    // work items of this warp: (unit group, chunk group), chunk groups innermost
+    const int n_groups = (u_end - u_begin + UPI - 1) / UPI;
+    const int ncg = (nchunks - ks + KSPLIT * UNROLL - 1) / (KSPLIT * UNROLL);
+    const int n_items = n_groups * ncg;
+
+    auto load_item = [&](int it, Slot<UNROLL, ROWS>& s) {
+        const int u0 = u_begin + (it / ncg) * UPI;
+        const int c0 = ks + (it % ncg) * (KSPLIT * UNROLL);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = ((c0 + u * KSPLIT) << 9) + kl;
+            const bool live = k < K;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                const int un = min(u0 + r / UNIT, u_end - 1);     // duplicate the last unit; its result is dropped
+                const size_t row = (size_t)(un + (r % UNIT) * unit_stride);
+                if (live) {
+                    s.w[u][r] = ld_stream_v4(qs + row * K + k);
+                    s.sc[u][r] = ld_scale<ScaleT>(scales + row * kblocks + (k >> 5));
+                } else {
+                    s.w[u][r] = make_uint4(0x0, 0x0, 0x0, 0x0);
+                    s.sc[u][r] = 0.f;
+                }
+            }
+        }
+    };
+
+    float acc[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+
+    auto compute_item = [&](int it, const Slot<UNROLL, ROWS>& s) {
+        const int c0 = ks + (it % ncg) * (KSPLIT * UNROLL);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = ((c0 + u * KSPLIT) << 9) + kl;
+            if (k < K) {
+                Dot16<ActT, MODE> d16;
+                d16.load(xs, k);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(d16.dot(s.w[u][r]), s.sc[u][r], acc[r]);
+            }
+        }
+        if (it % ncg != ncg - 1) return;
+        // last chunk group of this unit group: reduce and store
+        const int u0 = u_begin + (it / ncg) * UPI;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
+        if (KSPLIT > 1) {
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) red[warp * ROWS + r] = acc[r];
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(KSPLIT * 32) : "memory");
+            if (ks == 0 && lane < UPI) {
+                float sum[UNIT];
+#pragma unroll
+                for (int j = 0; j < UNIT; ++j) {
+                    sum[j] = 0.f;
+#pragma unroll
+                    for (int q = 0; q < KSPLIT; ++q) sum[j] += red[(rg * KSPLIT + q) * ROWS + lane * UNIT + j];
+                }
+                if (u0 + lane < u_end) epi.store(u0 + lane, sum);
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(KSPLIT * 32) : "memory");
+        } else if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < UPI; ++i)
+                if (u0 + i < u_end) epi.store(u0 + i, &acc[i * UNIT]);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+    };
+
+    // The weights do not depend on the kernel before this one: put the first loads in flight, let
+    // the next kernel start launching, and only then wait for the producer of x and stage x.
+    Slot<UNROLL, ROWS> s0, s1;
+    pdl_launch_dependents();
+    if (n_items > 0) load_item(0, s0);
+    if (n_items > 1) load_item(1, s1);
+    pdl_wait();
+    pro.stage(xs, K, red);
+    __syncthreads();
+
+    for (int it = 0; it < n_items; it += 2) {
+        compute_item(it, s0);
+        if (it + 2 < n_items) load_item(it + 2, s0);
+        if (it + 1 < n_items) {
+            compute_item(it + 1, s1);
+            if (it + 3 < n_items) load_item(it + 3, s1);
+        }
+    }
+}
+
 struct Plan { int ksplit; int grid; };
 
 // Pick the K split and grid: enough warps in flight to cover HBM latency even when N is small.
@@ -329,18 +466,29 @@ inline Plan plan(const rcu_device* dev, int n_units, int unit, int K, int ctas_p
 }
 
 template <class ScaleT, class ActT, int MODE, class Prologue, class Epilogue>
-rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const Prologue& pro, const Epilogue& epi, int N, int K) {
+// overlap = launch with programmatic stream serialization: the kernel may start while its predecessor
+// in the stream is still draining; it touches nothing but weights until griddepcontrol.wait returns.
+rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const Prologue& pro, const Epilogue& epi, int N, int K,
+                  bool overlap = false, int ctas_per_sm = 3, bool pipelined = false) {
     constexpr int UNROLL = 2;
+    if (pipelined && ctas_per_sm > 2) ctas_per_sm = 2;
     constexpr int UNIT = Epilogue::UNIT;
     const int n_units = N / UNIT;
-    const Plan p = plan(dev, n_units, UNIT, K);
+    const Plan p = plan(dev, n_units, UNIT, K, ctas_per_sm);
     const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float);
     if (smem > (size_t)dev->smem_optin) return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "gemv: K=%d does not fit the activation stage", K);
 #define RCU_GEMV_Q8_CASE(KS)                                                                                  \
     case KS: {                                                                                                \
-        auto kern = gemv_q8_kernel<ScaleT, ActT, KS, UNROLL, MODE, Prologue, Epilogue>;                       \
+        auto kern = pipelined ? gemv_q8_pipe_kernel<ScaleT, ActT, KS, UNROLL, MODE, Prologue, Epilogue>       \
+                              : gemv_q8_kernel<ScaleT, ActT, KS, UNROLL, MODE, Prologue, Epilogue>;            \
         if (smem > 48 * 1024) RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kern<<<p.grid, kThreads, smem, dev->stream>>>(qs, (const ScaleT*)scales, pro, epi, n_units, N / UNIT, K); \
+        cudaLaunchConfig_t cfg = {};                                                                          \
+        cfg.gridDim = dim3(p.grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = dev->stream; \
+        cudaLaunchAttribute attr[1];                                                                          \
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                      \
+        attr[0].val.programmaticStreamSerializationAllowed = 1;                                               \
+        cfg.attrs = attr; cfg.numAttrs = overlap ? 1 : 0;                                                     \
+        RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, qs, (const ScaleT*)scales, pro, epi, n_units, N / UNIT, K)); \
         break;                                                                                                \
     }
     switch (p.ksplit) {

@@ -30,8 +30,9 @@ rope_kernel(const T* __restrict__ x, T* __restrict__ out, int BH, int S, int D, 
         for (int bh = blockIdx.y; bh < BH; bh += gridDim.y) {
             const size_t o = ((size_t)bh * S + s) * D;
             const float x1 = to_f32<T>(x[o + i]), x2 = to_f32<T>(x[o + half + i]);
-            out[o + i] = from_f32<T>(rnd<T>(x1 * cs) - rnd<T>(x2 * sn));
-            out[o + half + i] = from_f32<T>(rnd<T>(x1 * sn) + rnd<T>(x2 * cs));
+            // each product is rounded on its own, as on the CPU (no fma contraction)
+            out[o + i] = from_f32<T>(__fsub_rn(rnd<T>(__fmul_rn(x1, cs)), rnd<T>(__fmul_rn(x2, sn))));
+            out[o + half + i] = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(x1, sn)), rnd<T>(__fmul_rn(x2, cs))));
         }
     }
     // pass-through tail (only needed when out != x)
