@@ -267,6 +267,25 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
                            uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_cache, uint32_t rope_dim, float rope_base,
                            uint32_t position, void* out);
 
+/* ------------------------------------------------------------------ row-sharded Linear over the GPUs of a node
+ * No counterpart in the reference, which is single-device (gpu/device.rs:15-16).  A Linear's weight
+ * W[N,K] (ratchet-nn/src/linear.rs:17-24) is split by rows: rank r of g holds rows [r N/g, (r+1) N/g)
+ * as its own ratchet Q8_0 buffer.  One process per GPU; each creates a window (two full-size f16
+ * output slots + flags), exports it as a 64-byte CUDA IPC handle, the host framework exchanges the
+ * handles, and every rank imports its peers'.  rcu_gemv_q8_allgather runs the local GEMV; its last
+ * CTA stores the output slice into every peer's window over NVLink and raises their flags, then this
+ * rank waits (bounded: RCU_ERR_TIMEOUT at the next sync) for its peers' slices.  *y_full is the
+ * device pointer of the gathered f16 [N] output, valid until the call after next. */
+typedef struct rcu_comm rcu_comm;
+rcu_status rcu_comm_create(rcu_device* dev, int rank, int world, uint64_t slot_bytes, rcu_comm** out);
+rcu_status rcu_comm_export(rcu_comm* comm, void* handle64);
+rcu_status rcu_comm_import(rcu_comm* comm, int peer, const void* handle64);
+void rcu_comm_destroy(rcu_comm* comm);
+int rcu_comm_rank(const rcu_comm* comm);
+int rcu_comm_world(const rcu_comm* comm);
+rcu_status rcu_gemv_q8_allgather(rcu_comm* comm, const rcu_tensor* w_shard, const rcu_tensor* x, const rcu_tensor* bias_shard,
+                                 void** y_full);
+
 #ifdef __cplusplus
 }
 #endif

@@ -140,6 +140,13 @@ SIGNATURES = {
     "rcu_decoder_position": (C.c_uint32, [C.c_void_p]),
     "rcu_decoder_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rcu_decoder_kernels_per_step": (C.c_uint32, [C.c_void_p]),
+    "rcu_comm_create": (C.c_int, [_DEV, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "rcu_comm_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "rcu_comm_import": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "rcu_comm_destroy": (None, [C.c_void_p]),
+    "rcu_comm_rank": (C.c_int, [C.c_void_p]),
+    "rcu_comm_world": (C.c_int, [C.c_void_p]),
+    "rcu_gemv_q8_allgather": (C.c_int, [C.c_void_p, _T, _T, _T, C.POINTER(C.c_void_p)]),
     "rcu_attn_decode": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   C.c_uint32, C.c_float, C.c_uint32, C.c_void_p]),
 }

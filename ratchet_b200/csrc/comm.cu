@@ -1,0 +1,166 @@
+// Row-sharded Linear across the GPUs of one node: peer-mapped output buffers and a GEMV whose last
+// CTA pushes its output slice to every peer (gemvq8::PushEpilogueH), so the all-gather that follows
+// a column-parallel Linear costs no extra collective launch.
+//
+// The reference has no multi-device path (gpu/device.rs:15-16 pins the ordinal to 0); this is the
+// sharding its Linear (ratchet-nn/src/linear.rs:17-24) admits: the rows of W[N,K] are independent,
+// Q8_0 blocks run along K inside a row, so rank r owns rows [r N/g, (r+1) N/g) as its own ratchet
+// buffer and the only exchange is the gather of the output slices.
+//
+// One process per GPU.  Each rank allocates one "window": two full-size output slots (double
+// buffered by step parity) followed by two flag arrays of `world` words and a ticket.  Windows are
+// exported as CUDA IPC handles, exchanged by the host framework, and opened by every peer.  Data
+// moves with plain peer stores issued by the producing GPU into the consumer's own HBM (all later
+// reads are local); completion is a system-scope release store of the step number into the
+// consumer's flag word, which the consumer acquires with a bounded spin.  No TMA, no multicast.
+#include "gemv_q8.cuh"
+
+namespace {
+constexpr int kSlots = 2;
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;   // 2 s per wait, then RCU_DEVFLAG_TIMEOUT
+
+struct Window {
+    char* base = nullptr;
+    size_t slot_bytes = 0;
+    char* slot(int s) const { return base + (size_t)s * slot_bytes; }
+    unsigned int* flags(int s, int world) const { return reinterpret_cast<unsigned int*>(base + kSlots * slot_bytes) + (size_t)s * world; }
+    unsigned int* ticket(int world) const { return flags(kSlots, world); }
+    static size_t bytes(size_t slot_bytes, int world) { return kSlots * slot_bytes + (size_t)(kSlots * world + 4) * sizeof(unsigned int); }
+};
+
+// lane p waits until peer p's flag for this slot reaches seq
+__global__ void wait_flags_kernel(const unsigned int* flags, int world, int self, unsigned int seq, int* status) {
+    const int p = threadIdx.x;
+    if (p >= world || p == self) return;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+        if ((int)(v - seq) >= 0) return;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > kWaitBudgetNs) {
+            atomicOr(status, RCU_DEVFLAG_TIMEOUT);
+            return;
+        }
+        __nanosleep(100);
+    }
+}
+}  // namespace
+
+struct rcu_comm {
+    rcu_device* dev = nullptr;
+    int rank = 0, world = 1;
+    Window local;
+    Window peers[gemvq8::kMaxPeers];   // peers[rank] == local
+    bool opened[gemvq8::kMaxPeers] = {};
+    unsigned int seq = 0;
+};
+
+extern "C" {
+
+rcu_status rcu_comm_create(rcu_device* dev, int rank, int world, uint64_t slot_bytes, rcu_comm** out) {
+    if (!dev || !out) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(dev, world >= 1 && world <= gemvq8::kMaxPeers && rank >= 0 && rank < world, "comm: rank %d of %d", rank, world);
+    RCU_REQUIRE(dev, slot_bytes % 16 == 0 && slot_bytes > 0, "comm: slot size must be a positive multiple of 16 bytes");
+    DevGuard g(dev->ordinal);
+    rcu_comm* c = new rcu_comm();
+    c->dev = dev;
+    c->rank = rank;
+    c->world = world;
+    c->local.slot_bytes = slot_bytes;
+    const size_t total = Window::bytes(slot_bytes, world);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, total);   // a dedicated allocation: IPC handles export whole allocations
+    if (e != cudaSuccess) { delete c; return rcu_fail(dev, RCU_ERR_OOM, "comm: cudaMalloc(%zu): %s", total, cudaGetErrorString(e)); }
+    c->local.base = (char*)p;
+    cudaMemsetAsync(p, 0, total, dev->stream);
+    cudaStreamSynchronize(dev->stream);
+    c->peers[rank] = c->local;
+    c->opened[rank] = false;
+    *out = c;
+    return RCU_OK;
+}
+
+rcu_status rcu_comm_export(rcu_comm* c, void* handle64) {
+    if (!c || !handle64) return RCU_ERR_INVALID_ARG;
+    DevGuard g(c->dev->ordinal);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    RCU_CUDA(c->dev, cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle64, c->local.base));
+    return RCU_OK;
+}
+
+rcu_status rcu_comm_import(rcu_comm* c, int peer, const void* handle64) {
+    if (!c || !handle64) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(c->dev, peer >= 0 && peer < c->world && peer != c->rank, "comm: bad peer %d", peer);
+    DevGuard g(c->dev->ordinal);
+    void* p = nullptr;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    RCU_CUDA(c->dev, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    c->peers[peer].base = (char*)p;
+    c->peers[peer].slot_bytes = c->local.slot_bytes;
+    c->opened[peer] = true;
+    return RCU_OK;
+}
+
+void rcu_comm_destroy(rcu_comm* c) {
+    if (!c) return;
+    DevGuard g(c->dev->ordinal);
+    cudaStreamSynchronize(c->dev->stream);
+    for (int p = 0; p < c->world; ++p)
+        if (c->opened[p]) cudaIpcCloseMemHandle(c->peers[p].base);
+    cudaFree(c->local.base);
+    delete c;
+}
+
+int rcu_comm_rank(const rcu_comm* c) { return c ? c->rank : -1; }
+int rcu_comm_world(const rcu_comm* c) { return c ? c->world : 0; }
+
+rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const rcu_tensor* x, const rcu_tensor* bias_shard,
+                                 void** y_full) {
+    if (!c || !y_full) return RCU_ERR_INVALID_ARG;
+    rcu_device* dev = c->dev;
+    RCU_REQUIRE(dev, t_valid(w_shard) && t_valid(x), "gemv_allgather: invalid tensor descriptor");
+    RCU_REQUIRE(dev, w_shard->rank == 2 && dt_is_q8(w_shard->dt) && x->dt == RCU_F16, "gemv_allgather: needs a Q8_0 [N/g, K] shard and f16 activations");
+    const uint64_t n_local = w_shard->shape[0], K = w_shard->shape[1];
+    RCU_REQUIRE(dev, t_numel(x) == K && K % 32 == 0, "gemv_allgather: x must hold K = %llu elements", (unsigned long long)K);
+    RCU_REQUIRE(dev, n_local % 8 == 0, "gemv_allgather: shard rows must be a multiple of 8");
+    RCU_REQUIRE(dev, n_local * c->world * 2 <= c->local.slot_bytes, "gemv_allgather: output (%llu B) exceeds the window slot", (unsigned long long)(n_local * c->world * 2));
+    RCU_REQUIRE(dev, !bias_shard || (bias_shard->dt == RCU_F16 && t_numel(bias_shard) == n_local), "gemv_allgather: bias shard mismatch");
+    for (int p = 0; p < c->world; ++p)
+        RCU_REQUIRE(dev, p == c->rank || c->opened[p], "gemv_allgather: peer %d has not been imported", p);
+    DevGuard g(dev->ordinal);
+    const unsigned int seq = ++c->seq;
+    const int slot = (int)(seq & 1u);
+    gemvq8::PushEpilogueH epi;
+    epi.bias = bias_shard ? (const __half*)bias_shard->data : nullptr;
+    epi.y_local = reinterpret_cast<__half*>(c->local.slot(slot)) + (size_t)c->rank * n_local;
+    epi.slice_elems = (int)n_local;
+    epi.ticket = c->local.ticket(c->world);
+    epi.n_peers = 0;
+    for (int p = 0; p < c->world; ++p) {
+        if (p == c->rank) continue;
+        epi.peer_dst[epi.n_peers] = reinterpret_cast<__half*>(c->peers[p].slot(slot)) + (size_t)c->rank * n_local;
+        epi.peer_flag[epi.n_peers] = c->peers[p].flags(slot, c->world) + c->rank;
+        epi.n_peers++;
+    }
+    epi.seq = seq;
+    const int8_t* qs = (const int8_t*)w_shard->data;
+    const void* sc = (const char*)w_shard->data + align256(n_local * K);
+    gemvq8::PlainPrologue<__half> pro{(const __half*)x->data};
+    const bool pipe = n_local * K < ((uint64_t)128 << 20);
+    rcu_status st = w_shard->dt == RCU_Q8_0H
+                        ? gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, false, 3, pipe)
+                        : gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, false, 3, pipe);
+    if (st != RCU_OK) return st;
+    if (c->world > 1) {
+        wait_flags_kernel<<<1, 32, 0, dev->stream>>>(c->local.flags(slot, c->world), c->world, c->rank, seq, dev->d_status);
+        RCU_LAUNCH_CHECK(dev);
+    }
+    *y_full = c->local.slot(slot);
+    return RCU_OK;
+}
+
+}  // extern "C"

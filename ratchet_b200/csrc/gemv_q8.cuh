@@ -193,6 +193,7 @@ template <class ActT> struct PlainEpilogue {
         if (bias) s += to_f32<ActT>(bias[u]);
         y[u] = from_f32<ActT>(s);
     }
+    __device__ __forceinline__ void finish() const {}
 };
 
 // y = residual + Linear(x): the Linear output is rounded to f16 first, then added in f16
@@ -205,6 +206,7 @@ struct ResidualEpilogueH {
         const float lin = __half2float(__float2half_rn(acc[0]));
         y[u] = __float2half_rn(lin + __half2float(__ldcg(residual + u)));
     }
+    __device__ __forceinline__ void finish() const {}
 };
 
 // Fused gate_up projection of phi3/mlp.rs:31-39: unit u pairs row u (gate) with row u + N/2 (up);
@@ -217,6 +219,53 @@ struct SiluGateEpilogueH {
         const float up = __half2float(__float2half_rn(acc[1]));
         const float act = __half2float(__float2half_rn(gate / (1.0f + expf(-gate))));
         y[u] = __float2half_rn(up * act);
+    }
+    __device__ __forceinline__ void finish() const {}
+};
+
+// Output shard of a row-sharded Linear, all-gathered by the kernel itself: units are stored into this
+// GPU's slice of its own full-size output buffer; the last CTA of the grid to finish (ticket counter)
+// then copies the slice into the same place of every peer's buffer with plain 16-byte stores over
+// NVLink (peer-mapped memory, no multicast, no collective library) and raises a flag on each peer
+// with a system-scope release store.  Consumers wait on their own flags (bounded) before reading.
+constexpr int kMaxPeers = 8;
+struct PushEpilogueH {
+    static constexpr int UNIT = 1;
+    const __half* bias;            // local slice of the bias or nullptr
+    __half* y_local;               // this rank's slice inside its own full buffer
+    int slice_elems;               // elements in the slice (multiple of 8)
+    unsigned int* ticket;          // zero between launches
+    __half* peer_dst[kMaxPeers];   // where the slice goes in each peer's full buffer
+    unsigned int* peer_flag[kMaxPeers];   // this rank's flag word on each peer
+    int n_peers;
+    unsigned int seq;              // value the flags take when this step's slice has landed
+    __device__ __forceinline__ void store(int u, const float* acc) const {
+        float s = acc[0];
+        if (bias) s += __half2float(bias[u]);
+        y_local[u] = __float2half_rn(s);
+    }
+    __device__ __forceinline__ void finish() const {
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int t = atomicAdd(ticket, 1u);
+            is_last = (t == gridDim.x - 1);
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        const uint4* src = reinterpret_cast<const uint4*>(y_local);
+        const int n16 = slice_elems >> 3;
+        for (int p = 0; p < n_peers; ++p) {
+            uint4* dst = reinterpret_cast<uint4*>(peer_dst[p]);
+            for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
+        }
+        __threadfence_system();
+        __syncthreads();
+        if ((int)threadIdx.x < n_peers)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag[threadIdx.x]), "r"(seq) : "memory");
+        if (threadIdx.x == 0) *ticket = 0;
     }
 };
 
@@ -319,6 +368,7 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
                 if (u0 + i < u_end) epi.store(u0 + i, &acc[i * UNIT]);
         }
     }
+    epi.finish();
 }
 
 // Variant for short kernels (the GEMVs of a decode step): two register slots of loads are put in
@@ -446,6 +496,7 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
             if (it + 3 < n_items) load_item(it + 3, s1);
         }
     }
+    epi.finish();
 }
 
 struct Plan { int ksplit; int grid; };

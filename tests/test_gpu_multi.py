@@ -1,0 +1,72 @@
+"""Row-sharded Q8_0 GEMV with the fused push all-gather on 2+ GPUs of one node (one process per GPU,
+plain peer stores; NVLS and multicast are not involved).  Skipped on a single-GPU box."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as orc
+        from ratchet_b200 import Device, capi
+        from ratchet_b200.comm import Comm, shard_q8
+        torch.cuda.set_device(rank)
+        dev = Device(rank)
+        ok = True
+        worst = 0.0
+        for (N, K, half) in [(4096, 3072, True), (1024, 8192, False), (65536 // 8, 1024, True)]:
+            g = np.random.Generator(np.random.PCG64(N + K))
+            w = (g.standard_normal((N, K)) * 0.02).astype(np.float16 if half else np.float32)
+            full = orc.quantize_q8(w)
+            dt = capi.Q8_0H if half else capi.Q8_0F
+            comm = Comm(dev, rank, world, N)
+            dw = dev.from_quantized(shard_q8(full, dt, N, K, rank, world), dt, (N // world, K))
+            for step in range(4):   # several steps: double-buffered slots and step-numbered flags
+                x = g.standard_normal((1, K)).astype(np.float16)
+                ref = orc.gemv_q8(full, N, K, half, x.reshape(-1)).astype(np.float64)
+                y = comm.linear(dw, dev.from_numpy(x), N).to_numpy().astype(np.float64).reshape(-1)
+                err = np.abs(y - ref).max() / (np.sqrt(np.mean(ref * ref)) + 1e-30)
+                worst = max(worst, err)
+                ok = ok and err < 1e-2
+            dist.barrier()
+            comm.close()
+        dev.close()
+        q.put((rank, ok, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_gemv_push_allgather(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    res = sorted(q.get(timeout=10) for _ in range(world))
+    assert all(ok for _, ok, _ in res), res
