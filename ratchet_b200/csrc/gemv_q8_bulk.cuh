@@ -71,9 +71,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
 }
 // bounded wait; returns false if it gave up (or another thread of the CTA already did)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* status) {
+    unsigned long long t0 = 0;
     for (unsigned i = 0; i < kBulkSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
+        if ((i & 1023u) == 1023u) {     // also bound the wait in wall time: one second
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 1000000000ull) break;
+        }
     }
     *abort_flag = 1;
     atomicOr(status, RCU_DEVFLAG_TIMEOUT);

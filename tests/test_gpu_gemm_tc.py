@@ -1,0 +1,79 @@
+"""The tcgen05 prefill GEMM (Linear convention, f16 activations) against the CPU oracle:
+dequantise (bit-exact) then f32-accumulated matmul, within 1e-2 of the result's scale."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from ratchet_b200 import Device
+    d = Device(0)
+    yield d
+    d.close()
+
+
+def check(got, ref, tol, what):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    assert got.shape == ref.shape, what
+    scale = np.sqrt(np.mean(ref * ref)) + 1e-30
+    bad = np.abs(got - ref) > tol * (scale + np.abs(ref))
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside {tol}; max abs {np.abs(got - ref).max():.3e}, rms {scale:.3e}"
+
+
+# (M, N, K): full tiles, ragged M / N / K edges, several k-steps beyond the pipeline depth, both tile widths
+SHAPES = [(128, 256, 256), (512, 512, 1024), (100, 200, 136), (37, 64, 64), (2048, 256, 512), (130, 1032, 3072), (1500, 384, 384)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_tc_f16(dev, M, N, K, with_bias):
+    g = np.random.Generator(np.random.PCG64(M * 7 + N + K))
+    w = (g.standard_normal((N, K)) * 0.05).astype(np.float16)
+    x = g.standard_normal((M, K)).astype(np.float16)
+    b = g.standard_normal(N).astype(np.float16) if with_bias else None
+    ref = orc.matmul(w, x, b, False, True, True)
+    y = dev.matmul(dev.from_numpy(w), dev.from_numpy(x), None if b is None else dev.from_numpy(b), False, True, True)
+    assert y.shape == (M, N)
+    check(y.to_numpy(), ref, 1e-2, f"f16 {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("kind", ["Q8_0H", "Q4_KH"])
+@pytest.mark.parametrize("M,N,K", [(128, 512, 768), (512, 256, 3072), (77, 96, 512)])
+def test_gemm_tc_quantised(dev, kind, M, N, K):
+    from ratchet_b200 import capi
+    g = np.random.Generator(np.random.PCG64(M + N + K))
+    w = (g.standard_normal((N, K)) * 0.02)
+    x = g.standard_normal((2, M, K)).astype(np.float16)     # a leading batch dimension folds into M
+    if kind == "Q8_0H":
+        buf = orc.quantize_q8(w.astype(np.float16))
+        wd = orc.dequantize_q8(buf, (N, K), True)
+        dt = capi.Q8_0H
+    else:
+        buf = orc.quantize_q4k(w.astype(np.float32), True)
+        wd = orc.dequantize_q4k(buf, (N, K), True)
+        dt = capi.Q4_KH
+    ref = orc.matmul(wd, x, None, False, True, True)
+    y = dev.matmul(dev.from_quantized(buf, dt, (N, K)), dev.from_numpy(x), None, False, True, True)
+    assert y.shape == (2, M, N)
+    check(y.to_numpy(), ref, 1e-2, f"{kind} {M}x{N}x{K}")
+
+
+def test_config3_q4k_prefill_shape(dev):
+    """Config 3 at its smallest M: x [128, 3072] f16 N(0,1), W [8192, 3072] N(0, 0.02) in ratchet Q4_K
+    (f16 super-block scales), out [128, 8192] f16."""
+    from ratchet_b200 import capi
+    g = np.random.Generator(np.random.PCG64(0))
+    M, N, K = 128, 8192, 3072
+    w = (g.standard_normal((N, K), dtype=np.float32) * np.float32(0.02))
+    x = g.standard_normal((M, K)).astype(np.float16)
+    buf = orc.quantize_q4k(w, True)
+    assert buf.size == 14155776          # 144 bytes per 256-weight super-block
+    wd = orc.dequantize_q4k(buf, (N, K), True)
+    ref = orc.matmul(wd, x, None, False, True, True)
+    y = dev.matmul(dev.from_quantized(buf, capi.Q4_KH, (N, K)), dev.from_numpy(x), None, False, True, True)
+    check(y.to_numpy(), ref, 1e-2, "config 3, M=128")
