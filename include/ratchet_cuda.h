@@ -267,6 +267,20 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
                            uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_cache, uint32_t rope_dim, float rope_base,
                            uint32_t position, void* out);
 
+/* rcu_attn_decode without any device allocation.  It has no counterpart in the reference.  It exists
+ * for callers that cannot allocate device memory when they need attention: plug-ins running inside a
+ * host framework that owns the device heap, latency-bound serving loops that cannot take the device
+ * synchronisation of an allocation, processes that have given all free memory to their KV caches.
+ * The split-KV scratch is a fixed 546 KiB array inside the library's device image (held by every GPU
+ * that loads the library until the process exits), which limits this variant to n_heads <= 64 and
+ * head_dim <= 128; larger requests return RCU_ERR_INVALID_ARG with a message naming the limit.
+ * Same arguments and results as rcu_attn_decode.  The first call on a device looks up the array's
+ * device address and should be made before any stream capture.  All calls on a device share the
+ * array: calls that overlap on the GPU race, so keep them on one stream or otherwise ordered. */
+rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, void* k_cache, void* v_cache, uint32_t n_heads,
+                                  uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_cache, uint32_t rope_dim,
+                                  float rope_base, uint32_t position, void* out);
+
 /* ------------------------------------------------------------------ row-sharded Linear over the GPUs of a node
  * No counterpart in the reference, which is single-device (gpu/device.rs:15-16).  A Linear's weight
  * W[N,K] (ratchet-nn/src/linear.rs:17-24) is split by rows: rank r of g holds rows [r N/g, (r+1) N/g)

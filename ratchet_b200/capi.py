@@ -140,6 +140,8 @@ SIGNATURES = {
     "rcu_decoder_position": (C.c_uint32, [C.c_void_p]),
     "rcu_decoder_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rcu_decoder_kernels_per_step": (C.c_uint32, [C.c_void_p]),
+    "rcu_attn_decode_static": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                         C.c_uint32, C.c_float, C.c_uint32, C.c_void_p]),
     "rcu_comm_create": (C.c_int, [_DEV, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
     "rcu_comm_export": (C.c_int, [C.c_void_p, C.c_void_p]),
     "rcu_comm_import": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),

@@ -574,3 +574,79 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of rcu_attn_decode.
+//
+// Some callers may not allocate device memory at the moment they need attention: code running
+// inside a host framework that owns the whole device heap and forbids foreign cudaMalloc calls, a
+// real-time serving loop whose latency budget cannot absorb an allocation (cudaMalloc synchronises
+// the device), or a process that has already handed all free memory to its KV caches.  For them
+// the split-KV scratch (per-head partial results, the per-head completion counters, the RoPE table
+// and the position word) lives in a fixed array in the library's own device image instead of in
+// memory obtained at run time.  Every GPU that loads the library carries these 546 KiB until the
+// process exits.
+//
+// The array is shared by every call on a device and keeps what the previous call left in it: the
+// counters are cleared at the start of each call, everything else is fully rewritten before it is
+// read.  Two calls that overlap on the GPU (different streams, or different host threads using
+// handles of the same device) race on it; callers must keep such calls ordered.
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kStaticMaxHeads = 64;
+constexpr int kStaticMaxHeadDim = 128;
+constexpr size_t kStaticPartialFloats = (size_t)kStaticMaxHeads * kSplits * (kStaticMaxHeadDim + 2);
+constexpr size_t kStaticPartialBytes = kStaticPartialFloats * sizeof(float);                      // 532480
+constexpr size_t kStaticCountersOff = kStaticPartialBytes;                                        // 64 x u32
+constexpr size_t kStaticRopeOff = kStaticCountersOff + 256;                                       // 256 x f32
+constexpr size_t kStaticPosOff = kStaticRopeOff + 256 * sizeof(float);
+constexpr size_t kStaticScratchBytes = kStaticPosOff + 256;
+
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticScratchBytes];
+
+// Device address of the array, per CUDA device ordinal.  In host code the symbol's name is only a
+// handle for the runtime, never a pointer a kernel could use, so the address is looked up once per
+// device (with that device current) and cached here.
+constexpr int kMaxDeviceOrdinals = 64;
+void* g_attn_static_addr[kMaxDeviceOrdinals] = {};
+std::mutex g_attn_static_mu;
+}  // namespace
+
+extern "C" rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, void* k_cache, void* v_cache, uint32_t n_heads,
+                                             uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_cache, uint32_t rope_dim,
+                                             float rope_base, uint32_t position, void* out) {
+    if (!dev || !qkv || !k_cache || !v_cache || !out) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(dev, n_heads >= 1 && n_heads <= (uint32_t)kStaticMaxHeads,
+                "attn_decode_static: n_heads %u exceeds the built-in scratch (at most %d heads); use rcu_attn_decode", n_heads, kStaticMaxHeads);
+    RCU_REQUIRE(dev, head_dim <= (uint32_t)kStaticMaxHeadDim,
+                "attn_decode_static: head_dim %u exceeds the built-in scratch (at most %d); use rcu_attn_decode", head_dim, kStaticMaxHeadDim);
+    RCU_REQUIRE(dev, n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attn_decode_static: n_heads must be a multiple of n_kv_heads");
+    RCU_REQUIRE(dev, position < max_cache, "attn_decode_static: position %u outside the cache (%u)", position, max_cache);
+    RCU_REQUIRE(dev, rope_dim % 2 == 0 && rope_dim <= head_dim && rope_dim <= 256, "attn_decode_static: bad rope_dim");
+    RCU_REQUIRE(dev, dev->ordinal >= 0 && dev->ordinal < kMaxDeviceOrdinals, "attn_decode_static: device ordinal %d not supported", dev->ordinal);
+    DevGuard g(dev->ordinal);
+    unsigned char* base = nullptr;
+    {
+        // first call on this device: resolve the array's device address (do this before any stream capture)
+        std::lock_guard<std::mutex> lock(g_attn_static_mu);
+        if (!g_attn_static_addr[dev->ordinal]) {
+            void* p = nullptr;
+            RCU_CUDA(dev, cudaGetSymbolAddress(&p, g_attn_static_scratch));
+            g_attn_static_addr[dev->ordinal] = p;
+        }
+        base = (unsigned char*)g_attn_static_addr[dev->ordinal];
+    }
+    float* partial = reinterpret_cast<float*>(base);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(base + kStaticCountersOff);
+    float* rope_tab = reinterpret_cast<float*>(base + kStaticRopeOff);
+    uint32_t* d_pos = reinterpret_cast<uint32_t*>(base + kStaticPosOff);
+    // the completion counters must start at zero whatever an earlier (possibly failed) call left behind
+    RCU_CUDA(dev, cudaMemsetAsync(counters, 0, (size_t)kStaticMaxHeads * sizeof(unsigned int), dev->stream));
+    set_u32_kernel<<<1, 1, 0, dev->stream>>>(d_pos, position);
+    RCU_LAUNCH_CHECK(dev);
+    rope_table_kernel<<<1, 128, 0, dev->stream>>>(d_pos, logf(rope_base), (int)rope_dim / 2, rope_tab);
+    RCU_LAUNCH_CHECK(dev);
+    AttnParams ap{(const __half*)qkv, (__half*)k_cache, (__half*)v_cache, (int)n_heads, (int)n_kv_heads, (int)max_cache, (int)rope_dim,
+                  d_pos, rope_tab, 1.0f / sqrtf((float)head_dim), partial, counters, (__half*)out};
+    return launch_attn(dev, ap, (int)head_dim);
+}
