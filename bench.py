@@ -252,6 +252,51 @@ def gemv_sweep(dev, torch, stream):
     return out
 
 
+def _q4kh_weights(N, K, seed):
+    """Random ratchet Q4_KH buffer (dtype/blocks.rs:124-148): random nibbles and 6-bit scale/min codes,
+    f16 super-block d / dmin of the magnitude an N(0, 0.02) weight produces."""
+    from ratchet_b200 import capi
+    rng = np.random.Generator(np.random.PCG64(seed))
+    n = N * K
+    nb = n // 256
+    off = capi.dtype_segments(capi.Q4_KH, n)
+    buf = np.zeros(capi.dtype_nbytes(capi.Q4_KH, n), np.uint8)
+    buf[off[0]: off[0] + n // 2] = rng.integers(0, 256, n // 2, dtype=np.uint8)
+    buf[off[1]: off[1] + nb * 12] = rng.integers(0, 256, nb * 12, dtype=np.uint8)
+    buf[off[2]: off[2] + nb * 2] = np.full(nb, 0.0011, np.float16).view(np.uint8)
+    buf[off[3]: off[3] + nb * 2] = np.full(nb, 0.00015, np.float16).view(np.uint8)
+    return buf
+
+
+def prefill_gemm_bench(dev, torch, stream):
+    """Config 3: x [M, 3072] f16 . W[8192, 3072]^T with W in ratchet Q4_KH, out [M, 8192] f16, M in
+    {128, 512, 2048}: dequantise-to-f16 kernel + tcgen05 GEMM, timed together from a CUDA graph, and
+    the GEMM alone on f16 weights (tensor-pipe figure)."""
+    from ratchet_b200 import capi
+    N, K = 8192, 3072
+    wq = dev.from_quantized(_q4kh_weights(N, K, 21), capi.Q4_KH, (N, K))
+    wf = dev.dequantize(wq)
+    peak_tf = 1678.2
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            peak_tf = float(json.load(f)["bf16_tflops"])
+    out = []
+    for M in (128, 512, 2048):
+        x = dev.from_numpy(np.random.Generator(np.random.PCG64(M)).standard_normal((M, K)).astype(np.float16))
+        y = dev.empty(capi.F16, (M, N))
+        run_q = lambda i: dev.matmul(wq, x, None, False, True, True, out=y)
+        run_f = lambda i: dev.matmul(wf, x, None, False, True, True, out=y)
+        run_q(0); run_f(0)
+        ms_q = _time_graph(torch, stream, run_q, 20)
+        ms_f = _time_graph(torch, stream, run_f, 20)
+        flops = 2.0 * M * N * K
+        out.append({"M": M, "N": N, "K": K, "q4k_us": ms_q * 1e3, "q4k_tflops": flops / ms_q / 1e9, "f16_gemm_us": ms_f * 1e3,
+                    "f16_gemm_tflops": flops / ms_f / 1e9, "f16_gemm_frac_of_measured_bf16_peak": flops / ms_f / 1e9 / peak_tf,
+                    "bytes": M * K * 2 + 14155776 + M * N * 2})
+    return out
+
+
 PHI3 = dict(n_layers=32, d=3072, n_heads=32, head_dim=96, ffn=8192, vocab=32064, max_cache=4096, kv_prior=1024)
 
 
@@ -479,6 +524,7 @@ def run_ours(args):
     extras = {}
     if world == 1 and not args.rows and not args.no_extras:
         extras["gemv_sweep"] = gemv_sweep(dev, torch, stream)
+        extras["q4k_prefill_gemm"] = prefill_gemm_bench(dev, torch, stream)
         extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
     if rank == 0:
         line.update(extras)

@@ -5,35 +5,57 @@
 
 namespace {
 
-// 16 int8 per thread: one 16-byte load, one scale, 16 products rounded in the scale type.
+template <class T> struct Pack8;
+template <> struct Pack8<__half> {
+    __device__ static __forceinline__ void store(__half* dst, const float* v) {
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(v[i]);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+    }
+};
+template <> struct Pack8<float> {
+    __device__ static __forceinline__ void store(float* dst, const float* v) {
+        reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+// 8 int8 per thread: one 8-byte load, one scale, products rounded once in the scale type, one
+// 16-byte (f16) or two 16-byte (f32) stores; consecutive threads write consecutive vectors.
 template <class ScaleT>
 __global__ void __launch_bounds__(256)
-dequant_q8_kernel(const uint4* __restrict__ q, const ScaleT* __restrict__ d, ScaleT* __restrict__ out, size_t n16) {
+dequant_q8_kernel(const uint2* __restrict__ q, const ScaleT* __restrict__ d, ScaleT* __restrict__ out, size_t n8) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
-        const uint4 w = q[i];
-        const float sc = to_f32<ScaleT>(d[i >> 1]);
-        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-        ScaleT* o = out + i * 16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const uint2 w = q[i];
+        const float sc = to_f32<ScaleT>(d[i >> 2]);
+        const uint32_t ws[2] = {w.x, w.y};
+        float v[8];
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int a = 0; a < 2; ++a)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int v = (int)(ws[a] << (8 * (3 - j))) >> 24;   // quant.rs:121-125
-                o[a * 4 + j] = from_f32<ScaleT>((float)v * sc);
+                const int qv = (int)(ws[a] << (8 * (3 - j))) >> 24;   // quant.rs:121-125
+                v[a * 4 + j] = rnd<ScaleT>((float)qv * sc);
             }
+        Pack8<ScaleT>::store(out + i * 8, v);
     }
 }
 
-// one thread per (super-block, 32-weight sub-block)
+// 8 weights per thread (half of a 16-byte run of nibbles): consecutive threads write consecutive
+// 16-byte vectors.  Weight index w -> super-block w/256, sub-block (w%256)/32, position w%32; the
+// nibbles of sub-blocks 2c and 2c+1 share the 32 bytes of chunk c (low / high nibble).
 template <class FP>
 __global__ void __launch_bounds__(256)
 dequant_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scales, const FP* __restrict__ dmin,
-                   const FP* __restrict__ d, FP* __restrict__ out, size_t nsub) {
+                   const FP* __restrict__ d, FP* __restrict__ out, size_t n8) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nsub; i += stride) {
-        const size_t b = i >> 3;
-        const int j = (int)(i & 7);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const size_t w0 = i * 8;
+        const size_t b = w0 >> 8;
+        const int within = (int)(w0 & 255);
+        const int j = within >> 5, l0 = within & 31;
         const uint8_t* sc = scales + b * 12;
         uint32_t s, m;
         if (j < 4) {
@@ -45,11 +67,15 @@ dequant_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ s
         }
         const float delta = rnd<FP>((float)s * to_f32<FP>(d[b]));
         const float mn = rnd<FP>((float)m * to_f32<FP>(dmin[b]));
-        const uint8_t* qb = qs + b * 128 + (j >> 1) * 32;
-        FP* o = out + b * 256 + j * 32;
+        const uint2 qw = *reinterpret_cast<const uint2*>(qs + b * 128 + (j >> 1) * 32 + l0);
         const int shift = (j & 1) * 4;
-#pragma unroll 8
-        for (int l = 0; l < 32; ++l) o[l] = from_f32<FP>(fmaf((float)((qb[l] >> shift) & 0xF), delta, -mn));
+        const uint32_t ws[2] = {qw.x >> shift, qw.y >> shift};
+        float v[8];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[a * 4 + e] = rnd<FP>(fmaf((float)((ws[a] >> (8 * e)) & 0xF), delta, -mn));
+        Pack8<FP>::store(out + w0, v);
     }
 }
 
@@ -68,13 +94,13 @@ extern "C" rcu_status rcu_dequantize(rcu_device* dev, const rcu_tensor* src, rcu
     const int cap = dev->sm_count * 8;
     if (dt_is_q8(src->dt)) {
         RCU_REQUIRE(dev, n % 32 == 0, "dequantize: Q8_0 needs a multiple of 32 elements");   // quant.rs:102-103
-        const size_t n16 = n / 16;
-        const int grid = (int)std::min<size_t>((n16 + 255) / 256, (size_t)cap);
-        if (src->dt == RCU_Q8_0F) dequant_q8_kernel<float><<<grid, 256, 0, dev->stream>>>((const uint4*)base, (const float*)(base + off[1]), (float*)dst->data, n16);
-        else dequant_q8_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint4*)base, (const __half*)(base + off[1]), (__half*)dst->data, n16);
+        const size_t n8 = n / 8;
+        const int grid = (int)std::min<size_t>((n8 + 255) / 256, (size_t)cap);
+        if (src->dt == RCU_Q8_0F) dequant_q8_kernel<float><<<grid, 256, 0, dev->stream>>>((const uint2*)base, (const float*)(base + off[1]), (float*)dst->data, n8);
+        else dequant_q8_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint2*)base, (const __half*)(base + off[1]), (__half*)dst->data, n8);
     } else {
         RCU_REQUIRE(dev, n % 256 == 0, "dequantize: Q4_K needs a multiple of 256 elements");
-        const size_t nsub = n / 32;
+        const size_t nsub = n / 8;
         const int grid = (int)std::min<size_t>((nsub + 255) / 256, (size_t)cap);
         if (src->dt == RCU_Q4_KF) dequant_q4k_kernel<float><<<grid, 256, 0, dev->stream>>>((const uint8_t*)base, (const uint8_t*)base + off[1], (const float*)(base + off[2]), (const float*)(base + off[3]), (float*)dst->data, nsub);
         else dequant_q4k_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint8_t*)base, (const uint8_t*)base + off[1], (const __half*)(base + off[2]), (const __half*)(base + off[3]), (__half*)dst->data, nsub);
