@@ -14,12 +14,16 @@
 //                      the accumulator barrier;
 //   warps 2-5          epilogue: tcgen05.ld the f32 accumulators (lane = token row, column =
 //                      output feature), add bias, round to f16, store rows.
-// Quantised weights (Q8_0H, Q4_KH) are dequantised to f16 first by rcu_dequantize (bit-exact with
-// the CPU dequantiser) into pooled scratch and then take the same path.
+// Quantised weights (Q8_0H, Q4_KH) are dequantised inside the kernel (up to 512 token rows): TMA
+// brings the packed bytes of the weight tile into shared memory, further warps convert them to f16
+// with the CPU dequantiser's arithmetic and write the swizzled tile the MMA reads.  Larger M
+// dequantises once into pooled scratch and runs the f16 kernel.
 //
 // Every mbarrier wait is bounded; a wait that gives up sets RCU_DEVFLAG_TIMEOUT and an abort word in
 // shared memory that ends all other waits of the CTA, and the CTA still frees its tensor memory.
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "gemv_q8_bulk.cuh"   // mbarrier + tensor-map helpers
 
@@ -95,19 +99,86 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v) {
 
 namespace {
 
-template <int BN>
-__global__ void __launch_bounds__(kThreadsTc, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const __half* __restrict__ bias,
-               __half* __restrict__ out, int M, int N, int K, int* status) {
+enum { WK_F16 = 0, WK_Q8 = 1, WK_Q4K = 2 };   // how the weight tile reaches shared memory
+
+struct QuantArgs {
+    const void* scales;     // Q8_0H: f16 block scales [N * K/32]; Q4_KH: 12-byte (scale, min) packs [N * K/256]
+    const __half* d;        // Q4_KH super-block scale  [N * K/256]
+    const __half* dmin;     // Q4_KH super-block min    [N * K/256]
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+// 8 consecutive int8 (two packed words) -> 8 f16 weights q * d.  byte ^ 0x80 under exponent byte 0x64
+// is the half 1024 + (q + 128); subtracting 1152 gives q exactly, and the f16 product q * d is the f32
+// product rounded once (quant.rs:121-125 on f16 scales).
+__device__ __forceinline__ uint4 dequant8_q8(uint32_t w0, uint32_t w1, __half2 d2) {
+    const __half2 off = __float2half2_rn(1152.0f);
+    const uint32_t x0 = w0 ^ 0x80808080u, x1 = w1 ^ 0x80808080u;
+    uint4 o;
+    o.x = as_u32(__hmul2_rn(__hsub2_rn(as_h2(prmt(x0, 0x64646464u, 0x4140u)), off), d2));
+    o.y = as_u32(__hmul2_rn(__hsub2_rn(as_h2(prmt(x0, 0x64646464u, 0x4342u)), off), d2));
+    o.z = as_u32(__hmul2_rn(__hsub2_rn(as_h2(prmt(x1, 0x64646464u, 0x4140u)), off), d2));
+    o.w = as_u32(__hmul2_rn(__hsub2_rn(as_h2(prmt(x1, 0x64646464u, 0x4342u)), off), d2));
+    return o;
+}
+
+// 8 consecutive 4-bit codes (the low nibbles of two words already shifted for the sub-block) ->
+// fma(q, delta, -min) in f16 with a single rounding (quantized.rs:230).
+__device__ __forceinline__ uint4 dequant8_q4(uint32_t x0, uint32_t x1, __half2 delta2, __half2 negmin2) {
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+    uint4 o;
+    {
+        const uint32_t p02 = (x0 & 0x000F000Fu) | 0x64006400u, p13 = ((x0 >> 8) & 0x000F000Fu) | 0x64006400u;
+        o.x = as_u32(__hfma2(__hsub2_rn(as_h2(prmt(p02, p13, 0x5410u)), k1024), delta2, negmin2));
+        o.y = as_u32(__hfma2(__hsub2_rn(as_h2(prmt(p02, p13, 0x7632u)), k1024), delta2, negmin2));
+    }
+    {
+        const uint32_t p02 = (x1 & 0x000F000Fu) | 0x64006400u, p13 = ((x1 >> 8) & 0x000F000Fu) | 0x64006400u;
+        o.z = as_u32(__hfma2(__hsub2_rn(as_h2(prmt(p02, p13, 0x5410u)), k1024), delta2, negmin2));
+        o.w = as_u32(__hfma2(__hsub2_rn(as_h2(prmt(p02, p13, 0x7632u)), k1024), delta2, negmin2));
+    }
+    return o;
+}
+
+// byte i (0..11) of a 12-byte pack held in three registers (selects, no indexed register array)
+__device__ __forceinline__ uint32_t pack_byte(const uint32_t* w, int i) {
+    const uint32_t word = i < 4 ? w[0] : (i < 8 ? w[1] : w[2]);
+    return (word >> (8 * (i & 3))) & 0xFFu;
+}
+
+// One CTA computes one 128 x BN output tile.  WK_F16: the weight tile arrives by TMA like the
+// activation tile.  WK_Q8 / WK_Q4K: TMA brings the packed bytes of the tile (BN rows x 64 int8 or
+// BN rows x 32 nibble bytes) into the tail of the stage's weight area; warps 6-9 read them into
+// registers, convert to f16 and write the 128-byte-swizzled K-major tile the MMA reads, so the
+// dequantised matrix never exists in global memory.
+// converting warps per CTA: two per scheduler for the wide tile (one 32-weight task per thread per stage)
+__host__ __device__ constexpr int conv_warps(int bn) { return bn >= 128 ? 8 : 4; }
+
+// Two CTAs share an SM (half of its shared memory and at most half of its tensor memory each), so one
+// CTA's pipeline fill and epilogue overlap the other's main loop.
+template <int BN, int WK, int STAGES>
+__global__ void __launch_bounds__(WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, 2)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QuantArgs qa,
+               const __half* __restrict__ bias, __half* __restrict__ out, int M, int N, int K, int* status) {
     constexpr int A_BYTES = TM * TK * 2;          // 16 KiB
     constexpr int B_BYTES = BN * TK * 2;
     constexpr int STAGE = A_BYTES + B_BYTES;
+    constexpr int RAW_ROW = WK == WK_Q8 ? 64 : 32;
+    constexpr int RAW_BYTES = WK == WK_F16 ? 0 : BN * RAW_ROW;
     extern __shared__ unsigned char smem_dyn[];
     // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * STAGE);
-    uint64_t* empty = full + kStages;
-    uint64_t* accum_bar = empty + kStages;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* raw_full = empty + STAGES;
+    uint64_t* accum_bar = raw_full + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -116,9 +187,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const int nk = (K + TK - 1) / TK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], WK == WK_F16 ? 1 : conv_warps(BN));   // TMA transaction, or one arrival per converting warp
             mbar_init(&empty[s], 1);
+            mbar_init(&raw_full[s], 1);
         }
         mbar_init(accum_bar, 1);
         *abort_flag = 0;
@@ -137,12 +209,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     if (warp == 0) {
         if (lane == 0) {
             for (int it = 0; it < nk; ++it) {
-                const int s = it % kStages;
-                if (it >= kStages && !mbar_wait(&empty[s], ((it / kStages) - 1) & 1, abort_flag, status)) break;
-                mbar_expect_tx(&full[s], STAGE);
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) break;
                 unsigned char* st = smem + s * STAGE;
-                tma_load_2d(st, &xmap, it * TK, m0, &full[s]);             // activations: rows m0.., k it*64..
-                tma_load_2d(st + A_BYTES, &wmap, it * TK, n0, &full[s]);   // weights: rows n0..
+                if (WK == WK_F16) {
+                    mbar_expect_tx(&full[s], STAGE);
+                    tma_load_2d(st, &xmap, it * TK, m0, &full[s]);             // activations: rows m0.., k it*64..
+                    tma_load_2d(st + A_BYTES, &wmap, it * TK, n0, &full[s]);   // weights: rows n0..
+                } else {
+                    mbar_expect_tx(&raw_full[s], A_BYTES + RAW_BYTES);
+                    tma_load_2d(st, &xmap, it * TK, m0, &raw_full[s]);
+                    tma_load_2d(st + STAGE - RAW_BYTES, &wmap, it * RAW_ROW, n0, &raw_full[s]);   // packed bytes of 64 weights per row
+                }
             }
         }
     } else if (warp == 1) {
@@ -150,8 +228,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             constexpr uint32_t idesc = umma_idesc_f16(TM, BN);
             bool ok = true;
             for (int it = 0; it < nk && ok; ++it) {
-                const int s = it % kStages;
-                ok = mbar_wait(&full[s], (it / kStages) & 1, abort_flag, status);
+                const int s = it % STAGES;
+                ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, status);
                 if (!ok) break;
                 tc_fence_after();
                 unsigned char* st = smem + s * STAGE;
@@ -166,7 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
             umma_commit(accum_bar);          // accumulators complete (arrives even after an abort so the epilogue ends)
         }
-    } else {
+    } else if (warp < 6) {
         // epilogue warps 2..5: tensor-memory lane quarter = warp index modulo 4
         const int q = warp & 3;
         const bool ok = mbar_wait(accum_bar, 0, abort_flag, status);
@@ -195,6 +273,135 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 }
             }
         }
+    } else if (WK != WK_F16) {
+        // converting warps 6...  Task = (tile row r, half h): 32 weights = one Q8_0 block or one Q4_K
+        // sub-block = four 16-byte chunks of the row's 128-byte swizzled line.
+        constexpr int CT = conv_warps(BN) * 32;      // converting threads
+        constexpr int TPT = BN * 2 / CT;
+        constexpr int PF = 4;                       // Q8_0: block scales are fetched this many stages ahead
+        const int dt = threadIdx.x - kThreadsTc;
+        // Scales come from global memory and are requested ahead of use, so their latency overlaps the
+        // conversion of earlier stages: Q8_0 keeps a queue of PF block scales per task; Q4_K keeps the
+        // current and the next super-block's packs (one super-block = four stages).
+        __half q8_queue[PF][TPT];
+        uint32_t pk_cur[TPT][3], pk_next[TPT][3];
+        __half dd_cur[TPT][2], dd_next[TPT][2];
+        auto q8_fetch = [&](int stage, int t) -> __half {
+            const int task = dt + t * CT, r = task >> 1, h = task & 1;
+            const int row = n0 + r, kk = stage * TK + h * 32;
+            if (row < N && kk < K) return reinterpret_cast<const __half*>(qa.scales)[(size_t)row * (K >> 5) + (kk >> 5)];
+            return __float2half_rn(0.f);
+        };
+        auto q4_fetch = [&](int sblock, int t, uint32_t* pk, __half* dd) {
+            const int task = dt + t * CT, r = task >> 1;
+            const int row = n0 + r;
+            pk[0] = pk[1] = pk[2] = 0u;
+            dd[0] = dd[1] = __float2half_rn(0.f);
+            if (row < N && sblock * 256 < K) {
+                const size_t sb = (size_t)row * (K >> 8) + sblock;
+                const uint32_t* g = reinterpret_cast<const uint32_t*>(qa.scales) + sb * 3;
+                pk[0] = __ldg(g); pk[1] = __ldg(g + 1); pk[2] = __ldg(g + 2);
+                dd[0] = qa.d[sb];
+                dd[1] = qa.dmin[sb];
+            }
+        };
+#pragma unroll
+        for (int t = 0; t < TPT; ++t) {
+            if (WK == WK_Q8) {
+#pragma unroll
+                for (int p = 0; p < PF; ++p) q8_queue[p][t] = q8_fetch(p, t);
+            } else {
+                q4_fetch(0, t, pk_next[t], dd_next[t]);
+            }
+        }
+        bool stop = false;
+        for (int it0 = 0; it0 < nk && !stop; it0 += PF) {
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {               // unrolled: queue slot u is a fixed register
+            const int it = it0 + u;
+            if (it >= nk || stop) break;
+            const int s = it % STAGES;
+            const int k0 = it * TK;
+            __half2 mul2[TPT], neg2[TPT];
+            bool valid[TPT];
+#pragma unroll
+            for (int t = 0; t < TPT; ++t) {
+                const int task = dt + t * CT, r = task >> 1, h = task & 1;
+                const int row = n0 + r;
+                valid[t] = row < N && k0 + h * 32 < K;
+                neg2[t] = __float2half2_rn(0.f);
+                if (WK == WK_Q8) {
+                    mul2[t] = __half2half2(q8_queue[u][t]);
+                    q8_queue[u][t] = q8_fetch(it + PF, t);     // consumed PF stages from now
+                } else {
+                    if ((it & 3) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 3; ++i) pk_cur[t][i] = pk_next[t][i];
+                        dd_cur[t][0] = dd_next[t][0];
+                        dd_cur[t][1] = dd_next[t][1];
+                        q4_fetch((it >> 2) + 1, t, pk_next[t], dd_next[t]);
+                    }
+                    const uint32_t* w = pk_cur[t];
+                    const int j = (it & 3) * 2 + h;
+                    uint32_t sc, mn;
+                    if (j < 4) {                                   // quantized.rs:158-204
+                        sc = pack_byte(w, j) & 63u;
+                        mn = pack_byte(w, j + 4) & 63u;
+                    } else {
+                        sc = (pack_byte(w, j + 4) & 0xFu) | ((pack_byte(w, j - 4) >> 6) << 4);
+                        mn = (pack_byte(w, j + 4) >> 4) | ((pack_byte(w, j) >> 6) << 4);
+                    }
+                    // delta = fp(scale * d), min = fp(m * dmin): small integers times f16, rounded once
+                    mul2[t] = __half2half2(__hmul_rn(__uint2half_rn(sc), dd_cur[t][0]));
+                    neg2[t] = __half2half2(__hneg(__hmul_rn(__uint2half_rn(mn), dd_cur[t][1])));
+                }
+            }
+            const bool arrived = mbar_wait(&raw_full[s], (it / STAGES) & 1, abort_flag, status);
+            unsigned char* bt = smem + s * STAGE + A_BYTES;
+            const unsigned char* raw = smem + s * STAGE + STAGE - RAW_BYTES;
+            uint4 qv[TPT][2];
+#pragma unroll
+            for (int t = 0; t < TPT; ++t) {
+                const int task = dt + t * CT, r = task >> 1, h = task & 1;
+                const uint4* src = reinterpret_cast<const uint4*>(raw + r * RAW_ROW + (WK == WK_Q8 ? h * 32 : 0));
+                qv[t][0] = src[0];
+                qv[t][1] = src[1];
+            }
+            // the packed bytes sit inside the area the f16 tile is written to: every task's bytes are in
+            // registers before any thread stores (named barrier 1: the four converting warps).  The same
+            // barrier tells all of them whether any wait gave up, so they leave the loop together.
+            uint32_t gave_up;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.eq.u32 q, %1, 0;\n\t"
+                "barrier.cta.red.or.pred p, 1, %2, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(gave_up)
+                : "r"((uint32_t)arrived), "n"(CT)
+                : "memory");
+            if (gave_up) { stop = true; break; }
+#pragma unroll
+            for (int t = 0; t < TPT; ++t) {
+                const int task = dt + t * CT, r = task >> 1, h = task & 1;
+                const uint32_t w[8] = {qv[t][0].x, qv[t][0].y, qv[t][0].z, qv[t][0].w, qv[t][1].x, qv[t][1].y, qv[t][1].z, qv[t][1].w};
+                unsigned char* line = bt + r * 128;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                    if (valid[t]) {
+                        if (WK == WK_Q8) o = dequant8_q8(w[2 * i], w[2 * i + 1], mul2[t]);
+                        else o = dequant8_q4(w[2 * i] >> (4 * h), w[2 * i + 1] >> (4 * h), mul2[t], neg2[t]);
+                    }
+                    const int chunk = (4 * h + i) ^ (r & 7);           // 128-byte swizzle: 16-byte chunk index xor row-in-group
+                    *reinterpret_cast<uint4*>(line + chunk * 16) = o;
+                }
+            }
+            // generic-proxy stores -> visible to the tensor core's async-proxy reads, then one arrival per warp
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -203,13 +410,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     }
 }
 
-template <int BN>
-rcu_status launch_tc(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, void* out, int M, int N, int K) {
-    const size_t smem = (size_t)kStages * (TM * TK * 2 + BN * TK * 2) + 1024 + 256;
-    auto kern = gemm_tc_kernel<BN>;
+template <int BN, int WK>
+rcu_status launch_tc(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const QuantArgs& qa, const void* bias, void* out,
+                     int M, int N, int K) {
+    constexpr int STAGE = TM * TK * 2 + BN * TK * 2;
+    constexpr int STAGES = (100 * 1024) / STAGE;     // two CTAs per SM
+    const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
+    auto kern = gemm_tc_kernel<BN, WK, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM);
-    kern<<<grid, kThreadsTc, smem, dev->stream>>>(xmap, wmap, (const __half*)bias, (__half*)out, M, N, K, dev->d_status);
+    kern<<<grid, WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, smem, dev->stream>>>(xmap, wmap, qa, (const __half*)bias, (__half*)out, M, N, K,
+                                                                                      dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -242,29 +453,61 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
     if (!rcu_gemm_tc_eligible(lhs_dt, act_dt, M, N, K)) return RCU_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w)) & 15) return RCU_ERR_UNSUPPORTED;
     DevGuard g(dev->ordinal);
-    const void* wf16 = w;
-    void* scratch = nullptr;
+    // Quantised weights.  The fused kernel converts a weight tile once per 128-row token tile, i.e.
+    // M/128 times over the whole problem; beyond kFusedMaxM token rows that repeated conversion costs
+    // more than converting the matrix once into pooled f16 scratch (which stays in L2) and running the
+    // f16 kernel on it.  RCU_GEMM_FUSED=0/1 forces either path.
+    constexpr uint64_t kFusedMaxM = 512;
     if (lhs_dt != RCU_F16) {
-        // dequantise to f16 (bit-exact with quant.rs / quantized.rs arithmetic) into pooled scratch
-        rcu_status st = rcu_alloc(dev, N * K * 2, &scratch);
-        if (st != RCU_OK) return st;
-        rcu_tensor src{lhs_dt, 2, {N, K, 1, 1}, const_cast<void*>(w)};
-        rcu_tensor dst{RCU_F16, 2, {N, K, 1, 1}, scratch};
-        st = rcu_dequantize(dev, &src, &dst);
-        if (st != RCU_OK) { rcu_free(dev, scratch); return st; }
-        wf16 = scratch;
+        const char* force = getenv("RCU_GEMM_FUSED");
+        const bool fused = force ? atoi(force) != 0 : M <= kFusedMaxM;
+        if (!fused) {
+            void* scratch = nullptr;
+            rcu_status st = rcu_alloc(dev, N * K * 2, &scratch);
+            if (st != RCU_OK) return st;
+            rcu_tensor src{lhs_dt, 2, {N, K, 1, 1}, const_cast<void*>(w)};
+            rcu_tensor dst{RCU_F16, 2, {N, K, 1, 1}, scratch};
+            st = rcu_dequantize(dev, &src, &dst);
+            if (st == RCU_OK) st = rcu_gemm_tc_dispatch(dev, RCU_F16, scratch, act_dt, x, bias, y, M, N, K);
+            rcu_free(dev, scratch);   // the pool reuses blocks in stream order
+            return st;
+        }
     }
     // tile width: enough CTAs to cover the SMs when M is small
     const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128);
     const int bn = tiles128 >= (uint64_t)dev->sm_count ? 128 : 64;
     CUtensorMap xmap, wmap;
+    QuantArgs qa{nullptr, nullptr, nullptr};
+    bool maps = make_map_f16_sw128(&xmap, x, M, K, TM);
+    const int wk = lhs_dt == RCU_F16 ? WK_F16 : (lhs_dt == RCU_Q8_0H ? WK_Q8 : WK_Q4K);
+    size_t off[4];
+    if (wk == WK_F16) {
+        maps = maps && make_map_f16_sw128(&wmap, w, N, K, (uint32_t)bn);
+    } else {
+        rcu_dtype_segments(lhs_dt, N * K, off);
+        const char* base = (const char*)w;
+        if (wk == WK_Q8) {
+            // packed int8 [N, K]: 64 bytes of a row per stage
+            maps = maps && gemvq8::make_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, N, K, 64, (uint32_t)bn);
+            qa.scales = base + off[1];
+        } else {
+            // nibble bytes [N, K/2]: 32 bytes of a row per stage (sub-blocks 2c and 2c+1 of a super-block)
+            maps = maps && gemvq8::make_map_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, N, K / 2, 32, (uint32_t)bn);
+            qa.scales = base + off[1];
+            qa.dmin = (const __half*)(base + off[2]);
+            qa.d = (const __half*)(base + off[3]);
+        }
+    }
     rcu_status st = RCU_OK;
-    if (!make_map_f16_sw128(&xmap, x, M, K, TM) || !make_map_f16_sw128(&wmap, wf16, N, K, (uint32_t)bn))
+    if (!maps)
         st = rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu)", (unsigned long long)M,
                       (unsigned long long)N, (unsigned long long)K);
-    if (st == RCU_OK) st = bn == 128 ? launch_tc<128>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K)
-                                     : launch_tc<64>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K);
-    // the pool reuses blocks in stream order, so the scratch can go back right after the launch
-    if (scratch) rcu_free(dev, scratch);
+#define RCU_TC(BN_, WK_) launch_tc<BN_, WK_>(dev, xmap, wmap, qa, bias, y, (int)M, (int)N, (int)K)
+    if (st == RCU_OK) {
+        if (wk == WK_F16) st = bn == 128 ? RCU_TC(128, WK_F16) : RCU_TC(64, WK_F16);
+        else if (wk == WK_Q8) st = bn == 128 ? RCU_TC(128, WK_Q8) : RCU_TC(64, WK_Q8);
+        else st = bn == 128 ? RCU_TC(128, WK_Q4K) : RCU_TC(64, WK_Q4K);
+    }
+#undef RCU_TC
     return st;
 }

@@ -20,15 +20,34 @@ inline int copy_grid(const rcu_device* dev, size_t work) {
 }
 
 // rows x row_bytes, source/destination row pitches in bytes. U = bytes per thread step.
-template <class U>
+// I is the index type of the flat unit counter: 32-bit division whenever the unit count allows it.
+template <class U, class I>
 __global__ void __launch_bounds__(256)
 copy2d_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t rows, size_t row_units, size_t spitch, size_t dpitch) {
     const size_t total = rows * row_units;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const size_t r = i / row_units, c = i - r * row_units;
-        *reinterpret_cast<U*>(dst + r * dpitch + c * sizeof(U)) = *reinterpret_cast<const U*>(src + r * spitch + c * sizeof(U));
+    const I ru = (I)row_units;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + stride < total; i += 2 * stride) {      // two units in flight per thread
+        const I r0 = (I)i / ru, c0 = (I)i - r0 * ru;
+        const I r1 = (I)(i + stride) / ru, c1 = (I)(i + stride) - r1 * ru;
+        const U u0 = *reinterpret_cast<const U*>(src + (size_t)r0 * spitch + (size_t)c0 * sizeof(U));
+        const U u1 = *reinterpret_cast<const U*>(src + (size_t)r1 * spitch + (size_t)c1 * sizeof(U));
+        *reinterpret_cast<U*>(dst + (size_t)r0 * dpitch + (size_t)c0 * sizeof(U)) = u0;
+        *reinterpret_cast<U*>(dst + (size_t)r1 * dpitch + (size_t)c1 * sizeof(U)) = u1;
     }
+    if (i < total) {
+        const I r = (I)i / ru, c = (I)i - r * ru;
+        *reinterpret_cast<U*>(dst + (size_t)r * dpitch + (size_t)c * sizeof(U)) = *reinterpret_cast<const U*>(src + (size_t)r * spitch + (size_t)c * sizeof(U));
+    }
+}
+
+template <class U>
+void launch_copy2d(rcu_device* dev, const char* s, char* d, size_t rows, size_t row_units, size_t spitch, size_t dpitch) {
+    const size_t total = rows * row_units;
+    const int grid = copy_grid(dev, total / 2 + 1);
+    if (total <= 0xffffffffull) copy2d_kernel<U, uint32_t><<<grid, 256, 0, dev->stream>>>(s, d, rows, row_units, spitch, dpitch);
+    else copy2d_kernel<U, uint64_t><<<grid, 256, 0, dev->stream>>>(s, d, rows, row_units, spitch, dpitch);
 }
 
 rcu_status copy2d(rcu_device* dev, const void* src, void* dst, size_t rows, size_t row_bytes, size_t spitch, size_t dpitch) {
@@ -36,10 +55,11 @@ rcu_status copy2d(rcu_device* dev, const void* src, void* dst, size_t rows, size
     const uintptr_t bits = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | row_bytes | spitch | dpitch;
     const char* s = (const char*)src;
     char* d = (char*)dst;
-    if ((bits & 15) == 0) copy2d_kernel<uint4><<<copy_grid(dev, rows * (row_bytes / 16)), 256, 0, dev->stream>>>(s, d, rows, row_bytes / 16, spitch, dpitch);
-    else if ((bits & 3) == 0) copy2d_kernel<uint32_t><<<copy_grid(dev, rows * (row_bytes / 4)), 256, 0, dev->stream>>>(s, d, rows, row_bytes / 4, spitch, dpitch);
-    else if ((bits & 1) == 0) copy2d_kernel<uint16_t><<<copy_grid(dev, rows * (row_bytes / 2)), 256, 0, dev->stream>>>(s, d, rows, row_bytes / 2, spitch, dpitch);
-    else copy2d_kernel<uint8_t><<<copy_grid(dev, rows * row_bytes), 256, 0, dev->stream>>>(s, d, rows, row_bytes, spitch, dpitch);
+    if ((bits & 15) == 0) launch_copy2d<uint4>(dev, s, d, rows, row_bytes / 16, spitch, dpitch);
+    else if ((bits & 7) == 0) launch_copy2d<uint2>(dev, s, d, rows, row_bytes / 8, spitch, dpitch);
+    else if ((bits & 3) == 0) launch_copy2d<uint32_t>(dev, s, d, rows, row_bytes / 4, spitch, dpitch);
+    else if ((bits & 1) == 0) launch_copy2d<uint16_t>(dev, s, d, rows, row_bytes / 2, spitch, dpitch);
+    else launch_copy2d<uint8_t>(dev, s, d, rows, row_bytes, spitch, dpitch);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -51,16 +71,37 @@ struct Remap4 {
     long long off;
 };
 
-template <class E>
-__global__ void __launch_bounds__(256) remap4_kernel(const E* __restrict__ src, E* __restrict__ dst, size_t n, Remap4 p) {
+// U is the unit a thread moves (strides, extents and the offset are in units); I the index type.
+template <class U, class I>
+__global__ void __launch_bounds__(256) remap4_kernel(const U* __restrict__ src, U* __restrict__ dst, size_t n, Remap4 p) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        size_t r = i;
+        I r = (I)i;
         const uint32_t i3 = (uint32_t)(r % p.d[3]); r /= p.d[3];
         const uint32_t i2 = (uint32_t)(r % p.d[2]); r /= p.d[2];
         const uint32_t i1 = (uint32_t)(r % p.d[1]); r /= p.d[1];
         const uint32_t i0 = (uint32_t)r;
         dst[i] = src[p.off + i0 * p.s[0] + i1 * p.s[1] + i2 * p.s[2] + i3 * p.s[3]];
+    }
+}
+
+// Innermost axis broadcast (source stride 0): one element read, V copies stored as one vector.
+template <class E, int V, class I>
+__global__ void __launch_bounds__(256) remap4_fill_kernel(const E* __restrict__ src, E* __restrict__ dst, size_t nvec, Remap4 p) {
+    struct alignas(sizeof(E) * V) VT { E v[V]; };
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const uint32_t row_units = p.d[3] / V;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        I r = (I)i;
+        r /= row_units;
+        const uint32_t i2 = (uint32_t)(r % p.d[2]); r /= p.d[2];
+        const uint32_t i1 = (uint32_t)(r % p.d[1]); r /= p.d[1];
+        const uint32_t i0 = (uint32_t)r;
+        const E e = src[p.off + i0 * p.s[0] + i1 * p.s[1] + i2 * p.s[2]];
+        VT o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.v[j] = e;
+        reinterpret_cast<VT*>(dst)[i] = o;
     }
 }
 
@@ -81,16 +122,94 @@ __global__ void __launch_bounds__(256) transpose_kernel(const E* __restrict__ sr
         if (c0 + j < C && r0 + tx < R) d[(size_t)(c0 + j) * R + r0 + tx] = tile[tx][j];
 }
 
-template <class E>
-rcu_status launch_remap(rcu_device* dev, const void* src, void* dst, size_t n, const Remap4& p) {
-    remap4_kernel<E><<<copy_grid(dev, n), 256, 0, dev->stream>>>((const E*)src, (E*)dst, n, p);
-    RCU_LAUNCH_CHECK(dev);
-    return RCU_OK;
+// 64x64 tile transpose moving element pairs: global loads take two elements of a source row, global
+// stores two elements of a destination row; eight pair loads are in flight per thread.  R and C even,
+// both pointers aligned to a pair.
+template <class E, class P>
+__global__ void __launch_bounds__(256) transpose_pair_kernel(const E* __restrict__ src, E* __restrict__ dst, int R, int C) {
+    constexpr int PITCH = sizeof(E) == 2 ? 66 : 65;
+    __shared__ E tile[64 * PITCH];
+    const size_t b = blockIdx.z;
+    const E* s = src + b * (size_t)R * C;
+    E* d = dst + b * (size_t)R * C;
+    const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+    P in[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int q = threadIdx.x + k * 256, row = q >> 5, pc = q & 31;
+        if (r0 + row < R && c0 + 2 * pc < C) in[k] = *reinterpret_cast<const P*>(s + (size_t)(r0 + row) * C + c0 + 2 * pc);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int q = threadIdx.x + k * 256, row = q >> 5, pc = q & 31;
+        const E* e = reinterpret_cast<const E*>(&in[k]);
+        tile[row * PITCH + 2 * pc] = e[0];
+        tile[row * PITCH + 2 * pc + 1] = e[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int q = threadIdx.x + k * 256, oc = q >> 5, pr = q & 31;
+        if (c0 + oc < C && r0 + 2 * pr < R) {
+            P o;
+            E* e = reinterpret_cast<E*>(&o);
+            e[0] = tile[(2 * pr) * PITCH + oc];
+            e[1] = tile[(2 * pr + 1) * PITCH + oc];
+            *reinterpret_cast<P*>(d + (size_t)(c0 + oc) * R + r0 + 2 * pr) = o;
+        }
+    }
 }
 
+template <class U>
+void launch_remap(rcu_device* dev, const void* src, void* dst, size_t n, const Remap4& p) {
+    if (n <= 0xffffffffull) remap4_kernel<U, uint32_t><<<copy_grid(dev, n), 256, 0, dev->stream>>>((const U*)src, (U*)dst, n, p);
+    else remap4_kernel<U, uint64_t><<<copy_grid(dev, n), 256, 0, dev->stream>>>((const U*)src, (U*)dst, n, p);
+}
+
+template <class E>
+void launch_fill(rcu_device* dev, const void* src, void* dst, size_t nvec, const Remap4& p) {
+    constexpr int V = 16 / sizeof(E);
+    if (nvec <= 0xffffffffull) remap4_fill_kernel<E, V, uint32_t><<<copy_grid(dev, nvec), 256, 0, dev->stream>>>((const E*)src, (E*)dst, nvec, p);
+    else remap4_fill_kernel<E, V, uint64_t><<<copy_grid(dev, nvec), 256, 0, dev->stream>>>((const E*)src, (E*)dst, nvec, p);
+}
+
+// `p` is in elements of `es` bytes.  When the innermost destination axis is contiguous in the source
+// the move is re-expressed in the widest unit (16, 8 or 4 bytes) that divides the innermost extent,
+// every outer stride, the offset and both pointers; a broadcast innermost axis stores whole vectors
+// of one repeated element; anything else moves one element per thread.
 rcu_status remap(rcu_device* dev, int dt, const void* src, void* dst, size_t n, const Remap4& p) {
     if (n == 0) return RCU_OK;
-    return dt_esize(dt) == 2 ? launch_remap<uint16_t>(dev, src, dst, n, p) : launch_remap<uint32_t>(dev, src, dst, n, p);
+    const size_t es = dt_esize(dt);
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst);
+    if (p.s[3] == 1 || p.d[3] == 1) {
+        for (size_t ub = 16; ub > es; ub >>= 1) {
+            const size_t v = ub / es;
+            bool ok = (ptrs & (ub - 1)) == 0 && p.d[3] % v == 0 && p.off % (long long)v == 0 && p.d[3] > 1;
+            for (int i = 0; i < 3 && ok; ++i) ok = p.s[i] % (long long)v == 0;
+            if (!ok) continue;
+            Remap4 q = p;
+            q.d[3] = (uint32_t)(p.d[3] / v);
+            q.off = p.off / (long long)v;
+            for (int i = 0; i < 3; ++i) q.s[i] = p.s[i] / (long long)v;
+            q.s[3] = 1;
+            const size_t nu = n / v;
+            if (ub == 16) launch_remap<uint4>(dev, src, dst, nu, q);
+            else if (ub == 8) launch_remap<uint2>(dev, src, dst, nu, q);
+            else launch_remap<uint32_t>(dev, src, dst, nu, q);
+            RCU_LAUNCH_CHECK(dev);
+            return RCU_OK;
+        }
+    } else if (p.s[3] == 0 && p.d[3] % (16 / es) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        const size_t nvec = n / (16 / es);
+        if (es == 2) launch_fill<uint16_t>(dev, src, dst, nvec, p);
+        else launch_fill<uint32_t>(dev, src, dst, nvec, p);
+        RCU_LAUNCH_CHECK(dev);
+        return RCU_OK;
+    }
+    if (es == 2) launch_remap<uint16_t>(dev, src, dst, n, p);
+    else launch_remap<uint32_t>(dev, src, dst, n, p);
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
 }
 
 inline bool movable_dtype(int dt) { return dt == RCU_F32 || dt == RCU_F16 || dt == RCU_BF16 || dt == RCU_I32 || dt == RCU_U32; }
@@ -145,6 +264,83 @@ gather_q8_kernel(const uint32_t* __restrict__ q, const ScaleT* __restrict__ d, c
     }
 }
 
+// Row gather (dim 0 of a 2-D table): dst row k = src row ids[k], moved in units of U.
+template <class U, class I>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const U* __restrict__ src, const int32_t* __restrict__ ids, U* __restrict__ dst, size_t n_ids, size_t row_units,
+                   size_t src_dim, int* status) {
+    const size_t total = n_ids * row_units;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const I ru = (I)row_units;
+    auto row_of = [&](I k) -> size_t {
+        long long id = ids[k];
+        if (id < 0 || (size_t)id >= src_dim) {   // the WGSL clamps (ops/select.rs:157); also report it
+            atomicOr(status, RCU_DEVFLAG_BOUNDS);
+            id = id < 0 ? 0 : (long long)src_dim - 1;
+        }
+        return (size_t)id;
+    };
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + stride < total; i += 2 * stride) {
+        const I k0 = (I)i / ru, c0 = (I)i - k0 * ru;
+        const I k1 = (I)(i + stride) / ru, c1 = (I)(i + stride) - k1 * ru;
+        const U u0 = src[row_of(k0) * row_units + c0];
+        const U u1 = src[row_of(k1) * row_units + c1];
+        dst[i] = u0;
+        dst[i + stride] = u1;
+    }
+    if (i < total) {
+        const I k = (I)i / ru, c = (I)i - k * ru;
+        dst[i] = src[row_of(k) * row_units + c];
+    }
+}
+
+template <class ScaleT> struct Q8Out;
+template <> struct Q8Out<__half> {
+    __device__ static __forceinline__ void store8(__half* dst, const float* v) {
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = __float2half_rn(v[i]);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+    }
+};
+template <> struct Q8Out<float> {
+    __device__ static __forceinline__ void store8(float* dst, const float* v) {
+        reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+// Q8_0 row gather, 16 values per thread: one 16-byte load of packed int8 (half a 32-block, one
+// scale), 16-byte stores.  Row length % 16 == 0.
+template <class ScaleT>
+__global__ void __launch_bounds__(256)
+gather_q8_rows16_kernel(const uint4* __restrict__ q, const ScaleT* __restrict__ d, const int32_t* __restrict__ ids,
+                        ScaleT* __restrict__ dst, size_t n_ids, uint32_t row16, size_t src_dim, int* status) {
+    const size_t total = n_ids * row16;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t k = i / row16;
+        const uint32_t c = (uint32_t)(i - k * row16);
+        long long id = ids[k];
+        if (id < 0 || (size_t)id >= src_dim) {
+            atomicOr(status, RCU_DEVFLAG_BOUNDS);
+            id = id < 0 ? 0 : (long long)src_dim - 1;
+        }
+        const size_t unit = (size_t)id * row16 + c;           // 16-value unit in the table
+        const uint4 w = q[unit];
+        const float sc = to_f32<ScaleT>(d[unit >> 1]);
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        float v[16];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[a * 4 + j] = rnd<ScaleT>((float)((int)(ws[a] << (8 * (3 - j))) >> 24) * sc);   // quant.rs:121-125
+        Q8Out<ScaleT>::store8(dst + i * 16, v);
+        Q8Out<ScaleT>::store8(dst + i * 16 + 8, v + 8);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -189,6 +385,16 @@ rcu_status rcu_permute(rcu_device* dev, const rcu_tensor* src, const uint32_t* p
     // [.., R, C] -> [.., C, R] with leading axes untouched: tiled transpose
     if (p4[0] == 0 && p4[1] == 1 && p4[2] == 3 && p4[3] == 2 && s4[0] * s4[1] <= 65535 && s4[2] > 1 && s4[3] > 1) {
         const int R = (int)s4[2], C = (int)s4[3];
+        const size_t pair = 2 * dt_esize(src->dt);
+        const bool pairs_ok = R % 2 == 0 && C % 2 == 0 &&
+                              ((reinterpret_cast<uintptr_t>(src->data) | reinterpret_cast<uintptr_t>(dst->data)) & (pair - 1)) == 0;
+        if (pairs_ok && (R + 63) / 64 <= 65535) {
+            dim3 g64((C + 63) / 64, (R + 63) / 64, (unsigned)(s4[0] * s4[1]));
+            if (pair == 4) transpose_pair_kernel<uint16_t, uint32_t><<<g64, 256, 0, dev->stream>>>((const uint16_t*)src->data, (uint16_t*)dst->data, R, C);
+            else transpose_pair_kernel<uint32_t, uint2><<<g64, 256, 0, dev->stream>>>((const uint32_t*)src->data, (uint32_t*)dst->data, R, C);
+            RCU_LAUNCH_CHECK(dev);
+            return RCU_OK;
+        }
         dim3 grid((C + 31) / 32, (R + 31) / 32, (unsigned)(s4[0] * s4[1]));
         if (grid.y <= 65535) {
             if (dt_esize(src->dt) == 2) transpose_kernel<uint16_t><<<grid, 256, 0, dev->stream>>>((const uint16_t*)src->data, (uint16_t*)dst->data, R, C);
@@ -318,6 +524,14 @@ rcu_status rcu_index_select(rcu_device* dev, const rcu_tensor* src, const rcu_te
         RCU_REQUIRE(dev, right % 4 == 0 && right >= 4, "index_select: Q8_0 gather needs dim 0 and a row length divisible by 4");
         const uint32_t* q = (const uint32_t*)src->data;
         const char* d = (const char*)src->data + align256(t_numel(src));
+        if (left == 1 && right % 16 == 0 && (reinterpret_cast<uintptr_t>(dst->data) & 15) == 0 && right / 16 <= 0xffffffffull) {
+            const uint32_t row16 = (uint32_t)(right / 16);
+            const int g16 = copy_grid(dev, n_ids * row16);
+            if (src->dt == RCU_Q8_0F) gather_q8_rows16_kernel<float><<<g16, 256, 0, dev->stream>>>((const uint4*)q, (const float*)d, (const int32_t*)ids->data, (float*)dst->data, n_ids, row16, src_dim, dev->d_status);
+            else gather_q8_rows16_kernel<__half><<<g16, 256, 0, dev->stream>>>((const uint4*)q, (const __half*)d, (const int32_t*)ids->data, (__half*)dst->data, n_ids, row16, src_dim, dev->d_status);
+            RCU_LAUNCH_CHECK(dev);
+            return RCU_OK;
+        }
         const int grid = copy_grid(dev, total / 4);
         if (src->dt == RCU_Q8_0F) gather_q8_kernel<float><<<grid, 256, 0, dev->stream>>>(q, (const float*)d, (const int32_t*)ids->data, (float*)dst->data, left, n_ids, right, src_dim, dev->d_status);
         else gather_q8_kernel<__half><<<grid, 256, 0, dev->stream>>>(q, (const __half*)d, (const int32_t*)ids->data, (__half*)dst->data, left, n_ids, right, src_dim, dev->d_status);
@@ -325,6 +539,23 @@ rcu_status rcu_index_select(rcu_device* dev, const rcu_tensor* src, const rcu_te
         return RCU_OK;
     }
     RCU_REQUIRE(dev, dt_is_float(src->dt), "index_select: unsupported dtype %d", src->dt);
+    if (left == 1) {   // whole rows move: widest unit the row length and the pointers allow
+        const size_t row_bytes = right * dt_esize(src->dt);
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(src->data) | reinterpret_cast<uintptr_t>(dst->data) | row_bytes;
+#define RCU_GATHER_ROWS(U)                                                                                                                \
+        {                                                                                                                                     \
+            const size_t ru = row_bytes / sizeof(U);                                                                                          \
+            const int gr = copy_grid(dev, n_ids * ru / 2 + 1);                                                                                \
+            if (n_ids * ru <= 0xffffffffull) gather_rows_kernel<U, uint32_t><<<gr, 256, 0, dev->stream>>>((const U*)src->data, (const int32_t*)ids->data, (U*)dst->data, n_ids, ru, src_dim, dev->d_status); \
+            else gather_rows_kernel<U, uint64_t><<<gr, 256, 0, dev->stream>>>((const U*)src->data, (const int32_t*)ids->data, (U*)dst->data, n_ids, ru, src_dim, dev->d_status); \
+        }
+        if ((bits & 15) == 0) RCU_GATHER_ROWS(uint4)
+        else if ((bits & 3) == 0) RCU_GATHER_ROWS(uint32_t)
+        else RCU_GATHER_ROWS(uint16_t)
+#undef RCU_GATHER_ROWS
+        RCU_LAUNCH_CHECK(dev);
+        return RCU_OK;
+    }
     const int grid = copy_grid(dev, total);
     if (dt_esize(src->dt) == 2) gather_kernel<uint16_t><<<grid, 256, 0, dev->stream>>>((const uint16_t*)src->data, (const int32_t*)ids->data, (uint16_t*)dst->data, left, n_ids, right, src_dim, dev->d_status);
     else gather_kernel<uint32_t><<<grid, 256, 0, dev->stream>>>((const uint32_t*)src->data, (const int32_t*)ids->data, (uint32_t*)dst->data, left, n_ids, right, src_dim, dev->d_status);

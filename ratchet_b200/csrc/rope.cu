@@ -13,39 +13,76 @@
 
 namespace {
 
-template <class T>
+template <class T, int V> struct alignas(sizeof(T) * V) RopeVec { T v[V]; };
+
+// Thread = V consecutive rotation pairs of one sequence position: the V angles are evaluated once
+// and applied to that position in every (batch, head) slice this thread visits, one vector load per
+// half and one vector store per half each time.  (dim/2) % V == 0 and D % V == 0.
+template <class T, int V>
 __global__ void __launch_bounds__(128)
-rope_kernel(const T* __restrict__ x, T* __restrict__ out, int BH, int S, int D, int dim, float ln_base, int offset) {
+rope_kernel(const T* x, T* out, int BH, int S, int D, int dim, float ln_base, int offset) {
+    typedef RopeVec<T, V> VT;
     const int half = dim >> 1;
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;   // over S * half
-    if (idx < S * half) {
-        const int s = idx / half, i = idx - s * half;
-        const float neg_i = -(float)i;
-        const float e = neg_i * ln_base / (float)half;       // f32 ops, left to right (cpu/rope.rs:38-41)
-        const float inv = (float)exp((double)e);
-        const float th = (float)(s + offset) * inv;
-        double sd, cd;
-        sincos((double)th, &sd, &cd);
-        const float sn = (float)sd, cs = (float)cd;
+    const int hv = half / V;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;   // over S * hv
+    if (idx < S * hv) {
+        const int s = idx / hv, i0 = (idx - s * hv) * V;
+        float sn[V], cs[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const float neg_i = -(float)(i0 + e);
+            const float ex = neg_i * ln_base / (float)half;   // f32 ops, left to right (cpu/rope.rs:38-41)
+            const float inv = (float)exp((double)ex);
+            const float th = (float)(s + offset) * inv;
+            double sd, cd;
+            sincos((double)th, &sd, &cd);
+            sn[e] = (float)sd;
+            cs[e] = (float)cd;
+        }
+#pragma unroll 2
         for (int bh = blockIdx.y; bh < BH; bh += gridDim.y) {
-            const size_t o = ((size_t)bh * S + s) * D;
-            const float x1 = to_f32<T>(x[o + i]), x2 = to_f32<T>(x[o + half + i]);
-            // each product is rounded on its own, as on the CPU (no fma contraction)
-            out[o + i] = from_f32<T>(__fsub_rn(rnd<T>(__fmul_rn(x1, cs)), rnd<T>(__fmul_rn(x2, sn))));
-            out[o + half + i] = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(x1, sn)), rnd<T>(__fmul_rn(x2, cs))));
+            const size_t o = ((size_t)bh * S + s) * D + i0;
+            const VT a = *reinterpret_cast<const VT*>(x + o);
+            const VT b = *reinterpret_cast<const VT*>(x + o + half);
+            VT ra, rb;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float x1 = to_f32<T>(a.v[e]), x2 = to_f32<T>(b.v[e]);
+                // each product is rounded on its own, as on the CPU (no fma contraction)
+                ra.v[e] = from_f32<T>(__fsub_rn(rnd<T>(__fmul_rn(x1, cs[e])), rnd<T>(__fmul_rn(x2, sn[e]))));
+                rb.v[e] = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(x1, sn[e])), rnd<T>(__fmul_rn(x2, cs[e]))));
+            }
+            *reinterpret_cast<VT*>(out + o) = ra;
+            *reinterpret_cast<VT*>(out + o + half) = rb;
         }
     }
     // pass-through tail (only needed when out != x)
     if (dim < D && out != x) {
-        const int tail = D - dim;
-        if (idx < S * tail) {
-            const int s = idx / tail, i = dim + (idx - s * tail);
+        const int tv = (D - dim) / V;
+        if (idx < S * tv) {
+            const int s = idx / tv, i = dim + (idx - s * tv) * V;
             for (int bh = blockIdx.y; bh < BH; bh += gridDim.y) {
                 const size_t o = ((size_t)bh * S + s) * D + i;
-                out[o] = x[o];
+                *reinterpret_cast<VT*>(out + o) = *reinterpret_cast<const VT*>(x + o);
             }
         }
     }
+}
+
+template <class T>
+void launch_rope(rcu_device* dev, const void* x, void* out, int BH, int S, int D, int dim, float ln_base, int offset) {
+    constexpr int VF = 16 / sizeof(T);
+    const int half = dim / 2;
+    const bool vec = half % VF == 0 && D % VF == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int v = vec ? VF : 1;
+    const int per_row = std::max(half, D - dim) / v;
+    const int work = S * per_row;
+    const int gx = (work + 127) / 128;
+    // enough (batch, head) slices per thread to amortise the angle evaluation, enough CTAs to fill the GPU
+    const int want = (dev->sm_count * 16 + gx - 1) / gx;
+    dim3 grid(gx, (unsigned)std::max(1, std::min(BH, want)));
+    if (vec) rope_kernel<T, VF><<<grid, 128, 0, dev->stream>>>((const T*)x, (T*)out, BH, S, D, dim, ln_base, offset);
+    else rope_kernel<T, 1><<<grid, 128, 0, dev->stream>>>((const T*)x, (T*)out, BH, S, D, dim, ln_base, offset);
 }
 
 }  // namespace
@@ -59,14 +96,10 @@ extern "C" rcu_status rcu_rope(rcu_device* dev, const rcu_tensor* x, uint32_t di
     RCU_REQUIRE(dev, dim >= 2 && dim % 2 == 0 && dim <= D, "rope: dim must be even and <= head dim");
     RCU_REQUIRE(dev, S * D <= 0x7fffffffull && B * H <= 0x7fffffffull, "rope: tensor too large");
     DevGuard g(dev->ordinal);
-    const int half = (int)dim / 2;
-    const int per_row = std::max(half, (int)(D - dim));
-    const int work = (int)S * per_row;
-    dim3 grid((work + 127) / 128, (unsigned)std::min<uint64_t>(B * H, 64));
     const float ln_base = logf(base);
     switch (x->dt) {
-        case RCU_F32: rope_kernel<float><<<grid, 128, 0, dev->stream>>>((const float*)x->data, (float*)dst->data, (int)(B * H), (int)S, (int)D, (int)dim, ln_base, (int)offset); break;
-        case RCU_F16: rope_kernel<__half><<<grid, 128, 0, dev->stream>>>((const __half*)x->data, (__half*)dst->data, (int)(B * H), (int)S, (int)D, (int)dim, ln_base, (int)offset); break;
+        case RCU_F32: launch_rope<float>(dev, x->data, dst->data, (int)(B * H), (int)S, (int)D, (int)dim, ln_base, (int)offset); break;
+        case RCU_F16: launch_rope<__half>(dev, x->data, dst->data, (int)(B * H), (int)S, (int)D, (int)dim, ln_base, (int)offset); break;
         default: return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "rope: dtype %d", x->dt);
     }
     RCU_LAUNCH_CHECK(dev);

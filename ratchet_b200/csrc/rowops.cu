@@ -14,9 +14,8 @@
 
 namespace {
 
-constexpr int kMaxPerLane = 32;     // warp-per-row path: N <= 1024
 constexpr int kCtaThreads = 256;
-constexpr int kMaxPerThread = 32;   // CTA-per-row path keeps N <= 8192 in registers
+constexpr int kPer = 4;             // 16-byte vectors a thread keeps in registers
 
 struct SumOp { __device__ static float id() { return 0.f; } __device__ static float f(float a, float b) { return a + b; } };
 struct MaxOp { __device__ static float id() { return -INFINITY; } __device__ static float f(float a, float b) { return fmaxf(a, b); } };
@@ -38,79 +37,129 @@ template <class Op> __device__ __forceinline__ float cta_reduce(float v, float* 
     return warp_reduce<Op>(r);
 }
 
+// Reduce two values across each group of G consecutive threads (G = 32: shuffles only; G > 32: one
+// shared-memory hop across the group's warps).  Every thread of the CTA must call it.
+template <class Op, int G> __device__ __forceinline__ void group_reduce2(float& a, float& b, float (*scratch)[32]) {
+    a = warp_reduce<Op>(a);
+    b = warp_reduce<Op>(b);
+    if (G > 32) {
+        constexpr int WPG = G / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();
+        if (lane == 0) { scratch[0][warp] = a; scratch[1][warp] = b; }
+        __syncthreads();
+        const int first = (warp / WPG) * WPG;
+        a = lane < WPG ? scratch[0][first + lane] : Op::id();
+        b = lane < WPG ? scratch[1][first + lane] : Op::id();
+        a = warp_reduce<Op>(a);
+        b = warp_reduce<Op>(b);
+    }
+}
+
 enum { MODE_LN = 0, MODE_RMS = 1, MODE_SOFTMAX = 2 };
 
-// One row per "group" of threads. WARP=true: group = warp (blockDim = 32 x rows_per_cta);
-// WARP=false: group = whole CTA.
-template <class T, int MODE, bool WARP, int PER>
-__global__ void __launch_bounds__(kCtaThreads)
+template <class T, int V> struct alignas(sizeof(T) * V) RowVec { T v[V]; };
+
+// One row per group of G threads (a CTA holds max(256, G) / G rows).  Thread t of the group owns
+// vectors t, t + G, ... (up to kPer of them, V elements each; N % V == 0): the row is read from
+// HBM once with all of a thread's loads in flight together, kept in registers as f32, and written
+// once.  16-bit types round to their own precision after every operation, as the CPU device does.
+template <class T, int MODE, int G, int V>
+__global__ void __launch_bounds__(G > kCtaThreads ? G : kCtaThreads)
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
            size_t rows, int N, float eps) {
-    __shared__ float scratch[32];
-    const int gsize = WARP ? 32 : blockDim.x;
-    const int gid = WARP ? (threadIdx.x & 31) : threadIdx.x;
-    const size_t groups_per_cta = WARP ? (blockDim.x >> 5) : 1;
-    const size_t gidx = WARP ? (threadIdx.x >> 5) : 0;
-    for (size_t row = (size_t)blockIdx.x * groups_per_cta + gidx; row < rows; row += (size_t)gridDim.x * groups_per_cta) {
-        // WARP=false: all threads of the CTA iterate together (row depends only on blockIdx)
-        const T* xr = x + row * (size_t)N;
-        T* orow = out + row * (size_t)N;
-        float v[PER];
+    typedef RowVec<T, V> VT;
+    constexpr int CTA = G > kCtaThreads ? G : kCtaThreads;
+    constexpr int GROUPS = CTA / G;
+    __shared__ float scratch[2][32];
+    const int g = threadIdx.x / G, t = threadIdx.x % G;
+    const int nvec = N / V;
+    for (size_t base = (size_t)blockIdx.x * GROUPS; base < rows; base += (size_t)gridDim.x * GROUPS) {
+        const size_t row = base + g;
+        const bool valid = row < rows;           // the loop bound is uniform across the CTA (barriers inside)
+        const VT* xr = reinterpret_cast<const VT*>(x + row * (size_t)N);
+        VT* orow = reinterpret_cast<VT*>(out + row * (size_t)N);
+        VT raw[kPer];
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int j = t + i * G;
+            if (valid && j < nvec) raw[i] = xr[j];
+        }
+        float v[kPer][V];
         float s = 0.f, s2 = 0.f, mx = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int j = gid + i * gsize;
-            if (j < N) {
-                v[i] = to_f32<T>(xr[j]);
-                if (MODE == MODE_SOFTMAX) mx = fmaxf(mx, v[i]);
-                else { s += v[i]; s2 += rnd<T>(v[i] * v[i]); }
+        for (int i = 0; i < kPer; ++i) {
+            const int j = t + i * G;
+            if (valid && j < nvec) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    v[i][e] = to_f32<T>(raw[i].v[e]);
+                    if (MODE == MODE_SOFTMAX) mx = fmaxf(mx, v[i][e]);
+                    else { s += v[i][e]; s2 += rnd<T>(v[i][e] * v[i][e]); }
+                }
             } else {
-                v[i] = 0.f;
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[i][e] = 0.f;
             }
         }
         if (MODE == MODE_SOFTMAX) {
-            mx = WARP ? warp_reduce<MaxOp>(mx) : cta_reduce<MaxOp>(mx, scratch);
-            float sum = 0.f;
+            float dummy = -INFINITY;
+            group_reduce2<MaxOp, G>(mx, dummy, scratch);
+            float sum = 0.f, zero = 0.f;
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int j = gid + i * gsize;
-                if (j < N) { v[i] = rnd<T>(expf(v[i] - mx)); sum += v[i]; }
+            for (int i = 0; i < kPer; ++i) {
+                const int j = t + i * G;
+                if (valid && j < nvec) {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) { v[i][e] = rnd<T>(sizeof(T) == 2 ? __expf(v[i][e] - mx) : expf(v[i][e] - mx)); sum += v[i][e]; }
+                }
             }
-            sum = WARP ? warp_reduce<SumOp>(sum) : cta_reduce<SumOp>(sum, scratch);
+            group_reduce2<SumOp, G>(sum, zero, scratch);
             sum = rnd<T>(sum);
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const int j = gid + i * gsize;
-                if (j < N) orow[j] = from_f32<T>(v[i] / sum);
+            for (int i = 0; i < kPer; ++i) {
+                const int j = t + i * G;
+                if (valid && j < nvec) {
+                    VT o;
+#pragma unroll
+                    for (int e = 0; e < V; ++e) o.v[e] = from_f32<T>(sizeof(T) == 2 ? __fdividef(v[i][e], sum) : v[i][e] / sum);
+                    orow[j] = o;
+                }
             }
         } else {
             const float nf = rnd<T>((float)N);
-            const float e = rnd<T>(eps);
+            const float e_ = rnd<T>(eps);
+            group_reduce2<SumOp, G>(s, s2, scratch);
+            float mu = 0.f, rstd;
             if (MODE == MODE_LN) {
-                s = WARP ? warp_reduce<SumOp>(s) : cta_reduce<SumOp>(s, scratch);
-                s2 = WARP ? warp_reduce<SumOp>(s2) : cta_reduce<SumOp>(s2, scratch);
-                const float mu = rnd<T>(rnd<T>(s) / nf);
+                mu = rnd<T>(rnd<T>(s) / nf);
                 const float ex2 = rnd<T>(rnd<T>(s2) / nf);
                 const float var = rnd<T>(ex2 - rnd<T>(mu * mu));
-                const float rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(var + e))));
-#pragma unroll
-                for (int i = 0; i < PER; ++i) {
-                    const int j = gid + i * gsize;
-                    if (j < N) {
-                        float y = rnd<T>(rnd<T>(v[i] - mu) * rstd);
-                        y = rnd<T>(y * to_f32<T>(gamma[j]));
-                        if (beta) y = rnd<T>(y + to_f32<T>(beta[j]));
-                        orow[j] = from_f32<T>(y);
-                    }
-                }
+                rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(var + e_))));
             } else {
-                s2 = WARP ? warp_reduce<SumOp>(s2) : cta_reduce<SumOp>(s2, scratch);
                 const float ms = rnd<T>(rnd<T>(s2) / nf);
-                const float rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(ms + e))));
+                rstd = rnd<T>(1.0f / rnd<T>(sqrtf(rnd<T>(ms + e_))));
+            }
 #pragma unroll
-                for (int i = 0; i < PER; ++i) {
-                    const int j = gid + i * gsize;
-                    if (j < N) orow[j] = from_f32<T>(rnd<T>(rnd<T>(v[i] * rstd) * to_f32<T>(gamma[j])));
+            for (int i = 0; i < kPer; ++i) {
+                const int j = t + i * G;
+                if (valid && j < nvec) {
+                    const VT gm = reinterpret_cast<const VT*>(gamma)[j];
+                    VT bt, o;
+                    if (MODE == MODE_LN && beta) bt = reinterpret_cast<const VT*>(beta)[j];
+#pragma unroll
+                    for (int e = 0; e < V; ++e) {
+                        float y;
+                        if (MODE == MODE_LN) {
+                            y = rnd<T>(rnd<T>(v[i][e] - mu) * rstd);
+                            y = rnd<T>(y * to_f32<T>(gm.v[e]));
+                            if (beta) y = rnd<T>(y + to_f32<T>(bt.v[e]));
+                        } else {
+                            y = rnd<T>(rnd<T>(v[i][e] * rstd) * to_f32<T>(gm.v[e]));
+                        }
+                        o.v[e] = from_f32<T>(y);
+                    }
+                    orow[j] = o;
                 }
             }
         }
@@ -155,30 +204,38 @@ row_kernel_long(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     }
 }
 
+template <class T, int MODE, int V>
+rcu_status launch_rows_v(rcu_device* dev, const T* xp, const T* gp, const T* bp, T* op, size_t rows, int N, float eps) {
+    const int nvec = N / V;
+    const size_t cap = (size_t)dev->sm_count * 8;
+#define RCU_ROW(G)                                                                                         \
+    {                                                                                                      \
+        constexpr int cta = G > kCtaThreads ? G : kCtaThreads;                                             \
+        const size_t groups = cta / G;                                                                     \
+        const int grid = (int)std::min<size_t>((rows + groups - 1) / groups, cap);                         \
+        row_kernel<T, MODE, G, V><<<grid, cta, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);            \
+    }
+    if (nvec <= 32 * kPer) RCU_ROW(32)
+    else if (nvec <= 128 * kPer) RCU_ROW(128)
+    else if (nvec <= 256 * kPer) RCU_ROW(256)
+    else RCU_ROW(1024)
+#undef RCU_ROW
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
 template <class T, int MODE>
 rcu_status launch_rows(rcu_device* dev, const void* x, const void* gamma, const void* beta, void* out, size_t rows, int N, float eps) {
     const T* xp = (const T*)x; const T* gp = (const T*)gamma; const T* bp = (const T*)beta; T* op = (T*)out;
-    const int cap = dev->sm_count * 8;
-    if (N <= 32 * kMaxPerLane) {
-        const int warps = 8;
-        const int grid = (int)std::min<size_t>((rows + warps - 1) / warps, (size_t)cap);
-#define RCU_ROW_WARP(P) row_kernel<T, MODE, true, P><<<grid, warps * 32, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps)
-        if (N <= 32 * 4) RCU_ROW_WARP(4);
-        else if (N <= 32 * 8) RCU_ROW_WARP(8);
-        else if (N <= 32 * 16) RCU_ROW_WARP(16);
-        else RCU_ROW_WARP(32);
-#undef RCU_ROW_WARP
-    } else if (N <= kCtaThreads * kMaxPerThread) {
-        const int grid = (int)std::min<size_t>(rows, (size_t)cap);
-#define RCU_ROW_CTA(P) row_kernel<T, MODE, false, P><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps)
-        if (N <= kCtaThreads * 8) RCU_ROW_CTA(8);
-        else if (N <= kCtaThreads * 16) RCU_ROW_CTA(16);
-        else RCU_ROW_CTA(32);
-#undef RCU_ROW_CTA
-    } else {
-        const int grid = (int)std::min<size_t>(rows, (size_t)cap);
-        row_kernel_long<T, MODE><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);
-    }
+    constexpr int VFULL = 16 / sizeof(T), VHALF = 8 / sizeof(T);
+    const uintptr_t ptr_bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                               reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta);
+    auto fits = [&](int v) { return N % v == 0 && (ptr_bits & ((uintptr_t)v * sizeof(T) - 1)) == 0 && N / v <= 1024 * kPer; };
+    if (fits(VFULL)) return launch_rows_v<T, MODE, VFULL>(dev, xp, gp, bp, op, rows, N, eps);
+    if (fits(VHALF)) return launch_rows_v<T, MODE, VHALF>(dev, xp, gp, bp, op, rows, N, eps);
+    if (fits(1)) return launch_rows_v<T, MODE, 1>(dev, xp, gp, bp, op, rows, N, eps);
+    const int grid = (int)std::min<size_t>(rows, (size_t)dev->sm_count * 8);
+    row_kernel_long<T, MODE><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -219,16 +276,34 @@ group_norm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T*
     }
 }
 
-template <class T, int KIND>
+// Warp per row; V elements per load (N % V == 0), four loads in flight per lane.
+template <class T, int KIND, int V>
 __global__ void __launch_bounds__(256) reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int N) {
+    typedef RowVec<T, V> VT;
     const int lane = threadIdx.x & 31;
     const size_t wpc = blockDim.x >> 5;
+    const int nvec = N / V;
     for (size_t row = (size_t)blockIdx.x * wpc + (threadIdx.x >> 5); row < rows; row += (size_t)gridDim.x * wpc) {
-        const T* xr = x + row * (size_t)N;
+        const VT* xr = reinterpret_cast<const VT*>(x + row * (size_t)N);
         float acc = KIND == RCU_REDUCE_MAX ? -INFINITY : 0.f;
-        for (int j = lane; j < N; j += 32) {
-            const float v = to_f32<T>(xr[j]);
-            acc = KIND == RCU_REDUCE_MAX ? fmaxf(acc, v) : acc + v;
+        for (int j0 = 0; j0 < nvec; j0 += 128) {
+            VT raw[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u * 32 + lane;
+                if (j < nvec) raw[u] = xr[j];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u * 32 + lane;
+                if (j < nvec) {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) {
+                        const float v = to_f32<T>(raw[u].v[e]);
+                        acc = KIND == RCU_REDUCE_MAX ? fmaxf(acc, v) : acc + v;
+                    }
+                }
+            }
         }
         acc = KIND == RCU_REDUCE_MAX ? warp_reduce<MaxOp>(acc) : warp_reduce<SumOp>(acc);
         if (KIND == RCU_REDUCE_MEAN) acc = rnd<T>(acc) / rnd<T>((float)N);   // cpu/norm.rs:72-89
@@ -291,7 +366,10 @@ rcu_status rcu_reduce(rcu_device* dev, int kind, const rcu_tensor* x, rcu_tensor
     RCU_REQUIRE(dev, kind >= RCU_REDUCE_SUM && kind <= RCU_REDUCE_MEAN, "reduce: unknown kind %d", kind);
     DevGuard g(dev->ordinal);
     const int grid = (int)std::min<size_t>((rows + 7) / 8, (size_t)dev->sm_count * 8);
-#define RCU_RED(T, K) reduce_rows_kernel<T, K><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (T*)dst->data, rows, (int)N)
+    const bool vec = N % 8 == 0 && (reinterpret_cast<uintptr_t>(x->data) & 15) == 0;   // 16-byte loads for 2- and 4-byte types
+#define RCU_RED(T, K)                                                                                                        \
+    if (vec) reduce_rows_kernel<T, K, 16 / sizeof(T)><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (T*)dst->data, rows, (int)N); \
+    else reduce_rows_kernel<T, K, 1><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (T*)dst->data, rows, (int)N)
 #define RCU_RED_T(T)                                       \
     switch (kind) {                                        \
         case RCU_REDUCE_SUM: RCU_RED(T, RCU_REDUCE_SUM); break; \
