@@ -227,6 +227,7 @@ void rcu_last_resolve_stats(rcu_device* dev, rcu_resolve_stats* out);
  * Weights are ratchet Q8_0 buffers (Q8_0H or Q8_0F), activations f16, norm scales f32, KV caches
  * f16 [n_kv_heads, max_cache, head_dim] per layer as ratchet-nn allocates them (kv_cache.rs:11-18).
  * All pointers are device memory owned by the caller and must outlive the decoder. */
+typedef struct rcu_comm rcu_comm;       /* exchange window between the GPUs of a node (declared with rcu_comm_* below) */
 typedef struct rcu_decoder rcu_decoder;
 typedef struct {
     uint32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn, vocab, max_cache, rope_dim;
@@ -246,6 +247,18 @@ typedef struct {
 rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers,
                               const void* tok_embd /* Q8_0 [vocab, d_model] */, const void* out_norm /* f32 [d_model] */,
                               const void* lm_head /* Q8_0 [vocab, d_model] */, rcu_decoder** out);
+/* The same decoder sharded over the GPUs of one node, one process per GPU (no counterpart in the
+ * reference, which drives one device).  `cfg` describes the WHOLE model; rank r of a world of g
+ * passes its own shards: qkv = the q, k and v rows of heads [r H/g, (r+1) H/g) (q rows, then k, then v),
+ * o / down = rows [r d/g, (r+1) d/g), gate_up = gate rows then up rows of ffn columns
+ * [r f/g, (r+1) f/g), lm_head = rows [r V/g, (r+1) V/g), KV caches for its own kv heads; norms and
+ * the embedding table are whole.  `comm` must be a fresh window (rcu_comm_create + every peer
+ * imported) with slots of at least 2 * max(d_model, ffn, vocab, n_heads * head_dim) bytes; the decoder
+ * owns its flags from here on.  All ranks must call rcu_decoder_step with the same token, in step;
+ * logits and arg-max are complete and identical on every rank.  A peer that stops answering ends
+ * each wait after two seconds; the next rcu_sync then returns RCU_ERR_TIMEOUT. */
+rcu_status rcu_decoder_create_sharded(rcu_device* dev, rcu_comm* comm, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers,
+                                      const void* tok_embd, const void* out_norm, const void* lm_head, rcu_decoder** out);
 void rcu_decoder_destroy(rcu_decoder* dec);
 /* Number of KV entries already in the caches = position of the next token (KVCache::entries). */
 rcu_status rcu_decoder_set_position(rcu_decoder* dec, uint32_t position);
@@ -290,7 +303,6 @@ rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, void* k_cach
  * CTA stores the output slice into every peer's window over NVLink and raises their flags, then this
  * rank waits (bounded: RCU_ERR_TIMEOUT at the next sync) for its peers' slices.  *y_full is the
  * device pointer of the gathered f16 [N] output, valid until the call after next. */
-typedef struct rcu_comm rcu_comm;
 rcu_status rcu_comm_create(rcu_device* dev, int rank, int world, uint64_t slot_bytes, rcu_comm** out);
 rcu_status rcu_comm_export(rcu_comm* comm, void* handle64);
 rcu_status rcu_comm_import(rcu_comm* comm, int peer, const void* handle64);

@@ -135,6 +135,8 @@ SIGNATURES = {
     # fused decode step
     "rcu_decoder_create": (C.c_int, [_DEV, C.POINTER(rcu_decoder_config), C.POINTER(rcu_decoder_layer), C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.POINTER(C.c_void_p)]),
+    "rcu_decoder_create_sharded": (C.c_int, [_DEV, C.c_void_p, C.POINTER(rcu_decoder_config), C.POINTER(rcu_decoder_layer), C.c_void_p,
+                                             C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
     "rcu_decoder_destroy": (None, [C.c_void_p]),
     "rcu_decoder_set_position": (C.c_int, [C.c_void_p, C.c_uint32]),
     "rcu_decoder_position": (C.c_uint32, [C.c_void_p]),

@@ -53,6 +53,56 @@ def shard_q8(buf: np.ndarray, dt: int, n_rows: int, k: int, rank: int, world: in
     return out
 
 
+def take_rows_q8(buf: np.ndarray, dt: int, n_rows: int, k: int, ranges: Sequence[Tuple[int, int]]) -> np.ndarray:
+    """Rows [a, b) for each (a, b) of `ranges`, in that order, of a ratchet Q8_0 buffer W[n_rows, k], as a
+    ratchet buffer of their own.  shard_q8 is the single-range case."""
+    if dt not in (capi.Q8_0F, capi.Q8_0H):
+        raise ValueError("take_rows_q8 takes Q8_0F / Q8_0H buffers")
+    if k % 32:
+        raise ValueError("k must hold whole 32-element blocks")
+    fp = 4 if dt == capi.Q8_0F else 2
+    raw = np.ascontiguousarray(buf).view(np.uint8).reshape(-1)
+    d_off = _align256(n_rows * k)
+    per_row = (k // 32) * fp
+    for a, b in ranges:
+        if not 0 <= a <= b <= n_rows:
+            raise ValueError(f"rows [{a}, {b}) outside [0, {n_rows})")
+    rows = sum(b - a for a, b in ranges)
+    out = np.zeros(_align256(rows * k) + _align256(rows * per_row), np.uint8)
+    q_at, d_at = 0, _align256(rows * k)
+    for a, b in ranges:
+        n = b - a
+        out[q_at: q_at + n * k] = raw[a * k: b * k]
+        out[d_at: d_at + n * per_row] = raw[d_off + a * per_row: d_off + b * per_row]
+        q_at += n * k
+        d_at += n * per_row
+    return out
+
+
+def decoder_shard_ranges(n_heads: int, n_kv_heads: int, head_dim: int, d_model: int, ffn: int, vocab: int, rank: int,
+                         world: int) -> dict:
+    """Row ranges of each Linear that rank `rank` of `world` owns in the sharded decode step
+    (rcu_decoder_create_sharded): attention is split by heads (q, k and v rows of the rank's heads),
+    the gated MLP by ffn columns (gate rows then up rows of the rank's columns), every other Linear and
+    the logits by contiguous output rows."""
+    for name, n in (("n_heads", n_heads), ("n_kv_heads", n_kv_heads), ("d_model", d_model), ("ffn", ffn), ("vocab", vocab)):
+        if n % world:
+            raise ValueError(f"{name} = {n} does not split over {world} ranks")
+    hq, hk = n_heads // world, n_kv_heads // world
+    q0 = rank * hq * head_dim
+    k0 = n_heads * head_dim + rank * hk * head_dim
+    v0 = (n_heads + n_kv_heads) * head_dim + rank * hk * head_dim
+    f0, f1 = shard_rows(ffn, rank, world)
+    return {
+        "qkv": [(q0, q0 + hq * head_dim), (k0, k0 + hk * head_dim), (v0, v0 + hk * head_dim)],
+        "o": [shard_rows(d_model, rank, world)],
+        "gate_up": [(f0, f1), (ffn + f0, ffn + f1)],
+        "down": [shard_rows(d_model, rank, world)],
+        "lm_head": [shard_rows(vocab, rank, world)],
+        "kv_heads": shard_rows(n_kv_heads, rank, world),
+    }
+
+
 def exchange_handles(local: bytes, rank: int, world: int, group=None) -> List[bytes]:
     """All-gather of the 64-byte IPC handles through torch.distributed (any backend)."""
     import torch.distributed as dist

@@ -7,26 +7,19 @@
 // Q8_0 blocks run along K inside a row, so rank r owns rows [r N/g, (r+1) N/g) as its own ratchet
 // buffer and the only exchange is the gather of the output slices.
 //
-// One process per GPU.  Each rank allocates one "window": two full-size output slots (double
-// buffered by step parity) followed by two flag arrays of `world` words and a ticket.  Windows are
-// exported as CUDA IPC handles, exchanged by the host framework, and opened by every peer.  Data
-// moves with plain peer stores issued by the producing GPU into the consumer's own HBM (all later
-// reads are local); completion is a system-scope release store of the step number into the
-// consumer's flag word, which the consumer acquires with a bounded spin.  No TMA, no multicast.
-#include "gemv_q8.cuh"
+// One process per GPU.  Each rank allocates one "window" (comm.cuh): full-size output slots (this
+// entry point alternates between the first two by step parity) followed by a flag array of `world`
+// words per slot and the ticket words.  Windows are exported as CUDA IPC handles, exchanged by the
+// host framework, and opened by every peer.  Data moves with plain peer stores issued by the producing
+// GPU into the consumer's own HBM (all later reads are local); completion is a system-scope release
+// store of the step number into the consumer's flag word, which the consumer acquires with a bounded
+// spin.  No TMA, no multicast.
+#include "comm.cuh"
 
 namespace {
-constexpr int kSlots = 2;
+using rcu_window::Window;
+using rcu_window::kSlots;
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;   // 2 s per wait, then RCU_DEVFLAG_TIMEOUT
-
-struct Window {
-    char* base = nullptr;
-    size_t slot_bytes = 0;
-    char* slot(int s) const { return base + (size_t)s * slot_bytes; }
-    unsigned int* flags(int s, int world) const { return reinterpret_cast<unsigned int*>(base + kSlots * slot_bytes) + (size_t)s * world; }
-    unsigned int* ticket(int world) const { return flags(kSlots, world); }
-    static size_t bytes(size_t slot_bytes, int world) { return kSlots * slot_bytes + (size_t)(kSlots * world + 4) * sizeof(unsigned int); }
-};
 
 // lane p waits until peer p's flag for this slot reaches seq
 __global__ void wait_flags_kernel(const unsigned int* flags, int world, int self, unsigned int seq, int* status) {
@@ -48,15 +41,6 @@ __global__ void wait_flags_kernel(const unsigned int* flags, int world, int self
     }
 }
 }  // namespace
-
-struct rcu_comm {
-    rcu_device* dev = nullptr;
-    int rank = 0, world = 1;
-    Window local;
-    Window peers[gemvq8::kMaxPeers];   // peers[rank] == local
-    bool opened[gemvq8::kMaxPeers] = {};
-    unsigned int seq = 0;
-};
 
 extern "C" {
 
@@ -132,6 +116,7 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
     for (int p = 0; p < c->world; ++p)
         RCU_REQUIRE(dev, p == c->rank || c->opened[p], "gemv_allgather: peer %d has not been imported", p);
     DevGuard g(dev->ordinal);
+    RCU_REQUIRE(dev, !c->bound, "gemv_allgather: this window belongs to a sharded decoder");
     const unsigned int seq = ++c->seq;
     const int slot = (int)(seq & 1u);
     gemvq8::PushEpilogueH epi;

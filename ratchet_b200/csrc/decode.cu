@@ -17,6 +17,7 @@
 #include <cmath>
 #include <cstdlib>
 
+#include "comm.cuh"
 #include "gemv_q8_bulk.cuh"
 
 namespace {
@@ -35,6 +36,7 @@ struct AttnParams {
     float* partial;                // [H][kSplits][HD + 2]: m, l, unnormalised o
     unsigned int* counters;        // [H], zero between launches
     __half* out;                   // [H * HD]
+    gemvq8::PushInfo push;         // slice_elems > 0: the CTA that completes the last head sends `out` to the peers
 };
 
 __device__ __forceinline__ float f16r(float v) { return __half2float(__float2half_rn(v)); }
@@ -219,6 +221,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
         p.out[(size_t)h * HD + d] = __float2half_rn(o / L);
     }
     if (tid == 0) p.counters[h] = 0;                 // ready for the next launch
+    if (p.push.slice_elems > 0) p.push.run();         // sharded decoder: heads of this rank -> every peer
 }
 
 __global__ void set_u32_kernel(uint32_t* p, uint32_t v);
@@ -261,9 +264,44 @@ rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool 
 
 __global__ void set_u32_kernel(uint32_t* p, uint32_t v) { *p = v; }
 
+__device__ __forceinline__ void argmax_advance_body(const __half* logits, int n, int32_t* out, uint32_t* d_pos);
+
 // arg-max over f16 logits (first maximum wins, as the host loop in phi3/generate.rs:103-108) and
 // position advance (KVCache::update(1)).
 __global__ void __launch_bounds__(1024) argmax_advance_kernel(const __half* logits, int n, int32_t* out, uint32_t* d_pos) {
+    argmax_advance_body(logits, n, out, d_pos);
+}
+
+// The sharded decoder's last kernel: waits for every rank's slice of the logits, copies the gathered
+// vector to the caller's buffer, takes the arg-max and advances the position and the step counter.
+__global__ void __launch_bounds__(1024) argmax_advance_gathered_kernel(gemvq8::WaitInfo w, const __half* gathered, __half* logits_out,
+                                                                        int n, int32_t* out, uint32_t* d_pos, unsigned int* d_step) {
+    if (w.flags != nullptr) {
+        const int p = threadIdx.x;
+        if (p < w.world && p != w.self) {
+            const unsigned int seq = __ldcg(w.step) * w.per_step + w.idx + 1u;
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w.flags + p) : "memory");
+                if ((int)(v - seq) >= 0) break;
+                if (*reinterpret_cast<volatile int*>(w.status) & RCU_DEVFLAG_TIMEOUT) break;
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                if (t - t0 > 2000000000ull) { atomicOr(w.status, RCU_DEVFLAG_TIMEOUT); break; }
+            }
+        }
+        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < n / 8; i += blockDim.x)
+        reinterpret_cast<uint4*>(logits_out)[i] = __ldcg(reinterpret_cast<const uint4*>(gathered) + i);
+    __syncthreads();
+    argmax_advance_body(logits_out, n, out, d_pos);
+    if (threadIdx.x == 0) *d_step += 1;
+}
+
+__device__ __forceinline__ void argmax_advance_body(const __half* logits, int n, int32_t* out, uint32_t* d_pos) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     if (out) {
@@ -373,6 +411,9 @@ struct rcu_decoder {
     uint32_t position = 0;
     uint32_t kernels_per_step = 0;
     uint64_t steps = 0;
+    // sharded across the GPUs of a node (null: single GPU).  cfg holds the whole model's sizes.
+    rcu_comm* comm = nullptr;
+    unsigned int* d_step = nullptr;       // steps taken, on the device: the exchanges' sequence numbers derive from it
     // captured step
     cudaGraphExec_t graph_exec = nullptr;
     const int32_t* cap_token = nullptr;
@@ -428,6 +469,123 @@ rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_d
     return RCU_OK;
 }
 
+// One decode step with every Linear sharded by output rows over the ranks of `d->comm` and each
+// output all-gathered by the kernel that produces it (gemvq8::PushWrap / the attention kernel's push),
+// consumed after a bounded flag wait in the next kernel's prologue (gemvq8::WaitWrap):
+//   qkv rows of this rank's heads -> attention on those heads (its own slice of the KV cache)
+//     -> gather of the head outputs      [slot 1, exchange 2 li]
+//   o rows + residual   -> gather of x   [slot 0, exchange 2 li]
+//   gate/up rows + SiLU -> gather of act [slot 1, exchange 2 li + 1]
+//   down rows + residual-> gather of x   [slot 0, exchange 2 li + 1]
+//   lm_head rows        -> gather of logits [slot 2, one exchange per step]
+// Every output element is computed by one rank with the arithmetic of the single-GPU step, so the
+// gathered vectors are bit-identical to it.  Slot 0 always holds x: a rank updates its own rows in
+// place and peers overwrite only theirs; a slot is rewritten by a peer only after an exchange that
+// the reader of the previous contents has already signalled.
+rcu_status run_sequence_sharded(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev) {
+    rcu_device* dev = d->dev;
+    rcu_comm* cm = d->comm;
+    const rcu_decoder_config& c = d->cfg;
+    const int W = cm->world, r = cm->rank;
+    const int D = (int)c.d_model, HD = (int)c.head_dim, L = (int)c.n_layers;
+    const int H = (int)c.n_heads, Hl = H / W, Hkvl = (int)c.n_kv_heads / W;
+    const int qkv_nl = (Hl + 2 * Hkvl) * HD, Dl = D / W, ffn = (int)c.ffn, ffnl = ffn / W, Vl = (int)c.vocab / W;
+    __half* slotX = reinterpret_cast<__half*>(cm->local.slot(0));
+    __half* slotA = reinterpret_cast<__half*>(cm->local.slot(1));
+    __half* slotL = reinterpret_cast<__half*>(cm->local.slot(2));
+    auto make_push = [&](int slot, size_t elem_off, int elems, unsigned per_step, unsigned idx, int n_ctas, int ticket) {
+        gemvq8::PushInfo p{};
+        p.y_local = reinterpret_cast<__half*>(cm->local.slot(slot)) + elem_off;
+        p.slice_elems = elems;
+        p.ticket = cm->local.ticket(W, ticket);
+        p.n_peers = 0;
+        for (int q = 0; q < W; ++q) {
+            if (q == r) continue;
+            p.peer_dst[p.n_peers] = reinterpret_cast<__half*>(cm->peers[q].slot(slot)) + elem_off;
+            p.peer_flag[p.n_peers] = cm->peers[q].flags(slot, W) + r;
+            p.n_peers++;
+        }
+        p.step = d->d_step;
+        p.per_step = per_step;
+        p.idx = idx;
+        p.n_ctas = n_ctas;
+        return p;
+    };
+    auto make_wait = [&](int slot, unsigned per_step, unsigned idx) {
+        gemvq8::WaitInfo w{};
+        w.flags = cm->local.flags(slot, W);
+        w.world = W;
+        w.self = r;
+        w.step = d->d_step;
+        w.per_step = per_step;
+        w.idx = idx;
+        w.status = dev->d_status;
+        return w;
+    };
+    const unsigned perX = 2u * L, perA = 2u * L;
+    rope_table_kernel<<<1, 128, 0, dev->stream>>>(d->scratch.d_pos, logf(c.rope_base), (int)c.rope_dim / 2, d->scratch.rope_tab);
+    RCU_LAUNCH_CHECK(dev);
+    // embedding: every rank holds the table and gathers the same row into its own x
+    rcu_tensor table{c.weight_dt, 2, {c.vocab, c.d_model, 1, 1}, const_cast<void*>(d->tok_embd)};
+    rcu_tensor ids{RCU_I32, 1, {1, 1, 1, 1}, const_cast<int32_t*>(token_dev)};
+    rcu_tensor xrow{RCU_F16, 2, {1, c.d_model, 1, 1}, slotX};
+    rcu_status st;
+    if (c.weight_dt == RCU_Q8_0H) {
+        st = rcu_index_select(dev, &table, &ids, 0, &xrow);
+    } else {
+        rcu_tensor x32{RCU_F32, 2, {1, c.d_model, 1, 1}, d->act};
+        st = rcu_index_select(dev, &table, &ids, 0, &x32);
+        if (st == RCU_OK) st = rcu_cast(dev, &x32, &xrow);
+    }
+    if (st != RCU_OK) return st;
+    for (int li = 0; li < L; ++li) {
+        const rcu_decoder_layer& Lw = d->layers[li];
+        gemvq8::WaitInfo wx_prev{};   // x of the previous layer's down projection (layer 0 reads the embedding: no wait)
+        if (li > 0) wx_prev = make_wait(0, perX, 2u * (li - 1) + 1u);
+        st = gemv(dev, c.weight_dt, Lw.qkv,
+                  gemvq8::WaitWrap<gemvq8::RmsNormPrologueH>{{slotX, (const float*)Lw.attn_norm, c.rms_eps}, wx_prev},
+                  gemvq8::PlainEpilogue<__half>{nullptr, d->qkv}, qkv_nl, D);
+        if (st != RCU_OK) return st;
+        AttnParams ap{d->qkv, (__half*)Lw.k_cache, (__half*)Lw.v_cache, Hl, Hkvl, (int)c.max_cache, (int)c.rope_dim,
+                      d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters,
+                      slotA + (size_t)r * Hl * HD, make_push(1, (size_t)r * Hl * HD, Hl * HD, perA, 2u * li, Hl, 1)};
+        st = launch_attn(dev, ap, HD, pdl_enabled());
+        if (st != RCU_OK) return st;
+        {
+            gemvq8::PushWrap<gemvq8::ResidualEpilogueH> epi{{slotX + (size_t)r * Dl, slotX + (size_t)r * Dl},
+                                                           make_push(0, (size_t)r * Dl, Dl, perX, 2u * li, 0, 0)};
+            st = gemv(dev, c.weight_dt, Lw.o, gemvq8::WaitWrap<gemvq8::PlainPrologue<__half>>{{slotA}, make_wait(1, perA, 2u * li)}, epi,
+                           Dl, H * HD);
+            if (st != RCU_OK) return st;
+        }
+        {
+            gemvq8::PushWrap<gemvq8::SiluGateEpilogueH> epi{{slotA + (size_t)r * ffnl}, make_push(1, (size_t)r * ffnl, ffnl, perA, 2u * li + 1u, 0, 0)};
+            st = gemv(dev, c.weight_dt, Lw.gate_up,
+                           gemvq8::WaitWrap<gemvq8::RmsNormPrologueH>{{slotX, (const float*)Lw.ffn_norm, c.rms_eps}, make_wait(0, perX, 2u * li)}, epi,
+                           2 * ffnl, D);
+            if (st != RCU_OK) return st;
+        }
+        {
+            gemvq8::PushWrap<gemvq8::ResidualEpilogueH> epi{{slotX + (size_t)r * Dl, slotX + (size_t)r * Dl},
+                                                           make_push(0, (size_t)r * Dl, Dl, perX, 2u * li + 1u, 0, 0)};
+            st = gemv(dev, c.weight_dt, Lw.down, gemvq8::WaitWrap<gemvq8::PlainPrologue<__half>>{{slotA}, make_wait(1, perA, 2u * li + 1u)},
+                           epi, Dl, ffn);
+            if (st != RCU_OK) return st;
+        }
+    }
+    {
+        gemvq8::PushWrap<gemvq8::PlainEpilogue<__half>> epi{{nullptr, slotL + (size_t)r * Vl}, make_push(2, (size_t)r * Vl, Vl, 1u, 0u, 0, 0)};
+        st = gemv(dev, c.weight_dt, d->lm_head,
+                       gemvq8::WaitWrap<gemvq8::RmsNormPrologueH>{{slotX, (const float*)d->out_norm, c.rms_eps}, make_wait(0, perX, 2u * (L - 1) + 1u)},
+                       epi, Vl, D);
+        if (st != RCU_OK) return st;
+    }
+    argmax_advance_gathered_kernel<<<1, 1024, 0, dev->stream>>>(make_wait(2, 1u, 0u), slotL, (__half*)logits_dev, (int)c.vocab, argmax_dev,
+                                                                 d->scratch.d_pos, d->d_step);
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -463,6 +621,41 @@ rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, co
     return RCU_OK;
 }
 
+rcu_status rcu_decoder_create_sharded(rcu_device* dev, rcu_comm* comm, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers,
+                                      const void* tok_embd, const void* out_norm, const void* lm_head, rcu_decoder** out) {
+    if (!dev || !comm || !cfg || !layers || !tok_embd || !out_norm || !lm_head || !out) return RCU_ERR_INVALID_ARG;
+    const uint32_t W = (uint32_t)comm->world;
+    RCU_REQUIRE(dev, comm->dev == dev, "sharded decoder: the window belongs to another device");
+    RCU_REQUIRE(dev, !comm->bound && comm->seq == 0, "sharded decoder: the window must be fresh (its flags count this decoder's steps)");
+    for (int p = 0; p < comm->world; ++p)
+        RCU_REQUIRE(dev, p == comm->rank || comm->opened[p], "sharded decoder: peer %d has not been imported", p);
+    RCU_REQUIRE(dev, cfg->n_heads % W == 0 && cfg->n_kv_heads % W == 0, "sharded decoder: heads (%u, %u kv) must divide over %u ranks",
+                cfg->n_heads, cfg->n_kv_heads, W);
+    // slices travel as 16-byte vectors and GEMV rows come in groups of 8
+    RCU_REQUIRE(dev, (cfg->d_model / W) % 8 == 0 && cfg->d_model % W == 0 && cfg->ffn % W == 0 && (cfg->ffn / W) % 8 == 0 &&
+                         cfg->vocab % W == 0 && (cfg->vocab / W) % 8 == 0 && (cfg->n_heads / W * cfg->head_dim) % 8 == 0,
+                "sharded decoder: d_model, ffn and vocab must split over %u ranks into multiples of 8 rows", W);
+    const size_t need = 2 * (size_t)std::max(std::max(cfg->d_model, cfg->ffn), std::max(cfg->vocab, cfg->n_heads * cfg->head_dim));
+    RCU_REQUIRE(dev, comm->local.slot_bytes >= need, "sharded decoder: window slots hold %zu bytes, %zu needed", comm->local.slot_bytes, need);
+    rcu_decoder_config local = *cfg;   // per-rank sizes for the shared validation and buffers
+    local.n_heads = cfg->n_heads / W;
+    local.n_kv_heads = cfg->n_kv_heads / W;
+    rcu_decoder* d = nullptr;
+    rcu_status st = rcu_decoder_create(dev, &local, layers, tok_embd, out_norm, lm_head, &d);
+    if (st != RCU_OK) return st;
+    d->cfg = *cfg;                     // the step works from the whole model's sizes
+    DevGuard g(dev->ordinal);
+    if (cudaMalloc(&d->d_step, sizeof(unsigned int)) != cudaSuccess) {
+        rcu_decoder_destroy(d);
+        return rcu_fail(dev, RCU_ERR_OOM, "sharded decoder: step counter");
+    }
+    cudaMemsetAsync(d->d_step, 0, sizeof(unsigned int), dev->stream);
+    d->comm = comm;
+    comm->bound = true;
+    *out = d;
+    return RCU_OK;
+}
+
 void rcu_decoder_destroy(rcu_decoder* d) {
     if (!d) return;
     DevGuard g(d->dev->ordinal);
@@ -476,6 +669,7 @@ void rcu_decoder_destroy(rcu_decoder* d) {
     cudaFree(d->qkv);
     cudaFree(d->attn);
     cudaFree(d->act);
+    cudaFree(d->d_step);
     delete d;
 }
 
@@ -503,7 +697,7 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
     if (!use_graph || d->steps == 0) {
         // first step runs eagerly: sets kernel attributes and counts the launches
         const uint64_t l0 = dev->launches;
-        st = run_sequence(d, token_dev, logits_dev, argmax_dev);
+        st = d->comm ? run_sequence_sharded(d, token_dev, logits_dev, argmax_dev) : run_sequence(d, token_dev, logits_dev, argmax_dev);
         d->kernels_per_step = (uint32_t)(dev->launches - l0);
     } else {
         if (!d->graph_exec || d->cap_token != token_dev || d->cap_logits != logits_dev || d->cap_argmax != argmax_dev) {
@@ -511,7 +705,7 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
             cudaGraph_t graph = nullptr;
             const uint64_t l0 = dev->launches;
             RCU_CUDA(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
-            st = run_sequence(d, token_dev, logits_dev, argmax_dev);
+            st = d->comm ? run_sequence_sharded(d, token_dev, logits_dev, argmax_dev) : run_sequence(d, token_dev, logits_dev, argmax_dev);
             cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
             dev->launches = l0;   // capture launched nothing
             if (st != RCU_OK) { if (graph) cudaGraphDestroy(graph); return st; }

@@ -269,6 +269,103 @@ struct PushEpilogueH {
     }
 };
 
+// ------------------------------------------------------------------------------------------------
+// The same exchange for kernels replayed from a CUDA graph: the sequence number is not a launch
+// argument but step * per_step + idx + 1, with `step` read from device memory (the decoder's step
+// counter), so one captured graph produces a fresh number on every replay.
+// ------------------------------------------------------------------------------------------------
+struct PushInfo {
+    __half* y_local;               // this rank's slice inside its own full buffer (also the source of the copy)
+    int slice_elems;               // elements in the slice (multiple of 8); 0 = no push
+    unsigned int* ticket;          // zero between launches
+    __half* peer_dst[kMaxPeers];
+    unsigned int* peer_flag[kMaxPeers];
+    int n_peers;
+    const unsigned int* step;
+    unsigned int per_step, idx;
+    int n_ctas;                    // CTAs that call run() in this launch (ticket target); 0 = every CTA of a 1-D grid
+    // Every thread of every participating CTA calls this after its last store to y_local.
+    __device__ __forceinline__ void run() const {
+        __shared__ int push_is_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int t = atomicAdd(ticket, 1u);
+            push_is_last = (t == (n_ctas > 0 ? (unsigned int)n_ctas : gridDim.x) - 1u);
+        }
+        __syncthreads();
+        if (!push_is_last) return;
+        __threadfence();
+        const uint4* src = reinterpret_cast<const uint4*>(y_local);
+        const int n16 = slice_elems >> 3;
+        for (int p = 0; p < n_peers; ++p) {
+            uint4* dst = reinterpret_cast<uint4*>(peer_dst[p]);
+            for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
+        }
+        __threadfence_system();
+        __syncthreads();
+        const unsigned int seq = __ldcg(step) * per_step + idx + 1u;
+        if ((int)threadIdx.x < n_peers)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag[threadIdx.x]), "r"(seq) : "memory");
+        if (threadIdx.x == 0) *ticket = 0;
+    }
+};
+
+template <class Inner> struct PushWrap {
+    static constexpr int UNIT = Inner::UNIT;
+    Inner inner;
+    PushInfo push;
+    __device__ __forceinline__ void store(int u, const float* acc) const { inner.store(u, acc); }
+    __device__ __forceinline__ void finish() const {
+        inner.finish();
+        push.run();
+    }
+};
+
+// Consumer side: wait (bounded) until every peer's flag for this exchange has reached the sequence
+// number.  Lane p of the CTA polls peer p's flag in this GPU's own memory; a wait that runs out of its
+// budget, or finds that an earlier wait already did, records RCU_DEVFLAG_TIMEOUT and goes on, so the
+// kernel always ends (the host sees the flag after the step).
+struct WaitInfo {
+    const unsigned int* flags;     // [world] in this rank's window; nullptr = nothing to wait for
+    int world, self;
+    const unsigned int* step;
+    unsigned int per_step, idx;
+    int* status;
+    __device__ __forceinline__ void wait() const {
+        if (flags == nullptr) return;
+        const int p = threadIdx.x;
+        if (p < world && p != self) {
+            const unsigned int seq = __ldcg(step) * per_step + idx + 1u;
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
+                if ((int)(v - seq) >= 0) break;
+                if (*reinterpret_cast<volatile int*>(status) & RCU_DEVFLAG_TIMEOUT) break;
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                if (t - t0 > 2000000000ull) {
+                    atomicOr(status, RCU_DEVFLAG_TIMEOUT);
+                    break;
+                }
+            }
+        }
+        // the kThreads staging threads only (a kernel may run extra warps that do not stage)
+        asm volatile("bar.sync 15, %0;" ::"n"(kThreads) : "memory");
+    }
+};
+
+template <class Inner> struct WaitWrap {
+    Inner inner;
+    WaitInfo w;
+    template <class ActT> __device__ __forceinline__ void stage(ActT* xs, int K, float* scratch) const {
+        w.wait();
+        inner.stage(xs, K, scratch);
+    }
+};
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -2,6 +2,7 @@
 // `dequantize` (ratchet-core/src/quant.rs:101-164) for Q8_0 and with the Q4_K decode arithmetic of
 // ops/matmul/quantized.rs:158-266 on the segment layout of ratchet-loader/src/gguf/dtype.rs:39-125.
 #include "common.cuh"
+#include "dequant.cuh"
 
 namespace {
 
@@ -29,6 +30,11 @@ dequant_q8_kernel(const uint2* __restrict__ q, const ScaleT* __restrict__ d, Sca
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
         const uint2 w = q[i];
+        if (sizeof(ScaleT) == 2) {   // f16: exponent-trick conversion and a native f16 multiply (same rounding)
+            const __half dh = reinterpret_cast<const __half*>(d)[i >> 2];
+            *reinterpret_cast<uint4*>(out + i * 8) = rcu_dequant::dequant8_q8(w.x, w.y, __half2half2(dh));
+            continue;
+        }
         const float sc = to_f32<ScaleT>(d[i >> 2]);
         const uint32_t ws[2] = {w.x, w.y};
         float v[8];
@@ -43,39 +49,52 @@ dequant_q8_kernel(const uint2* __restrict__ q, const ScaleT* __restrict__ d, Sca
     }
 }
 
-// 8 weights per thread (half of a 16-byte run of nibbles): consecutive threads write consecutive
-// 16-byte vectors.  Weight index w -> super-block w/256, sub-block (w%256)/32, position w%32; the
-// nibbles of sub-blocks 2c and 2c+1 share the 32 bytes of chunk c (low / high nibble).
+using rcu_dequant::pack_byte;
+
+// Thread = (super-block b, 32-byte chunk c, quarter q of the chunk): one 8-byte load of nibble bytes
+// yields 8 weights of sub-block 2c (low nibbles) and 8 of sub-block 2c+1 (high nibbles), each stored
+// as one 16-byte vector; four neighbouring lanes fill 64 consecutive bytes of each sub-block.  The pack
+// of 6-bit codes is read as three words, d and dmin once.
 template <class FP>
 __global__ void __launch_bounds__(256)
 dequant_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scales, const FP* __restrict__ dmin,
-                   const FP* __restrict__ d, FP* __restrict__ out, size_t n8) {
+                   const FP* __restrict__ d, FP* __restrict__ out, size_t nthreads) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
-        const size_t w0 = i * 8;
-        const size_t b = w0 >> 8;
-        const int within = (int)(w0 & 255);
-        const int j = within >> 5, l0 = within & 31;
-        const uint8_t* sc = scales + b * 12;
-        uint32_t s, m;
-        if (j < 4) {
-            s = sc[j] & 63u;
-            m = sc[j + 4] & 63u;
-        } else {
-            s = (sc[j + 4] & 0xFu) | ((uint32_t)(sc[j - 4] >> 6) << 4);
-            m = (uint32_t)(sc[j + 4] >> 4) | ((uint32_t)(sc[j] >> 6) << 4);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nthreads; i += stride) {
+        const size_t b = i >> 4;
+        const int c = (int)(i >> 2) & 3, q = (int)i & 3;
+        const uint2 qw = *reinterpret_cast<const uint2*>(qs + b * 128 + c * 32 + q * 8);
+        const uint32_t* pk = reinterpret_cast<const uint32_t*>(scales + b * 12);
+        const uint32_t w[3] = {pk[0], pk[1], pk[2]};
+        const float df = to_f32<FP>(d[b]), mf = to_f32<FP>(dmin[b]);
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+            const int j = 2 * c + hi;
+            uint32_t s, m;
+            if (j < 4) {
+                s = pack_byte(w, j) & 63u;
+                m = pack_byte(w, j + 4) & 63u;
+            } else {
+                s = (pack_byte(w, j + 4) & 0xFu) | ((pack_byte(w, j - 4) >> 6) << 4);
+                m = (pack_byte(w, j + 4) >> 4) | ((pack_byte(w, j) >> 6) << 4);
+            }
+            const float delta = rnd<FP>((float)s * df);
+            const float mn = rnd<FP>((float)m * mf);
+            FP* o = out + b * 256 + j * 32 + q * 8;
+            if (sizeof(FP) == 2) {   // f16: fma(q, delta, -min) with one rounding is the native half2 fma
+                const __half2 d2 = __float2half2_rn(delta), n2 = __float2half2_rn(-mn);   // both exact f16 values
+                *reinterpret_cast<uint4*>(o) = rcu_dequant::dequant8_q4(qw.x >> (4 * hi), qw.y >> (4 * hi), d2, n2);
+                continue;
+            }
+            const uint32_t ws[2] = {qw.x, qw.y};
+            float v[8];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    v[a * 4 + e] = rnd<FP>(fmaf((float)((ws[a] >> (8 * e + 4 * hi)) & 0xF), delta, -mn));
+            Pack8<FP>::store(o, v);
         }
-        const float delta = rnd<FP>((float)s * to_f32<FP>(d[b]));
-        const float mn = rnd<FP>((float)m * to_f32<FP>(dmin[b]));
-        const uint2 qw = *reinterpret_cast<const uint2*>(qs + b * 128 + (j >> 1) * 32 + l0);
-        const int shift = (j & 1) * 4;
-        const uint32_t ws[2] = {qw.x >> shift, qw.y >> shift};
-        float v[8];
-#pragma unroll
-        for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) v[a * 4 + e] = rnd<FP>(fmaf((float)((ws[a] >> (8 * e)) & 0xF), delta, -mn));
-        Pack8<FP>::store(out + w0, v);
     }
 }
 
@@ -100,7 +119,7 @@ extern "C" rcu_status rcu_dequantize(rcu_device* dev, const rcu_tensor* src, rcu
         else dequant_q8_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint2*)base, (const __half*)(base + off[1]), (__half*)dst->data, n8);
     } else {
         RCU_REQUIRE(dev, n % 256 == 0, "dequantize: Q4_K needs a multiple of 256 elements");
-        const size_t nsub = n / 8;
+        const size_t nsub = n / 16;
         const int grid = (int)std::min<size_t>((nsub + 255) / 256, (size_t)cap);
         if (src->dt == RCU_Q4_KF) dequant_q4k_kernel<float><<<grid, 256, 0, dev->stream>>>((const uint8_t*)base, (const uint8_t*)base + off[1], (const float*)(base + off[2]), (const float*)(base + off[3]), (float*)dst->data, nsub);
         else dequant_q4k_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint8_t*)base, (const uint8_t*)base + off[1], (const __half*)(base + off[2]), (const __half*)(base + off[3]), (__half*)dst->data, nsub);

@@ -10,12 +10,13 @@
 //
 // Each row is read from HBM once, kept in registers, reduced with warp shuffles (plus one
 // shared-memory hop across the warps of a CTA for long rows) and written once.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int kCtaThreads = 256;
-constexpr int kPer = 4;             // 16-byte vectors a thread keeps in registers
 
 struct SumOp { __device__ static float id() { return 0.f; } __device__ static float f(float a, float b) { return a + b; } };
 struct MaxOp { __device__ static float id() { return -INFINITY; } __device__ static float f(float a, float b) { return fmaxf(a, b); } };
@@ -60,15 +61,174 @@ enum { MODE_LN = 0, MODE_RMS = 1, MODE_SOFTMAX = 2 };
 
 template <class T, int V> struct alignas(sizeof(T) * V) RowVec { T v[V]; };
 
+__device__ __forceinline__ float exp2f_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Per-vector arithmetic.  The generic version computes in f32 and rounds to T after every operation.
+// The f16 version does the same steps with native half2 instructions: an f16 add or multiply of two
+// f16 values is the f32 operation rounded once to f16 (the f32 result is exact, or far from an f16
+// rounding boundary), so the results are identical and the f32<->f16 conversions disappear.
+template <class T, int V> struct RowMath {
+    typedef RowVec<T, V> VT;
+    __device__ static __forceinline__ void stats(const VT& x, float& s, float& s2) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) { const float v = to_f32<T>(x.v[e]); s += v; s2 += rnd<T>(v * v); }
+    }
+    __device__ static __forceinline__ VT layer_norm(const VT& x, float mu, float rstd, const VT& g, const VT* b) {
+        VT o;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float y = rnd<T>(rnd<T>(to_f32<T>(x.v[e]) - mu) * rstd);
+            y = rnd<T>(y * to_f32<T>(g.v[e]));
+            if (b) y = rnd<T>(y + to_f32<T>(b->v[e]));
+            o.v[e] = from_f32<T>(y);
+        }
+        return o;
+    }
+    __device__ static __forceinline__ VT rms_norm(const VT& x, float rstd, const VT& g) {
+        VT o;
+#pragma unroll
+        for (int e = 0; e < V; ++e) o.v[e] = from_f32<T>(rnd<T>(rnd<T>(to_f32<T>(x.v[e]) * rstd) * to_f32<T>(g.v[e])));
+        return o;
+    }
+    __device__ static __forceinline__ void maxv(const VT& x, float& mx) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) mx = fmaxf(mx, to_f32<T>(x.v[e]));
+    }
+    // x <- fp(exp(x - mx)) in place; the terms are added to `sum`
+    __device__ static __forceinline__ void exp_inplace(VT& x, float mx, float& sum) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const float d = to_f32<T>(x.v[e]) - mx;
+            const float p = rnd<T>(sizeof(T) == 2 ? __expf(d) : expf(d));
+            x.v[e] = from_f32<T>(p);
+            sum += p;
+        }
+    }
+    // 16-bit types multiply by the reciprocal (one unit in the last place of f32 away from the quotient,
+    // which almost never changes the rounded 16-bit result); f32 divides
+    __device__ static __forceinline__ VT normalise(const VT& p, float sum, float inv) {
+        VT o;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const float v = to_f32<T>(p.v[e]);
+            o.v[e] = from_f32<T>(sizeof(T) == 2 ? v * inv : v / sum);
+        }
+        return o;
+    }
+};
+
+template <int V> struct RowMath<__half, V> {
+    static_assert(V % 2 == 0 || V == 1, "f16 vectors hold pairs");
+    typedef RowVec<__half, V> VT;
+    __device__ static __forceinline__ void stats(const VT& x, float& s, float& s2) {
+        if (V == 1) {
+            const float v = __half2float(x.v[0]);
+            s += v;
+            s2 += rnd<__half>(v * v);
+        } else {
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e) {
+                const __half2 h = reinterpret_cast<const __half2*>(x.v)[e];
+                const float2 f = __half22float2(h), q = __half22float2(__hmul2_rn(h, h));
+                s += f.x; s += f.y;
+                s2 += q.x; s2 += q.y;
+            }
+        }
+    }
+    __device__ static __forceinline__ VT layer_norm(const VT& x, float mu, float rstd, const VT& g, const VT* b) {
+        VT o;
+        if (V == 1) {
+            __half y = __hmul_rn(__hmul_rn(__hsub_rn(x.v[0], __float2half_rn(mu)), __float2half_rn(rstd)), g.v[0]);
+            if (b) y = __hadd_rn(y, b->v[0]);
+            o.v[0] = y;
+        } else {
+            const __half2 mu2 = __float2half2_rn(mu), r2 = __float2half2_rn(rstd);   // both already f16 values
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e) {
+                __half2 y = __hmul2_rn(__hmul2_rn(__hsub2_rn(reinterpret_cast<const __half2*>(x.v)[e], mu2), r2),
+                                       reinterpret_cast<const __half2*>(g.v)[e]);
+                if (b) y = __hadd2_rn(y, reinterpret_cast<const __half2*>(b->v)[e]);
+                reinterpret_cast<__half2*>(o.v)[e] = y;
+            }
+        }
+        return o;
+    }
+    __device__ static __forceinline__ VT rms_norm(const VT& x, float rstd, const VT& g) {
+        VT o;
+        if (V == 1) {
+            o.v[0] = __hmul_rn(__hmul_rn(x.v[0], __float2half_rn(rstd)), g.v[0]);
+        } else {
+            const __half2 r2 = __float2half2_rn(rstd);
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e)
+                reinterpret_cast<__half2*>(o.v)[e] =
+                    __hmul2_rn(__hmul2_rn(reinterpret_cast<const __half2*>(x.v)[e], r2), reinterpret_cast<const __half2*>(g.v)[e]);
+        }
+        return o;
+    }
+    // softmax steps on pairs: one conversion instruction per pair in each direction, the maximum in
+    // native half2, exp in f32 (hardware exp2), the sum of the unrounded terms in f32
+    __device__ static __forceinline__ void maxv(const VT& x, float& mx) {
+        if (V == 1) {
+            mx = fmaxf(mx, __half2float(x.v[0]));
+        } else {
+            __half2 m = reinterpret_cast<const __half2*>(x.v)[0];
+#pragma unroll
+            for (int e = 1; e < V / 2; ++e) m = __hmax2(m, reinterpret_cast<const __half2*>(x.v)[e]);
+            const float2 f = __half22float2(m);
+            mx = fmaxf(mx, fmaxf(f.x, f.y));
+        }
+    }
+    __device__ static __forceinline__ void exp_inplace(VT& x, float mx, float& sum) {
+        const float kLog2e = 1.4426950408889634f;
+        const float bias = -mx * kLog2e;
+        if (V == 1) {
+            const float p = exp2f_fast(fmaf(__half2float(x.v[0]), kLog2e, bias));
+            x.v[0] = __float2half_rn(p);
+            sum += p;
+        } else {
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e) {
+                const float2 f = __half22float2(reinterpret_cast<const __half2*>(x.v)[e]);
+                const float p0 = exp2f_fast(fmaf(f.x, kLog2e, bias)), p1 = exp2f_fast(fmaf(f.y, kLog2e, bias));
+                reinterpret_cast<__half2*>(x.v)[e] = __floats2half2_rn(p0, p1);
+                sum += p0;
+                sum += p1;
+            }
+        }
+    }
+    __device__ static __forceinline__ VT normalise(const VT& p, float, float inv) {
+        VT o;
+        if (V == 1) {
+            o.v[0] = __float2half_rn(__half2float(p.v[0]) * inv);
+        } else {
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e) {
+                const float2 f = __half22float2(reinterpret_cast<const __half2*>(p.v)[e]);
+                reinterpret_cast<__half2*>(o.v)[e] = __floats2half2_rn(f.x * inv, f.y * inv);
+            }
+        }
+        return o;
+    }
+};
+
 // One row per group of G threads (a CTA holds max(256, G) / G rows).  Thread t of the group owns
-// vectors t, t + G, ... (up to kPer of them, V elements each; N % V == 0): the row is read from
-// HBM once with all of a thread's loads in flight together, kept in registers as f32, and written
-// once.  16-bit types round to their own precision after every operation, as the CPU device does.
-template <class T, int MODE, int G, int V>
+// vectors t, t + G, ... (up to kPer of them, V elements each; N % V == 0).  Rows of up to 512
+// vectors belong to one warp (G = 32, up to 16 vectors per lane): no block-wide barrier, so the warps
+// of a CTA stream independently.  The row is read from
+// HBM once with all of a thread's loads in flight together, kept in registers in its own type, and
+// written once.  16-bit types round to their own precision after every operation, as the CPU device
+// does.
+template <class T, int MODE, int G, int V, int kPer>
 __global__ void __launch_bounds__(G > kCtaThreads ? G : kCtaThreads)
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
            size_t rows, int N, float eps) {
     typedef RowVec<T, V> VT;
+    typedef RowMath<T, V> Math;
     constexpr int CTA = G > kCtaThreads ? G : kCtaThreads;
     constexpr int GROUPS = CTA / G;
     __shared__ float scratch[2][32];
@@ -85,48 +245,35 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
             const int j = t + i * G;
             if (valid && j < nvec) raw[i] = xr[j];
         }
-        float v[kPer][V];
-        float s = 0.f, s2 = 0.f, mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-            const int j = t + i * G;
-            if (valid && j < nvec) {
-#pragma unroll
-                for (int e = 0; e < V; ++e) {
-                    v[i][e] = to_f32<T>(raw[i].v[e]);
-                    if (MODE == MODE_SOFTMAX) mx = fmaxf(mx, v[i][e]);
-                    else { s += v[i][e]; s2 += rnd<T>(v[i][e] * v[i][e]); }
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < V; ++e) v[i][e] = 0.f;
-            }
-        }
         if (MODE == MODE_SOFTMAX) {
-            float dummy = -INFINITY;
+            float mx = -INFINITY, dummy = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int j = t + i * G;
+                if (valid && j < nvec) Math::maxv(raw[i], mx);
+            }
             group_reduce2<MaxOp, G>(mx, dummy, scratch);
             float sum = 0.f, zero = 0.f;
 #pragma unroll
             for (int i = 0; i < kPer; ++i) {
                 const int j = t + i * G;
-                if (valid && j < nvec) {
-#pragma unroll
-                    for (int e = 0; e < V; ++e) { v[i][e] = rnd<T>(sizeof(T) == 2 ? __expf(v[i][e] - mx) : expf(v[i][e] - mx)); sum += v[i][e]; }
-                }
+                if (valid && j < nvec) Math::exp_inplace(raw[i], mx, sum);
             }
             group_reduce2<SumOp, G>(sum, zero, scratch);
             sum = rnd<T>(sum);
+            const float inv = 1.0f / sum;
 #pragma unroll
             for (int i = 0; i < kPer; ++i) {
                 const int j = t + i * G;
-                if (valid && j < nvec) {
-                    VT o;
-#pragma unroll
-                    for (int e = 0; e < V; ++e) o.v[e] = from_f32<T>(sizeof(T) == 2 ? __fdividef(v[i][e], sum) : v[i][e] / sum);
-                    orow[j] = o;
-                }
+                if (valid && j < nvec) orow[j] = Math::normalise(raw[i], sum, inv);
             }
         } else {
+            float s = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const int j = t + i * G;
+                if (valid && j < nvec) Math::stats(raw[i], s, s2);
+            }
             const float nf = rnd<T>((float)N);
             const float e_ = rnd<T>(eps);
             group_reduce2<SumOp, G>(s, s2, scratch);
@@ -145,21 +292,13 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
                 const int j = t + i * G;
                 if (valid && j < nvec) {
                     const VT gm = reinterpret_cast<const VT*>(gamma)[j];
-                    VT bt, o;
-                    if (MODE == MODE_LN && beta) bt = reinterpret_cast<const VT*>(beta)[j];
-#pragma unroll
-                    for (int e = 0; e < V; ++e) {
-                        float y;
-                        if (MODE == MODE_LN) {
-                            y = rnd<T>(rnd<T>(v[i][e] - mu) * rstd);
-                            y = rnd<T>(y * to_f32<T>(gm.v[e]));
-                            if (beta) y = rnd<T>(y + to_f32<T>(bt.v[e]));
-                        } else {
-                            y = rnd<T>(rnd<T>(v[i][e] * rstd) * to_f32<T>(gm.v[e]));
-                        }
-                        o.v[e] = from_f32<T>(y);
+                    if (MODE == MODE_LN) {
+                        VT bt;
+                        if (beta) bt = reinterpret_cast<const VT*>(beta)[j];
+                        orow[j] = Math::layer_norm(raw[i], mu, rstd, gm, beta ? &bt : nullptr);
+                    } else {
+                        orow[j] = Math::rms_norm(raw[i], rstd, gm);
                     }
-                    orow[j] = o;
                 }
             }
         }
@@ -204,21 +343,26 @@ row_kernel_long(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     }
 }
 
+constexpr int kMaxRowVecs = 1024 * 8;   // longest row (in vectors) the register-resident kernel takes
+
 template <class T, int MODE, int V>
 rcu_status launch_rows_v(rcu_device* dev, const T* xp, const T* gp, const T* bp, T* op, size_t rows, int N, float eps) {
     const int nvec = N / V;
     const size_t cap = (size_t)dev->sm_count * 8;
-#define RCU_ROW(G)                                                                                         \
+#define RCU_ROW(G, PER)                                                                                    \
     {                                                                                                      \
         constexpr int cta = G > kCtaThreads ? G : kCtaThreads;                                             \
         const size_t groups = cta / G;                                                                     \
         const int grid = (int)std::min<size_t>((rows + groups - 1) / groups, cap);                         \
-        row_kernel<T, MODE, G, V><<<grid, cta, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);            \
+        row_kernel<T, MODE, G, V, PER><<<grid, cta, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);       \
     }
-    if (nvec <= 32 * kPer) RCU_ROW(32)
-    else if (nvec <= 128 * kPer) RCU_ROW(128)
-    else if (nvec <= 256 * kPer) RCU_ROW(256)
-    else RCU_ROW(1024)
+    if (nvec <= 32 * 4) RCU_ROW(32, 4)
+    else if (nvec <= 32 * 8) RCU_ROW(32, 8)
+    else if (nvec <= 32 * 16) RCU_ROW(32, 16)
+    else if (nvec <= 128 * 8) RCU_ROW(128, 8)
+    else if (nvec <= 256 * 8) RCU_ROW(256, 8)
+    else if (nvec <= 1024 * 4) RCU_ROW(1024, 4)
+    else RCU_ROW(1024, 8)
 #undef RCU_ROW
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
@@ -230,9 +374,10 @@ rcu_status launch_rows(rcu_device* dev, const void* x, const void* gamma, const 
     constexpr int VFULL = 16 / sizeof(T), VHALF = 8 / sizeof(T);
     const uintptr_t ptr_bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
                                reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta);
-    auto fits = [&](int v) { return N % v == 0 && (ptr_bits & ((uintptr_t)v * sizeof(T) - 1)) == 0 && N / v <= 1024 * kPer; };
-    if (fits(VFULL)) return launch_rows_v<T, MODE, VFULL>(dev, xp, gp, bp, op, rows, N, eps);
-    if (fits(VHALF)) return launch_rows_v<T, MODE, VHALF>(dev, xp, gp, bp, op, rows, N, eps);
+    auto fits = [&](int v) { return N % v == 0 && (ptr_bits & ((uintptr_t)v * sizeof(T) - 1)) == 0 && N / v <= kMaxRowVecs; };
+    constexpr bool kVector = !std::is_same<T, __nv_bfloat16>::value;   // bf16 activations are rare: scalar path only
+    if (kVector && fits(VFULL)) return launch_rows_v<T, MODE, kVector ? VFULL : 1>(dev, xp, gp, bp, op, rows, N, eps);
+    if (kVector && fits(VHALF)) return launch_rows_v<T, MODE, kVector ? VHALF : 1>(dev, xp, gp, bp, op, rows, N, eps);
     if (fits(1)) return launch_rows_v<T, MODE, 1>(dev, xp, gp, bp, op, rows, N, eps);
     const int grid = (int)std::min<size_t>(rows, (size_t)dev->sm_count * 8);
     row_kernel_long<T, MODE><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);

@@ -49,10 +49,16 @@ class DecoderLayer:
 
 
 class Decoder:
+    """``comm`` = None: the whole model on one GPU.  With a ``ratchet_b200.comm.Comm`` the step is sharded
+    over the comm's ranks (one process per GPU): ``cfg`` still describes the whole model, ``layers`` and
+    ``lm_head`` hold this rank's rows (``comm.decoder_shard_ranges``), the KV caches its own heads; the
+    comm must be fresh, with slots of ``max(d_model, ffn, vocab, n_heads * head_dim)`` elements, and every
+    rank must step with the same token."""
+
     def __init__(self, dev: Device, cfg: DecoderConfig, layers: List[DecoderLayer], tok_embd: Buffer, out_norm: Buffer,
-                 lm_head: Buffer):
+                 lm_head: Buffer, comm=None):
         self.dev, self.cfg = dev, cfg
-        self._keep = (layers, tok_embd, out_norm, lm_head)     # device memory must outlive the decoder
+        self._keep = (layers, tok_embd, out_norm, lm_head, comm)     # device memory must outlive the decoder
         c = capi.rcu_decoder_config(cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
                                     cfg.max_cache, cfg.rope_dim, cfg.rope_base, cfg.rms_eps, cfg.weight_dt)
         arr = (capi.rcu_decoder_layer * len(layers))()
@@ -60,7 +66,11 @@ class Decoder:
             arr[i] = capi.rcu_decoder_layer(l.attn_norm.ptr, l.qkv.ptr, l.o.ptr, l.ffn_norm.ptr, l.gate_up.ptr, l.down.ptr,
                                             l.k_cache.ptr, l.v_cache.ptr)
         h = C.c_void_p()
-        dev.check(dev._lib.rcu_decoder_create(dev.handle, C.byref(c), arr, tok_embd.ptr, out_norm.ptr, lm_head.ptr, C.byref(h)))
+        if comm is None:
+            dev.check(dev._lib.rcu_decoder_create(dev.handle, C.byref(c), arr, tok_embd.ptr, out_norm.ptr, lm_head.ptr, C.byref(h)))
+        else:
+            dev.check(dev._lib.rcu_decoder_create_sharded(dev.handle, comm._h, C.byref(c), arr, tok_embd.ptr, out_norm.ptr, lm_head.ptr,
+                                                          C.byref(h)))
         self._h = h
         self.token = dev.empty(capi.I32, (1,))
         self.logits = dev.empty(capi.F16, (1, 1, cfg.vocab))

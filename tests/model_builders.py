@@ -86,6 +86,34 @@ def phi3_decoder(dev, W, kv_prior, max_cache=4096, kv_seed=5):
     return dec
 
 
+def phi3_decoder_sharded(dev, W, kv_prior, comm, max_cache=4096, kv_seed=5):
+    """The same engine with every Linear sharded over the ranks of `comm` (this rank's rows, its own KV heads)."""
+    from ratchet_b200.comm import decoder_shard_ranges, take_rows_q8
+    from ratchet_b200.decoder import Decoder, DecoderConfig, DecoderLayer
+    d, H, ffn, vocab = W["d"], W["n_heads"], W["ffn"], W["vocab"]
+    hd = d // H
+    R = decoder_shard_ranges(H, H, hd, d, ffn, vocab, comm.rank, comm.world)
+    kv = phi3_kv(W, kv_prior, np.float16, max_cache, kv_seed)
+    wdt = W["embd"][1]
+    rows = lambda rng_list: sum(b - a for a, b in rng_list)
+
+    def shard(rd, n_rows, k, key):
+        return dev.from_quantized(take_rows_q8(rd[0], rd[1], n_rows, k, R[key]), rd[1], (rows(R[key]), k))
+
+    h0, h1 = R["kv_heads"]
+    layers = []
+    for li, lw in enumerate(W["layers"]):
+        layers.append(DecoderLayer(dev.from_numpy(lw["attn_norm"]), shard(lw["qkv"], 3 * d, d, "qkv"), shard(lw["o"], d, d, "o"),
+                                   dev.from_numpy(lw["ffn_norm"]), shard(lw["up"], 2 * ffn, d, "gate_up"), shard(lw["down"], d, ffn, "down"),
+                                   dev.from_numpy(np.ascontiguousarray(kv[li][0][0, h0:h1])),
+                                   dev.from_numpy(np.ascontiguousarray(kv[li][1][0, h0:h1]))))
+    cfg = DecoderConfig(len(layers), d, H, H, hd, ffn, vocab, max_cache, hd, 10000.0, 1e-5, wdt)
+    dec = Decoder(dev, cfg, layers, dev.from_quantized(W["embd"][0], wdt, (vocab, d)), dev.from_numpy(W["ln_post"]),
+                  shard(W["lm_head"], vocab, d, "lm_head"), comm=comm)
+    dec.position = kv_prior
+    return dec
+
+
 def phi3_model(T, dev, W, kv_prior, act_np, max_cache=4096, kv_seed=5):
     """Builds callers.Phi3 with a KV cache holding `kv_prior` N(0,1) positions (phi3/model.rs:160-202)."""
     d, H = W["d"], W["n_heads"]

@@ -70,3 +70,67 @@ def test_sharded_gemv_push_allgather(world):
         assert p.exitcode == 0
     res = sorted(q.get(timeout=10) for _ in range(world))
     assert all(ok for _, ok, _ in res), res
+
+
+def _decoder_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ratchet_b200 import Device
+        from ratchet_b200.comm import Comm
+        from . import model_builders as mb
+        torch.cuda.set_device(rank)
+        stream = torch.cuda.Stream()          # a real stream, so that steps after the first replay a CUDA graph
+        dev = Device(rank, stream=stream.cuda_stream)
+        # a narrow Phi-3: 3 layers, d 1024, 16 heads of 64, ffn 2048, vocab 4096, 100 cached positions
+        W = mb.phi3_weights(11, n_layers=3, d=1024, n_heads=16, ffn=2048, vocab=4096, quant="q8h")
+        steps, prior, cache = 5, 100, 256
+        single = mb.phi3_decoder(dev, W, prior, max_cache=cache)
+        ref_logits, ref_tokens = [], []
+        dev.h2d(single.token.ptr, np.array([7], np.int32))
+        for _ in range(steps):
+            single.step_device(single.token.ptr if not ref_tokens else single.next_token.ptr)
+            dev.sync()
+            ref_logits.append(single.logits.to_numpy().copy())
+            ref_tokens.append(int(single.next_token.to_numpy()[0]))
+        single.close()
+        comm = Comm(dev, rank, world, max(W["d"], W["ffn"], W["vocab"]))
+        sharded = mb.phi3_decoder_sharded(dev, W, prior, comm, max_cache=cache)
+        ok, tokens = True, []
+        dev.h2d(sharded.token.ptr, np.array([7], np.int32))
+        for i in range(steps):
+            sharded.step_device(sharded.token.ptr if i == 0 else sharded.next_token.ptr)
+            dev.sync()                         # raises if a flag wait ran out of time
+            got = sharded.logits.to_numpy()
+            tokens.append(int(sharded.next_token.to_numpy()[0]))
+            # every output element is computed by one rank with the single-GPU arithmetic: bit-identical
+            ok = ok and np.array_equal(got.view(np.uint16), ref_logits[i].view(np.uint16))
+        ok = ok and tokens == ref_tokens
+        dist.barrier()
+        sharded.close()
+        comm.close()
+        dev.close()
+        q.put((rank, ok, tokens, ref_tokens))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_decoder_matches_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_decoder_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    res = sorted(q.get(timeout=10) for _ in range(world))
+    assert all(ok for _, ok, _, _ in res), res

@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 
 from oracle import oracle as orc
 from ratchet_b200 import capi
-from ratchet_b200.comm import exchange_handles, shard_q8, shard_rows
+from ratchet_b200.comm import decoder_shard_ranges, exchange_handles, shard_q8, shard_rows, take_rows_q8
 
 
 def test_shard_rows():
@@ -75,6 +75,41 @@ def _worker(rank, world, port, q):
         q.put((rank, bool(np.array_equal(y.view(np.uint16), ref.view(np.uint16)))))
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_decoder_shards_cover_every_row_once(world):
+    """Sharded decode step: the union of the ranks' row ranges is every output row exactly once, the
+    qkv shard holds the q, k and v rows of the rank's own heads, gate and up rows pair up."""
+    H, Hkv, hd, d, ffn, vocab = 32, 32, 96, 3072, 8192, 32064
+    seen = {k: np.zeros(n, np.int32) for k, n in (("qkv", (H + 2 * Hkv) * hd), ("o", d), ("gate_up", 2 * ffn), ("down", d), ("lm_head", vocab))}
+    for r in range(world):
+        R = decoder_shard_ranges(H, Hkv, hd, d, ffn, vocab, r, world)
+        for k, cnt in seen.items():
+            for a, b in R[k]:
+                cnt[a:b] += 1
+        (q0, q1), (k0, k1), (v0, v1) = R["qkv"]
+        assert q1 - q0 == H // world * hd and k1 - k0 == v1 - v0 == Hkv // world * hd
+        assert k0 - H * hd == v0 - (H + Hkv) * hd == R["kv_heads"][0] * hd          # k and v rows of the same heads
+        (g0, g1), (u0, u1) = R["gate_up"]
+        assert u0 - g0 == ffn and u1 - g1 == ffn                                     # up row = gate row + ffn
+    assert all((c == 1).all() for c in seen.values())
+    with pytest.raises(ValueError):
+        decoder_shard_ranges(32, 32, 96, 3072, 8192, 32064, 0, 5)
+
+
+def test_take_rows_q8_concatenates_ranges():
+    g = np.random.Generator(np.random.PCG64(3))
+    N, K = 48, 64
+    w = (g.standard_normal((N, K)) * 0.02).astype(np.float16)
+    full = orc.quantize_q8(w)
+    sub = take_rows_q8(full, capi.Q8_0H, N, K, [(8, 16), (40, 48)])
+    picked = np.concatenate([w[8:16], w[40:48]])
+    assert np.array_equal(sub, orc.quantize_q8(picked))
+    assert np.array_equal(orc.dequantize_q8(sub, (16, K), True).view(np.uint16),
+                          np.concatenate([orc.dequantize_q8(full, (N, K), True)[8:16], orc.dequantize_q8(full, (N, K), True)[40:48]]).view(np.uint16))
+    with pytest.raises(ValueError):
+        take_rows_q8(full, capi.Q8_0H, N, K, [(40, 49)])
 
 
 def test_two_rank_gather_over_gloo():
