@@ -328,28 +328,43 @@ def phi3_decode_bytes(c):
     return int(w_elems * (1 + 2 / 32)) + kv + d * (1 + 2 / 32)
 
 
-def phi3_decode_bench(dev, torch, stream, steps, warmup):
+def phi3_decode_bench(dev, torch, stream, steps, warmup, rank=0, world=1, dist=None):
     """Phi-3-mini decode step (32 layers, hidden 3072, 32 heads x 96, MLP 8192, vocab 32064, Q8_0H
-    weights, 1024 prior KV positions of N(0,1) f16, batch 1) through the fused decode engine."""
+    weights, 1024 prior KV positions of N(0,1) f16, batch 1) through the fused decode engine.  With
+    world > 1 every Linear is sharded by output rows over the ranks (attention by heads) and each rank
+    holds its own rows, generated at the shard's shape: the weights are random either way."""
     from ratchet_b200 import capi
     from ratchet_b200.decoder import Decoder, DecoderConfig, DecoderLayer
     c = PHI3
     d, H, hd, ffn, V = c["d"], c["n_heads"], c["head_dim"], c["ffn"], c["vocab"]
+    g = world
+    Hl = H // g
     rng = np.random.Generator(np.random.PCG64(11))
-    host = {"qkv": _q8h_weights(3 * d, d, 1), "o": _q8h_weights(d, d, 2), "up": _q8h_weights(2 * ffn, d, 3), "down": _q8h_weights(d, ffn, 4)}
-    kv_host = np.zeros((H, c["max_cache"], hd), np.float16)
-    kv_host[:, : c["kv_prior"]] = rng.standard_normal((H, c["kv_prior"], hd)).astype(np.float16)
+    shapes = {"qkv": (3 * Hl * hd, d), "o": (d // g, d), "up": (2 * ffn // g, d), "down": (d // g, ffn)}
+    host = {k: _q8h_weights(n, kk, 100 * rank + i) for i, (k, (n, kk)) in enumerate(shapes.items())}
+    kv_host = np.zeros((Hl, c["max_cache"], hd), np.float16)
+    kv_host[:, : c["kv_prior"]] = rng.standard_normal((Hl, c["kv_prior"], hd)).astype(np.float16)
     ones = np.ones(d, np.float32)
     layers = []
     for _ in range(c["n_layers"]):   # every layer gets its own device copy: the step streams 32 distinct sets
-        layers.append(DecoderLayer(dev.from_numpy(ones), dev.from_quantized(host["qkv"], capi.Q8_0H, (3 * d, d)),
-                                   dev.from_quantized(host["o"], capi.Q8_0H, (d, d)), dev.from_numpy(ones),
-                                   dev.from_quantized(host["up"], capi.Q8_0H, (2 * ffn, d)), dev.from_quantized(host["down"], capi.Q8_0H, (d, ffn)),
+        layers.append(DecoderLayer(dev.from_numpy(ones), dev.from_quantized(host["qkv"], capi.Q8_0H, shapes["qkv"]),
+                                   dev.from_quantized(host["o"], capi.Q8_0H, shapes["o"]), dev.from_numpy(ones),
+                                   dev.from_quantized(host["up"], capi.Q8_0H, shapes["up"]), dev.from_quantized(host["down"], capi.Q8_0H, shapes["down"]),
                                    dev.from_numpy(kv_host), dev.from_numpy(kv_host)))
-    emb = dev.from_quantized(_q8h_weights(V, d, 5), capi.Q8_0H, (V, d))
-    head = dev.from_quantized(_q8h_weights(V, d, 6), capi.Q8_0H, (V, d))
+    emb = dev.from_quantized(_q8h_weights(V, d, 5), capi.Q8_0H, (V, d))          # same table on every rank
+    head = dev.from_quantized(_q8h_weights(V // g, d, 6 + rank), capi.Q8_0H, (V // g, d))
     cfg = DecoderConfig(c["n_layers"], d, H, H, hd, ffn, V, c["max_cache"], hd, 10000.0, 1e-5, capi.Q8_0H)
-    dec = Decoder(dev, cfg, layers, emb, dev.from_numpy(ones), head)
+    comm = None
+    if world > 1:
+        from ratchet_b200.comm import Comm
+        comm = Comm(dev, rank, world, max(d, ffn, V, H * hd), bytes_per_elem=4)
+    dec = Decoder(dev, cfg, layers, emb, dev.from_numpy(ones), head, comm=comm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     tok_host = torch.tensor([int(rng.integers(0, V))], dtype=torch.int32).pin_memory()
     tok_dev = torch.empty(1, dtype=torch.int32, device="cuda")
     tok_dev.copy_(tok_host)
@@ -370,23 +385,36 @@ def phi3_decode_bench(dev, torch, stream, steps, warmup):
 
     for _ in range(warmup):
         step()
+    barrier()
     l0 = dev.launches
     ms = _time_loop(torch, stream, step, steps)
     launches = (dev.launches - l0) // steps
+    barrier()
     for _ in range(3):
         step_e2e()
+    barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
         step_e2e()
+    barrier()
     e2e_s = (time.perf_counter() - t0) / steps
-    b = phi3_decode_bytes(c)
+    dev.sync()     # a flag wait that ran out of time surfaces here
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = (float(v) for v in t.tolist())
+    b = phi3_decode_bytes(c)            # whole model; each rank streams 1/world of the Linear weights and KV
     peak, kind = measured_peak()
-    res = {"metric": "phi3_mini_q8_0_decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "ms_per_token": ms,
+    res = {"metric": "phi3_mini_q8_0_decode_tokens_per_s", "value": 1e3 / ms, "unit": "tokens/s", "n_gpus": world, "ms_per_token": ms,
            "e2e_tokens_per_s": 1.0 / e2e_s, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": V * 2,
            "kernels_per_token": int(launches), "algorithmic_bytes_per_token": b, "achieved_gbs": b / ms / 1e6,
-           "roofline_frac": b / ms / 1e6 / peak, "roofline_tokens_per_s": peak * 1e9 / b, "peak_kind": f"of {kind}",
+           "roofline_frac": b / ms / 1e6 / (peak * world), "roofline_tokens_per_s": world * peak * 1e9 / b, "peak_kind": f"of {kind}",
+           "parallelism": "single GPU" if world == 1 else f"every Linear row-sharded x{world}, attention by heads, 4 fused all-gathers per layer (peer stores over NVLink)",
            "config": {"model": "phi-3-mini shape, random Q8_0H weights", **c, "steps": steps}}
     dec.close()
+    if comm is not None:
+        dist.barrier()
+        comm.close()
     return res
 
 
@@ -526,6 +554,13 @@ def run_ours(args):
         extras["gemv_sweep"] = gemv_sweep(dev, torch, stream)
         extras["q4k_prefill_gemm"] = prefill_gemm_bench(dev, torch, stream)
         extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
+    if world > 1 and not args.rows and not args.no_extras:
+        if comm is not None:            # the GEMV leg's window goes first: one exchange window per rank at a time
+            dist.barrier()
+            comm.close()
+            comm = None
+        extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3), rank=rank,
+                                                  world=world, dist=dist)
     if rank == 0:
         line.update(extras)
         print(json.dumps(line))

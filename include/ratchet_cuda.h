@@ -253,7 +253,7 @@ rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, co
  * o / down = rows [r d/g, (r+1) d/g), gate_up = gate rows then up rows of ffn columns
  * [r f/g, (r+1) f/g), lm_head = rows [r V/g, (r+1) V/g), KV caches for its own kv heads; norms and
  * the embedding table are whole.  `comm` must be a fresh window (rcu_comm_create + every peer
- * imported) with slots of at least 2 * max(d_model, ffn, vocab, n_heads * head_dim) bytes; the decoder
+ * imported) with slots of at least 4 * max(d_model, ffn, vocab, n_heads * head_dim) bytes; the decoder
  * owns its flags from here on.  All ranks must call rcu_decoder_step with the same token, in step;
  * logits and arg-max are complete and identical on every rank.  A peer that stops answering ends
  * each wait after two seconds; the next rcu_sync then returns RCU_ERR_TIMEOUT. */

@@ -116,10 +116,12 @@ def exchange_handles(local: bytes, rank: int, world: int, group=None) -> List[by
 class Comm:
     """One rank's window plus its peers' (``rcu_comm``)."""
 
-    def __init__(self, dev: Device, rank: int, world: int, max_out_elems: int, group=None):
+    def __init__(self, dev: Device, rank: int, world: int, max_out_elems: int, group=None, bytes_per_elem: int = 2):
+        """Slots hold `max_out_elems` elements of `bytes_per_elem` bytes: 2 for the f16 outputs of
+        ``linear``, 4 for a sharded ``Decoder`` (its exchanges carry one tagged word per element)."""
         self.dev, self.rank, self.world = dev, rank, world
         h = C.c_void_p()
-        slot_bytes = (max_out_elems * 2 + 15) // 16 * 16
+        slot_bytes = (max_out_elems * bytes_per_elem + 15) // 16 * 16
         dev.check(dev._lib.rcu_comm_create(dev.handle, rank, world, slot_bytes, C.byref(h)))
         self._h = h
         handle = (C.c_ubyte * 64)()

@@ -36,7 +36,7 @@ struct AttnParams {
     float* partial;                // [H][kSplits][HD + 2]: m, l, unnormalised o
     unsigned int* counters;        // [H], zero between launches
     __half* out;                   // [H * HD]
-    gemvq8::PushInfo push;         // slice_elems > 0: the CTA that completes the last head sends `out` to the peers
+    gemvq8::LLPush ll;             // ll.local != nullptr: the head outputs go to every rank's window instead of `out`
 };
 
 __device__ __forceinline__ float f16r(float v) { return __half2float(__float2half_rn(v)); }
@@ -218,10 +218,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
         float o = 0.f;
 #pragma unroll
         for (int j = 0; j < kSplits; ++j) o = fmaf(__ldcg(hp + j * (HD + 2) + 2 + d), wgt[j], o);
-        p.out[(size_t)h * HD + d] = __float2half_rn(o / L);
+        const __half r = __float2half_rn(o / L);
+        if (p.ll.local) p.ll.put(h * HD + d, r);     // sharded decoder: this rank's heads -> every rank
+        else p.out[(size_t)h * HD + d] = r;
     }
     if (tid == 0) p.counters[h] = 0;                 // ready for the next launch
-    if (p.push.slice_elems > 0) p.push.run();         // sharded decoder: heads of this rank -> every peer
 }
 
 __global__ void set_u32_kernel(uint32_t* p, uint32_t v);
@@ -272,32 +273,16 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const __half* logi
     argmax_advance_body(logits, n, out, d_pos);
 }
 
-// The sharded decoder's last kernel: waits for every rank's slice of the logits, copies the gathered
-// vector to the caller's buffer, takes the arg-max and advances the position and the step counter.
-__global__ void __launch_bounds__(1024) argmax_advance_gathered_kernel(gemvq8::WaitInfo w, const __half* gathered, __half* logits_out,
-                                                                        int n, int32_t* out, uint32_t* d_pos, unsigned int* d_step) {
-    if (w.flags != nullptr) {
-        const int p = threadIdx.x;
-        if (p < w.world && p != w.self) {
-            const unsigned int seq = __ldcg(w.step) * w.per_step + w.idx + 1u;
-            unsigned long long t0;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-            for (;;) {
-                unsigned int v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w.flags + p) : "memory");
-                if ((int)(v - seq) >= 0) break;
-                if (*reinterpret_cast<volatile int*>(w.status) & RCU_DEVFLAG_TIMEOUT) break;
-                unsigned long long t;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                if (t - t0 > 2000000000ull) { atomicOr(w.status, RCU_DEVFLAG_TIMEOUT); break; }
-            }
-        }
-        __syncthreads();
-    }
-    for (int i = threadIdx.x; i < n / 8; i += blockDim.x)
-        reinterpret_cast<uint4*>(logits_out)[i] = __ldcg(reinterpret_cast<const uint4*>(gathered) + i);
+// The sharded decoder's last kernel: takes every rank's slice of the logits from the exchange window
+// (waiting for the words still in flight), writes the gathered vector to the caller's buffer, takes
+// the arg-max and advances the position and the step counter.
+__global__ void __launch_bounds__(1024) argmax_advance_gathered_kernel(gemvq8::LLSource src, __half* logits_out, int n, int32_t* out,
+                                                                        uint32_t* d_pos, unsigned int* d_step) {
+    const uint32_t tag = src.seq.tag();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) logits_out[i] = gemvq8::ll_take(src.words, i, tag, src.status);
     __syncthreads();
     argmax_advance_body(logits_out, n, out, d_pos);
+    __syncthreads();          // every thread has read the step counter (through tag()) before it moves
     if (threadIdx.x == 0) *d_step += 1;
 }
 
@@ -469,19 +454,21 @@ rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_d
     return RCU_OK;
 }
 
-// One decode step with every Linear sharded by output rows over the ranks of `d->comm` and each
-// output all-gathered by the kernel that produces it (gemvq8::PushWrap / the attention kernel's push),
-// consumed after a bounded flag wait in the next kernel's prologue (gemvq8::WaitWrap):
+// One decode step with every Linear sharded by output rows over the ranks of `d->comm`.  Each output
+// vector is all-gathered by the kernel that produces it: results go, element by element, as tagged
+// words into every rank's window (gemvq8::LLPush), and the next kernel's prologue takes them from its
+// own window, waiting for the words still in flight (gemvq8::LL*PrologueH):
 //   qkv rows of this rank's heads -> attention on those heads (its own slice of the KV cache)
-//     -> gather of the head outputs      [slot 1, exchange 2 li]
-//   o rows + residual   -> gather of x   [slot 0, exchange 2 li]
-//   gate/up rows + SiLU -> gather of act [slot 1, exchange 2 li + 1]
-//   down rows + residual-> gather of x   [slot 0, exchange 2 li + 1]
-//   lm_head rows        -> gather of logits [slot 2, one exchange per step]
+//     -> head outputs to all ranks        [slot 1, exchange 2 li]
+//   o rows + residual    -> x to all      [slot 0, exchange 2 li]
+//   gate/up rows + SiLU  -> act to all    [slot 1, exchange 2 li + 1]
+//   down rows + residual -> x to all      [slot 0, exchange 2 li + 1]
+//   lm_head rows         -> logits to all [slot 2, one exchange per step]
 // Every output element is computed by one rank with the arithmetic of the single-GPU step, so the
 // gathered vectors are bit-identical to it.  Slot 0 always holds x: a rank updates its own rows in
-// place and peers overwrite only theirs; a slot is rewritten by a peer only after an exchange that
-// the reader of the previous contents has already signalled.
+// place and peers overwrite only theirs.  A place in a window is rewritten only by an exchange that
+// cannot start before every reader of its previous contents has finished: each exchange needs results
+// from all CTAs of the producing kernel on every rank, and a CTA reads its inputs before it produces.
 rcu_status run_sequence_sharded(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev) {
     rcu_device* dev = d->dev;
     rcu_comm* cm = d->comm;
@@ -490,45 +477,26 @@ rcu_status run_sequence_sharded(rcu_decoder* d, const int32_t* token_dev, void* 
     const int D = (int)c.d_model, HD = (int)c.head_dim, L = (int)c.n_layers;
     const int H = (int)c.n_heads, Hl = H / W, Hkvl = (int)c.n_kv_heads / W;
     const int qkv_nl = (Hl + 2 * Hkvl) * HD, Dl = D / W, ffn = (int)c.ffn, ffnl = ffn / W, Vl = (int)c.vocab / W;
-    __half* slotX = reinterpret_cast<__half*>(cm->local.slot(0));
-    __half* slotA = reinterpret_cast<__half*>(cm->local.slot(1));
-    __half* slotL = reinterpret_cast<__half*>(cm->local.slot(2));
-    auto make_push = [&](int slot, size_t elem_off, int elems, unsigned per_step, unsigned idx, int n_ctas, int ticket) {
-        gemvq8::PushInfo p{};
-        p.y_local = reinterpret_cast<__half*>(cm->local.slot(slot)) + elem_off;
-        p.slice_elems = elems;
-        p.ticket = cm->local.ticket(W, ticket);
+    auto words = [&](const rcu_window::Window& w, int slot) { return reinterpret_cast<uint32_t*>(w.slot(slot)); };
+    auto make_push = [&](int slot, size_t elem_off, unsigned per_step, unsigned idx) {
+        gemvq8::LLPush p{};
+        p.local = words(cm->local, slot) + elem_off;
         p.n_peers = 0;
-        for (int q = 0; q < W; ++q) {
-            if (q == r) continue;
-            p.peer_dst[p.n_peers] = reinterpret_cast<__half*>(cm->peers[q].slot(slot)) + elem_off;
-            p.peer_flag[p.n_peers] = cm->peers[q].flags(slot, W) + r;
-            p.n_peers++;
-        }
-        p.step = d->d_step;
-        p.per_step = per_step;
-        p.idx = idx;
-        p.n_ctas = n_ctas;
+        for (int q = 0; q < W; ++q)
+            if (q != r) p.peer[p.n_peers++] = words(cm->peers[q], slot) + elem_off;
+        p.seq = gemvq8::LLSeq{d->d_step, per_step, idx};
         return p;
     };
-    auto make_wait = [&](int slot, unsigned per_step, unsigned idx) {
-        gemvq8::WaitInfo w{};
-        w.flags = cm->local.flags(slot, W);
-        w.world = W;
-        w.self = r;
-        w.step = d->d_step;
-        w.per_step = per_step;
-        w.idx = idx;
-        w.status = dev->d_status;
-        return w;
+    auto make_src = [&](int slot, unsigned per_step, unsigned idx) {
+        return gemvq8::LLSource{words(cm->local, slot), gemvq8::LLSeq{d->d_step, per_step, idx}, dev->d_status};
     };
-    const unsigned perX = 2u * L, perA = 2u * L;
+    const unsigned per = 2u * L;      // exchanges per step on slot 0 and on slot 1
     rope_table_kernel<<<1, 128, 0, dev->stream>>>(d->scratch.d_pos, logf(c.rope_base), (int)c.rope_dim / 2, d->scratch.rope_tab);
     RCU_LAUNCH_CHECK(dev);
     // embedding: every rank holds the table and gathers the same row into its own x
     rcu_tensor table{c.weight_dt, 2, {c.vocab, c.d_model, 1, 1}, const_cast<void*>(d->tok_embd)};
     rcu_tensor ids{RCU_I32, 1, {1, 1, 1, 1}, const_cast<int32_t*>(token_dev)};
-    rcu_tensor xrow{RCU_F16, 2, {1, c.d_model, 1, 1}, slotX};
+    rcu_tensor xrow{RCU_F16, 2, {1, c.d_model, 1, 1}, d->x};
     rcu_status st;
     if (c.weight_dt == RCU_Q8_0H) {
         st = rcu_index_select(dev, &table, &ids, 0, &xrow);
@@ -540,47 +508,43 @@ rcu_status run_sequence_sharded(rcu_decoder* d, const int32_t* token_dev, void* 
     if (st != RCU_OK) return st;
     for (int li = 0; li < L; ++li) {
         const rcu_decoder_layer& Lw = d->layers[li];
-        gemvq8::WaitInfo wx_prev{};   // x of the previous layer's down projection (layer 0 reads the embedding: no wait)
-        if (li > 0) wx_prev = make_wait(0, perX, 2u * (li - 1) + 1u);
-        st = gemv(dev, c.weight_dt, Lw.qkv,
-                  gemvq8::WaitWrap<gemvq8::RmsNormPrologueH>{{slotX, (const float*)Lw.attn_norm, c.rms_eps}, wx_prev},
-                  gemvq8::PlainEpilogue<__half>{nullptr, d->qkv}, qkv_nl, D);
+        const gemvq8::PlainEpilogue<__half> to_qkv{nullptr, d->qkv};
+        if (li == 0)   // x is the embedding row, an ordinary vector
+            st = gemv(dev, c.weight_dt, Lw.qkv, gemvq8::RmsNormPrologueH{d->x, (const float*)Lw.attn_norm, c.rms_eps}, to_qkv, qkv_nl, D);
+        else
+            st = gemv(dev, c.weight_dt, Lw.qkv,
+                      gemvq8::LLRmsNormPrologueH{make_src(0, per, 2u * (li - 1) + 1u), (const float*)Lw.attn_norm, c.rms_eps}, to_qkv, qkv_nl, D);
         if (st != RCU_OK) return st;
         AttnParams ap{d->qkv, (__half*)Lw.k_cache, (__half*)Lw.v_cache, Hl, Hkvl, (int)c.max_cache, (int)c.rope_dim,
                       d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters,
-                      slotA + (size_t)r * Hl * HD, make_push(1, (size_t)r * Hl * HD, Hl * HD, perA, 2u * li, Hl, 1)};
+                      nullptr, make_push(1, (size_t)r * Hl * HD, per, 2u * li)};
         st = launch_attn(dev, ap, HD, pdl_enabled());
         if (st != RCU_OK) return st;
         {
-            gemvq8::PushWrap<gemvq8::ResidualEpilogueH> epi{{slotX + (size_t)r * Dl, slotX + (size_t)r * Dl},
-                                                           make_push(0, (size_t)r * Dl, Dl, perX, 2u * li, 0, 0)};
-            st = gemv(dev, c.weight_dt, Lw.o, gemvq8::WaitWrap<gemvq8::PlainPrologue<__half>>{{slotA}, make_wait(1, perA, 2u * li)}, epi,
-                           Dl, H * HD);
+            gemvq8::LLResidualEpilogueH epi{li == 0 ? d->x + (size_t)r * Dl : nullptr, words(cm->local, 0) + (size_t)r * Dl,
+                                            make_push(0, (size_t)r * Dl, per, 2u * li)};
+            st = gemv(dev, c.weight_dt, Lw.o, gemvq8::LLPlainPrologueH{make_src(1, per, 2u * li)}, epi, Dl, H * HD);
             if (st != RCU_OK) return st;
         }
         {
-            gemvq8::PushWrap<gemvq8::SiluGateEpilogueH> epi{{slotA + (size_t)r * ffnl}, make_push(1, (size_t)r * ffnl, ffnl, perA, 2u * li + 1u, 0, 0)};
-            st = gemv(dev, c.weight_dt, Lw.gate_up,
-                           gemvq8::WaitWrap<gemvq8::RmsNormPrologueH>{{slotX, (const float*)Lw.ffn_norm, c.rms_eps}, make_wait(0, perX, 2u * li)}, epi,
-                           2 * ffnl, D);
+            gemvq8::LLSiluGateEpilogueH epi{make_push(1, (size_t)r * ffnl, per, 2u * li + 1u)};
+            st = gemv(dev, c.weight_dt, Lw.gate_up, gemvq8::LLRmsNormPrologueH{make_src(0, per, 2u * li), (const float*)Lw.ffn_norm, c.rms_eps},
+                      epi, 2 * ffnl, D);
             if (st != RCU_OK) return st;
         }
         {
-            gemvq8::PushWrap<gemvq8::ResidualEpilogueH> epi{{slotX + (size_t)r * Dl, slotX + (size_t)r * Dl},
-                                                           make_push(0, (size_t)r * Dl, Dl, perX, 2u * li + 1u, 0, 0)};
-            st = gemv(dev, c.weight_dt, Lw.down, gemvq8::WaitWrap<gemvq8::PlainPrologue<__half>>{{slotA}, make_wait(1, perA, 2u * li + 1u)},
-                           epi, Dl, ffn);
+            gemvq8::LLResidualEpilogueH epi{nullptr, words(cm->local, 0) + (size_t)r * Dl, make_push(0, (size_t)r * Dl, per, 2u * li + 1u)};
+            st = gemv(dev, c.weight_dt, Lw.down, gemvq8::LLPlainPrologueH{make_src(1, per, 2u * li + 1u)}, epi, Dl, ffn);
             if (st != RCU_OK) return st;
         }
     }
     {
-        gemvq8::PushWrap<gemvq8::PlainEpilogue<__half>> epi{{nullptr, slotL + (size_t)r * Vl}, make_push(2, (size_t)r * Vl, Vl, 1u, 0u, 0, 0)};
+        gemvq8::LLPlainEpilogueH epi{make_push(2, (size_t)r * Vl, 1u, 0u)};
         st = gemv(dev, c.weight_dt, d->lm_head,
-                       gemvq8::WaitWrap<gemvq8::RmsNormPrologueH>{{slotX, (const float*)d->out_norm, c.rms_eps}, make_wait(0, perX, 2u * (L - 1) + 1u)},
-                       epi, Vl, D);
+                  gemvq8::LLRmsNormPrologueH{make_src(0, per, 2u * (L - 1) + 1u), (const float*)d->out_norm, c.rms_eps}, epi, Vl, D);
         if (st != RCU_OK) return st;
     }
-    argmax_advance_gathered_kernel<<<1, 1024, 0, dev->stream>>>(make_wait(2, 1u, 0u), slotL, (__half*)logits_dev, (int)c.vocab, argmax_dev,
+    argmax_advance_gathered_kernel<<<1, 1024, 0, dev->stream>>>(make_src(2, 1u, 0u), (__half*)logits_dev, (int)c.vocab, argmax_dev,
                                                                  d->scratch.d_pos, d->d_step);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
@@ -635,7 +599,7 @@ rcu_status rcu_decoder_create_sharded(rcu_device* dev, rcu_comm* comm, const rcu
     RCU_REQUIRE(dev, (cfg->d_model / W) % 8 == 0 && cfg->d_model % W == 0 && cfg->ffn % W == 0 && (cfg->ffn / W) % 8 == 0 &&
                          cfg->vocab % W == 0 && (cfg->vocab / W) % 8 == 0 && (cfg->n_heads / W * cfg->head_dim) % 8 == 0,
                 "sharded decoder: d_model, ffn and vocab must split over %u ranks into multiples of 8 rows", W);
-    const size_t need = 2 * (size_t)std::max(std::max(cfg->d_model, cfg->ffn), std::max(cfg->vocab, cfg->n_heads * cfg->head_dim));
+    const size_t need = 4 * (size_t)std::max(std::max(cfg->d_model, cfg->ffn), std::max(cfg->vocab, cfg->n_heads * cfg->head_dim));   // one word per element
     RCU_REQUIRE(dev, comm->local.slot_bytes >= need, "sharded decoder: window slots hold %zu bytes, %zu needed", comm->local.slot_bytes, need);
     rcu_decoder_config local = *cfg;   // per-rank sizes for the shared validation and buffers
     local.n_heads = cfg->n_heads / W;

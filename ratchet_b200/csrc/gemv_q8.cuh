@@ -270,100 +270,129 @@ struct PushEpilogueH {
 };
 
 // ------------------------------------------------------------------------------------------------
-// The same exchange for kernels replayed from a CUDA graph: the sequence number is not a launch
-// argument but step * per_step + idx + 1, with `step` read from device memory (the decoder's step
-// counter), so one captured graph produces a fresh number on every replay.
+// Low-latency exchange of short f16 vectors between the GPUs of a node (the all-gathers of a sharded
+// decode step).  Every element travels as one 32-bit word: the exchange's sequence number in the
+// high half, the f16 bits in the low half.  The producer of an element stores that word straight
+// into its own and every peer's window (an aligned 4-byte store is indivisible); a consumer polls a
+// word until its high half is the number it expects.  No separate flag, no fence, no ticket: the
+// latency of an exchange is one NVLink store, and each producing CTA sends as soon as it has a result.
+// Sequence numbers are (step * per_step + idx + 1) mod 65536 with `step` read from device memory, so a
+// CUDA graph replays with fresh numbers; a word is rewritten by every exchange that uses its place,
+// so the value it held before is always a different number.
 // ------------------------------------------------------------------------------------------------
-struct PushInfo {
-    __half* y_local;               // this rank's slice inside its own full buffer (also the source of the copy)
-    int slice_elems;               // elements in the slice (multiple of 8); 0 = no push
-    unsigned int* ticket;          // zero between launches
-    __half* peer_dst[kMaxPeers];
-    unsigned int* peer_flag[kMaxPeers];
+struct LLSeq {
+    const unsigned int* step;
+    unsigned int per_step, idx;
+    __device__ __forceinline__ uint32_t tag() const { return ((__ldg(step) * per_step + idx + 1u) & 0xFFFFu) << 16; }
+};
+
+struct LLPush {
+    uint32_t* local;               // this rank's window; element u lives at word u (nullptr: not in use)
+    uint32_t* peer[kMaxPeers];     // the same place in each peer's window
     int n_peers;
-    const unsigned int* step;
-    unsigned int per_step, idx;
-    int n_ctas;                    // CTAs that call run() in this launch (ticket target); 0 = every CTA of a 1-D grid
-    // Every thread of every participating CTA calls this after its last store to y_local.
-    __device__ __forceinline__ void run() const {
-        __shared__ int push_is_last;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned int t = atomicAdd(ticket, 1u);
-            push_is_last = (t == (n_ctas > 0 ? (unsigned int)n_ctas : gridDim.x) - 1u);
-        }
-        __syncthreads();
-        if (!push_is_last) return;
-        __threadfence();
-        const uint4* src = reinterpret_cast<const uint4*>(y_local);
-        const int n16 = slice_elems >> 3;
-        for (int p = 0; p < n_peers; ++p) {
-            uint4* dst = reinterpret_cast<uint4*>(peer_dst[p]);
-            for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
-        }
-        __threadfence_system();
-        __syncthreads();
-        const unsigned int seq = __ldcg(step) * per_step + idx + 1u;
-        if ((int)threadIdx.x < n_peers)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag[threadIdx.x]), "r"(seq) : "memory");
-        if (threadIdx.x == 0) *ticket = 0;
+    LLSeq seq;
+    __device__ __forceinline__ void put(int u, __half v) const {
+        const uint32_t word = seq.tag() | (uint32_t)__half_as_ushort(v);
+        local[u] = word;
+#pragma unroll 1
+        for (int p = 0; p < n_peers; ++p) peer[p][u] = word;
     }
 };
 
-template <class Inner> struct PushWrap {
-    static constexpr int UNIT = Inner::UNIT;
-    Inner inner;
-    PushInfo push;
-    __device__ __forceinline__ void store(int u, const float* acc) const { inner.store(u, acc); }
-    __device__ __forceinline__ void finish() const {
-        inner.finish();
-        push.run();
+// Poll word `i` until it carries `tag`.  The wait is bounded in time (two seconds); a wait that runs
+// out, or finds that another one already did, records RCU_DEVFLAG_TIMEOUT and returns what is there.
+__device__ __forceinline__ __half ll_take(const uint32_t* words, int i, uint32_t tag, int* status) {
+    uint32_t w;
+    unsigned long long t0 = 0;
+    for (unsigned int n = 0;; ++n) {
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(w) : "l"(words + i) : "memory");
+        if ((w & 0xFFFF0000u) == tag) break;
+        if ((n & 63u) == 63u) {
+            if (*reinterpret_cast<volatile int*>(status) & RCU_DEVFLAG_TIMEOUT) break;
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 2000000000ull) { atomicOr(status, RCU_DEVFLAG_TIMEOUT); break; }
+        }
     }
-};
+    return __ushort_as_half((unsigned short)(w & 0xFFFFu));
+}
 
-// Consumer side: wait (bounded) until every peer's flag for this exchange has reached the sequence
-// number.  Lane p of the CTA polls peer p's flag in this GPU's own memory; a wait that runs out of its
-// budget, or finds that an earlier wait already did, records RCU_DEVFLAG_TIMEOUT and goes on, so the
-// kernel always ends (the host sees the flag after the step).
-struct WaitInfo {
-    const unsigned int* flags;     // [world] in this rank's window; nullptr = nothing to wait for
-    int world, self;
-    const unsigned int* step;
-    unsigned int per_step, idx;
+struct LLSource {
+    const uint32_t* words;         // this rank's window
+    LLSeq seq;
     int* status;
-    __device__ __forceinline__ void wait() const {
-        if (flags == nullptr) return;
-        const int p = threadIdx.x;
-        if (p < world && p != self) {
-            const unsigned int seq = __ldcg(step) * per_step + idx + 1u;
-            unsigned long long t0;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-            for (;;) {
-                unsigned int v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
-                if ((int)(v - seq) >= 0) break;
-                if (*reinterpret_cast<volatile int*>(status) & RCU_DEVFLAG_TIMEOUT) break;
-                unsigned long long t;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                if (t - t0 > 2000000000ull) {
-                    atomicOr(status, RCU_DEVFLAG_TIMEOUT);
-                    break;
-                }
-            }
-        }
-        // the kThreads staging threads only (a kernel may run extra warps that do not stage)
-        asm volatile("bar.sync 15, %0;" ::"n"(kThreads) : "memory");
+};
+
+// Prologues reading x from an exchange (the plain ones above read an ordinary f16 vector).
+struct LLPlainPrologueH {
+    LLSource src;
+    __device__ __forceinline__ void stage(__half* xs, int K, float* /*scratch*/) const {
+        const uint32_t tag = src.seq.tag();
+        for (int i = threadIdx.x; i < K; i += kThreads) xs[i] = ll_take(src.words, i, tag, src.status);
     }
 };
 
-template <class Inner> struct WaitWrap {
-    Inner inner;
-    WaitInfo w;
-    template <class ActT> __device__ __forceinline__ void stage(ActT* xs, int K, float* scratch) const {
-        w.wait();
-        inner.stage(xs, K, scratch);
+struct LLRmsNormPrologueH {
+    LLSource src;
+    const float* gamma;
+    float eps;
+    __device__ __forceinline__ void stage(__half* xs, int K, float* scratch) const {
+        const uint32_t tag = src.seq.tag();
+        float s2 = 0.f;
+        for (int i = threadIdx.x; i < K; i += kThreads) {
+            const __half h = ll_take(src.words, i, tag, src.status);
+            xs[i] = h;
+            const float v = __half2float(h);
+            s2 = fmaf(v, v, s2);
+        }
+        s2 = warp_sum(s2);
+        if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = s2;
+        asm volatile("bar.sync 15, %0;" ::"n"(kThreads) : "memory");
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) tot += scratch[w];
+        const float rstd = 1.0f / sqrtf(tot / (float)K + eps);
+        for (int i = threadIdx.x; i < K; i += kThreads) xs[i] = __float2half_rn(__half2float(xs[i]) * rstd * __ldg(gamma + i));
     }
+};
+
+// Epilogues sending their slice of the output to every rank (u = row within this rank's shard; the
+// window pointers of LLPush already point at the shard's first element).
+struct LLPlainEpilogueH {
+    static constexpr int UNIT = 1;
+    LLPush out;
+    __device__ __forceinline__ void store(int u, const float* acc) const { out.put(u, __float2half_rn(acc[0])); }
+    __device__ __forceinline__ void finish() const {}
+};
+
+// y = residual + Linear(x) on this rank's rows of x.  The residual is the rank's own rows of the
+// current x: an ordinary f16 vector (`res_plain`, the embedding) or words of the window this epilogue
+// then overwrites in place (`res_words`; they were written by this rank itself in an earlier kernel).
+struct LLResidualEpilogueH {
+    static constexpr int UNIT = 1;
+    const __half* res_plain;
+    const uint32_t* res_words;
+    LLPush out;
+    __device__ __forceinline__ void store(int u, const float* acc) const {
+        const float lin = __half2float(__float2half_rn(acc[0]));
+        const float r = res_plain ? __half2float(__ldcg(res_plain + u))
+                                  : __half2float(__ushort_as_half((unsigned short)(__ldcg(res_words + u) & 0xFFFFu)));
+        out.put(u, __float2half_rn(lin + r));
+    }
+    __device__ __forceinline__ void finish() const {}
+};
+
+struct LLSiluGateEpilogueH {
+    static constexpr int UNIT = 2;
+    LLPush out;
+    __device__ __forceinline__ void store(int u, const float* acc) const {
+        const float gate = __half2float(__float2half_rn(acc[0]));
+        const float up = __half2float(__float2half_rn(acc[1]));
+        const float act = __half2float(__float2half_rn(gate / (1.0f + expf(-gate))));
+        out.put(u, __float2half_rn(up * act));
+    }
+    __device__ __forceinline__ void finish() const {}
 };
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

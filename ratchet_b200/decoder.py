@@ -52,8 +52,8 @@ class Decoder:
     """``comm`` = None: the whole model on one GPU.  With a ``ratchet_b200.comm.Comm`` the step is sharded
     over the comm's ranks (one process per GPU): ``cfg`` still describes the whole model, ``layers`` and
     ``lm_head`` hold this rank's rows (``comm.decoder_shard_ranges``), the KV caches its own heads; the
-    comm must be fresh, with slots of ``max(d_model, ffn, vocab, n_heads * head_dim)`` elements, and every
-    rank must step with the same token."""
+    comm must be fresh, with slots of ``max(d_model, ffn, vocab, n_heads * head_dim)`` elements of 4 bytes
+    (``Comm(..., bytes_per_elem=4)``), and every rank must step with the same token."""
 
     def __init__(self, dev: Device, cfg: DecoderConfig, layers: List[DecoderLayer], tok_embd: Buffer, out_norm: Buffer,
                  lm_head: Buffer, comm=None):

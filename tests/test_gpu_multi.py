@@ -97,7 +97,7 @@ def _decoder_worker(rank, world, port, q):
             ref_logits.append(single.logits.to_numpy().copy())
             ref_tokens.append(int(single.next_token.to_numpy()[0]))
         single.close()
-        comm = Comm(dev, rank, world, max(W["d"], W["ffn"], W["vocab"]))
+        comm = Comm(dev, rank, world, max(W["d"], W["ffn"], W["vocab"]), bytes_per_elem=4)
         sharded = mb.phi3_decoder_sharded(dev, W, prior, comm, max_cache=cache)
         ok, tokens = True, []
         dev.h2d(sharded.token.ptr, np.array([7], np.int32))
