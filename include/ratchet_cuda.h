@@ -284,7 +284,7 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
  * for callers that cannot allocate device memory when they need attention: plug-ins running inside a
  * host framework that owns the device heap, latency-bound serving loops that cannot take the device
  * synchronisation of an allocation, processes that have given all free memory to their KV caches.
- * The split-KV scratch is a fixed 546 KiB array inside the library's device image (held by every GPU
+ * The split-KV scratch is a fixed 2.04 MiB array inside the library's device image (held by every GPU
  * that loads the library until the process exits), which limits this variant to n_heads <= 64 and
  * head_dim <= 128; larger requests return RCU_ERR_INVALID_ARG with a message naming the limit.
  * Same arguments and results as rcu_attn_decode.  The first call on a device looks up the array's

@@ -22,7 +22,8 @@
 
 namespace {
 
-constexpr int kSplits = 16;        // CTAs per head (split-KV)
+constexpr int kTile = 64;           // cache positions per CTA (split-KV): CTA s of a head owns positions [64 s, 64 s + 64)
+constexpr int kMaxSplits = 128;     // the merge step assigns one thread per split: max_cache <= 8192
 constexpr int kAttnThreads = 128;
 
 struct AttnParams {
@@ -33,7 +34,7 @@ struct AttnParams {
     const uint32_t* d_pos;         // entries already in the cache = position of this token
     const float* rope_tab;         // cos[rope_dim/2] then sin[rope_dim/2] for this position
     float scale;
-    float* partial;                // [H][kSplits][HD + 2]: m, l, unnormalised o
+    float* partial;                // [H][ceil(max_cache / kTile)][HD + 2]: m, l, unnormalised o
     unsigned int* counters;        // [H], zero between launches
     __half* out;                   // [H * HD]
     gemvq8::LLPush ll;             // ll.local != nullptr: the head outputs go to every rank's window instead of `out`
@@ -70,12 +71,29 @@ __device__ __forceinline__ void rope_into(const __half* in, const float* tab, in
     }
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+
+inline int attn_splits(int max_cache) { return (max_cache + kTile - 1) / kTile; }
+
+// grid = (H, ceil(max_cache / kTile)): fixed by the cache capacity, so a captured launch stays valid as
+// the position advances; CTAs whose tile lies beyond the current position leave at once (heads are
+// the fast grid axis, so the working CTAs of all heads are scheduled before the idle ones).  A working CTA
+// starts by copying its 64 cached K rows and V rows into shared memory with 16-byte asynchronous
+// copies (every byte it will read is requested before anything is computed), applies RoPE to q (and to
+// the new k row if the tile holds the current position) while they arrive, then computes scores,
+// tile-local softmax statistics and the unnormalised output from shared memory.  The last CTA of a
+// head to finish merges the head's partial results.
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p) {
-    extern __shared__ float sc[];                   // scores / probabilities of this CTA's chunk
+    __shared__ __align__(16) __half Ks[kTile * HD];
+    __shared__ __align__(16) __half Vs[kTile * HD];
+    __shared__ float sc[kTile];                     // scores / probabilities of this CTA's tile
     __shared__ float q_s[HD], k_s[HD], v_s[HD];
     __shared__ float red[kAttnThreads / 32 + 2];
     __shared__ float o_s[4][HD];
+    __shared__ float wgt_s[kMaxSplits];
     __shared__ unsigned int ticket;
 
     // everything this kernel reads was produced by kernels before it in the stream; the kernel after
@@ -83,36 +101,56 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     gemvq8::pdl_launch_dependents();
     gemvq8::pdl_wait();
     const int tid = threadIdx.x;
-    const int h = blockIdx.y, s = blockIdx.x;
-    const int group = p.H / p.Hkv;
-    const int kvh = h / group;
+    const int h = blockIdx.x, s = blockIdx.y;
     const int P = (int)*p.d_pos;
     const int T = P + 1;
-    const int chunk = (T + kSplits - 1) / kSplits;
-    const int begin = s * chunk;
-    const int end = min(T, begin + chunk);
-    const int n = max(0, end - begin);
+    const int nsplit = (T + kTile - 1) / kTile;
+    if (s >= nsplit) return;
+    const int group = p.H / p.Hkv;
+    const int kvh = h / group;
+    const int begin = s * kTile;
+    const int end = min(T, begin + kTile);
+    const int n = end - begin;
     __half* K = p.kc + (size_t)kvh * p.max_cache * HD;
     __half* V = p.vc + (size_t)kvh * p.max_cache * HD;
+    const bool owns_new = P < end;                  // P >= begin always holds for a working CTA's last tile
+    {
+        // rows already in the cache: [begin, min(end, P))
+        const int n_cached = min(end, P) - begin;
+        const int vecs = n_cached * (HD / 8);
+        const uint4* kg = reinterpret_cast<const uint4*>(K + (size_t)begin * HD);
+        const uint4* vg = reinterpret_cast<const uint4*>(V + (size_t)begin * HD);
+        for (int i = tid; i < vecs; i += kAttnThreads) {
+            cp_async16(reinterpret_cast<uint4*>(Ks) + i, kg + i);
+            cp_async16(reinterpret_cast<uint4*>(Vs) + i, vg + i);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     const __half* q_in = p.qkv + (size_t)h * HD;
     const __half* k_in = p.qkv + (size_t)(p.H + kvh) * HD;
     const __half* v_in = p.qkv + (size_t)(p.H + p.Hkv + kvh) * HD;
-    const bool owns_new = begin <= P && P < end;
-
     rope_into<HD>(q_in, p.rope_tab, p.rope_dim, q_s);
     if (owns_new) {
         rope_into<HD>(k_in, p.rope_tab, p.rope_dim, k_s);
         for (int i = tid; i < HD; i += kAttnThreads) v_s[i] = __half2float(v_in[i]);
     }
     __syncthreads();
-    if (owns_new && h % group == 0) {
-        // Cache op (ops/cache.rs:73-103): the new row goes into the cache for later steps; this step
-        // reads it from shared memory.
+    if (owns_new) {
+        // Cache op (ops/cache.rs:73-103): the new row goes into the cache for later steps (written by
+        // one of the query heads that share this kv head); this step reads it from the tile.
+        const int row = P - begin;
         for (int i = tid; i < HD; i += kAttnThreads) {
-            K[(size_t)P * HD + i] = __float2half_rn(k_s[i]);
-            V[(size_t)P * HD + i] = __float2half_rn(v_s[i]);
+            const __half kh = __float2half_rn(k_s[i]), vh = __float2half_rn(v_s[i]);   // exact: both hold f16 values
+            Ks[row * HD + i] = kh;
+            Vs[row * HD + i] = vh;
+            if (h % group == 0) {
+                K[(size_t)P * HD + i] = kh;
+                V[(size_t)P * HD + i] = vh;
+            }
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
 
     // ---- phase 1: scores. four lanes per position, HD/4 dims each
     constexpr int DPL = HD / 4;
@@ -120,26 +158,21 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     float qreg[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) qreg[i] = q_s[sub * DPL + i];
-    for (int pl0 = 0; pl0 < n; pl0 += kAttnThreads / 4) {
+#pragma unroll
+    for (int pl0 = 0; pl0 < kTile; pl0 += kAttnThreads / 4) {
         const int pl = pl0 + (tid >> 2);
-        const int pos = begin + pl;
         float dot = 0.f;
         if (pl < n) {
-            if (pos == P) {
+            const uint4* kp = reinterpret_cast<const uint4*>(Ks + pl * HD + sub * DPL);
 #pragma unroll
-                for (int i = 0; i < DPL; ++i) dot = fmaf(qreg[i], k_s[sub * DPL + i], dot);
-            } else {
-                const uint4* kp = reinterpret_cast<const uint4*>(K + (size_t)pos * HD + sub * DPL);
+            for (int v = 0; v < DPL / 8; ++v) {
+                const uint4 w = kp[v];
+                const __half2* hp = reinterpret_cast<const __half2*>(&w);
 #pragma unroll
-                for (int v = 0; v < DPL / 8; ++v) {
-                    const uint4 w = ld_stream_v4(kp + v);
-                    const __half2* hp = reinterpret_cast<const __half2*>(&w);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = __half22float2(hp[j]);
-                        dot = fmaf(qreg[v * 8 + 2 * j], f.x, dot);
-                        dot = fmaf(qreg[v * 8 + 2 * j + 1], f.y, dot);
-                    }
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(hp[j]);
+                    dot = fmaf(qreg[v * 8 + 2 * j], f.x, dot);
+                    dot = fmaf(qreg[v * 8 + 2 * j + 1], f.y, dot);
                 }
             }
         }
@@ -149,19 +182,18 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     }
     __syncthreads();
 
-    // ---- phase 2: chunk-local softmax statistics
-    float m = -INFINITY;
-    for (int j = tid; j < n; j += kAttnThreads) m = fmaxf(m, sc[j]);
+    // ---- phase 2: tile-local softmax statistics
+    float m = tid < n ? sc[tid] : -INFINITY;        // kTile <= kAttnThreads
     m = warp_max(m);
     if ((tid & 31) == 0) red[tid >> 5] = m;
     __syncthreads();
     m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     __syncthreads();
     float l = 0.f;
-    for (int j = tid; j < n; j += kAttnThreads) {
-        const float e = expf(sc[j] - m);
-        sc[j] = e;
-        l += e;
+    if (tid < n) {
+        const float e = expf(sc[tid] - m);
+        sc[tid] = e;
+        l = e;
     }
     l = warp_sum(l);
     if ((tid & 31) == 0) red[tid >> 5] = l;
@@ -172,13 +204,11 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     constexpr int HP = HD / 2;
     constexpr int G = kAttnThreads / HP;            // position groups (2 for HD 96/128, 4 for 64)
     const int dp = tid % HP, g = tid / HP;
-    float2 acc = make_float2(0.f, 0.f);
     if (g < G) {
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 4
         for (int j = g; j < n; j += G) {
-            const int pos = begin + j;
-            float2 v;
-            if (pos == P) v = make_float2(v_s[2 * dp], v_s[2 * dp + 1]);
-            else v = __half22float2(*reinterpret_cast<const __half2*>(V + (size_t)pos * HD + 2 * dp));
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(Vs + j * HD + 2 * dp));
             const float pj = sc[j];
             acc.x = fmaf(pj, v.x, acc.x);
             acc.y = fmaf(pj, v.y, acc.y);
@@ -187,7 +217,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
         o_s[g][2 * dp + 1] = acc.y;
     }
     __syncthreads();
-    float* part = p.partial + ((size_t)h * kSplits + s) * (HD + 2);
+    const int max_splits = gridDim.y;
+    float* part = p.partial + ((size_t)h * max_splits + s) * (HD + 2);
     for (int d = tid; d < HD; d += kAttnThreads) {
         float o = 0.f;
 #pragma unroll
@@ -196,28 +227,35 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     }
     if (tid == 0) { part[0] = m; part[1] = l; }
 
-    // ---- combine: the last CTA of this head to finish merges the kSplits partials
+    // ---- combine: the last working CTA of this head to finish merges the head's partials
     __threadfence();
     __syncthreads();
     if (tid == 0) ticket = atomicAdd(&p.counters[h], 1u);
     __syncthreads();
-    if (ticket != kSplits - 1) return;
+    if (ticket != (unsigned int)nsplit - 1) return;
     __threadfence();
-    const float* hp = p.partial + (size_t)h * kSplits * (HD + 2);
-    float M = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kSplits; ++j) M = fmaxf(M, __ldcg(hp + j * (HD + 2)));
-    float L = 0.f;
-    float wgt[kSplits];
-#pragma unroll
-    for (int j = 0; j < kSplits; ++j) {
-        wgt[j] = expf(__ldcg(hp + j * (HD + 2)) - M);
-        L = fmaf(__ldcg(hp + j * (HD + 2) + 1), wgt[j], L);
+    const float* hp = p.partial + (size_t)h * max_splits * (HD + 2);
+    // one thread per split fetches its (m, l): all loads of the merge are in flight together
+    float mj = -INFINITY, lj = 0.f;
+    if (tid < nsplit) {
+        mj = __ldcg(hp + tid * (HD + 2));
+        lj = __ldcg(hp + tid * (HD + 2) + 1);
     }
+    float M = warp_max(mj);
+    if ((tid & 31) == 0) red[tid >> 5] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    const float wj = tid < nsplit ? expf(mj - M) : 0.f;
+    if (tid < nsplit) wgt_s[tid] = wj;
+    float L = warp_sum(lj * wj);
+    if ((tid & 31) == 0) red[tid >> 5] = L;
+    __syncthreads();
+    L = red[0] + red[1] + red[2] + red[3];
     for (int d = tid; d < HD; d += kAttnThreads) {
         float o = 0.f;
-#pragma unroll
-        for (int j = 0; j < kSplits; ++j) o = fmaf(__ldcg(hp + j * (HD + 2) + 2 + d), wgt[j], o);
+#pragma unroll 8
+        for (int j = 0; j < nsplit; ++j) o = fmaf(__ldcg(hp + j * (HD + 2) + 2 + d), wgt_s[j], o);
         const __half r = __float2half_rn(o / L);
         if (p.ll.local) p.ll.put(h * HD + d, r);     // sharded decoder: this rank's heads -> every rank
         else p.out[(size_t)h * HD + d] = r;
@@ -229,10 +267,11 @@ __global__ void set_u32_kernel(uint32_t* p, uint32_t v);
 __global__ void argmax_advance_kernel(const __half* logits, int n, int32_t* out, uint32_t* d_pos);
 
 rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool overlap = false) {
-    const int chunk_max = (p.max_cache + kSplits - 1) / kSplits;
-    const size_t smem = (size_t)chunk_max * sizeof(float);
+    if (attn_splits(p.max_cache) > kMaxSplits)
+        return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "attn_decode: max_cache %d exceeds %d positions", p.max_cache, kMaxSplits * kTile);
+    const size_t smem = 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kSplits, p.H);
+    cfg.gridDim = dim3(p.H, attn_splits(p.max_cache));
     cfg.blockDim = dim3(kAttnThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = dev->stream;
@@ -372,8 +411,8 @@ void free_attn_scratch(void* p) {
     delete s;
 }
 
-rcu_status alloc_attn_scratch(rcu_device* dev, int H, int head_dim, AttnScratch* s) {
-    s->partial_floats = (size_t)H * kSplits * (head_dim + 2);
+rcu_status alloc_attn_scratch(rcu_device* dev, int H, int head_dim, int max_cache, AttnScratch* s) {
+    s->partial_floats = (size_t)H * attn_splits(max_cache) * (head_dim + 2);
     RCU_CUDA(dev, cudaMalloc(&s->partial, s->partial_floats * sizeof(float)));
     RCU_CUDA(dev, cudaMalloc(&s->counters, (size_t)H * sizeof(unsigned int)));
     RCU_CUDA(dev, cudaMalloc(&s->rope_tab, 256 * sizeof(float)));
@@ -571,7 +610,7 @@ rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, co
     d->tok_embd = tok_embd;
     d->out_norm = out_norm;
     d->lm_head = lm_head;
-    rcu_status st = alloc_attn_scratch(dev, (int)cfg->n_heads, (int)cfg->head_dim, &d->scratch);
+    rcu_status st = alloc_attn_scratch(dev, (int)cfg->n_heads, (int)cfg->head_dim, (int)cfg->max_cache, &d->scratch);
     const size_t qkv_n = (size_t)(cfg->n_heads + 2 * cfg->n_kv_heads) * cfg->head_dim;
     const size_t act_n = std::max<size_t>(cfg->ffn, 2 * (size_t)cfg->d_model);   // also stages an f32 embedding row
     if (st == RCU_OK && (cudaMalloc(&d->x, cfg->d_model * sizeof(__half)) != cudaSuccess || cudaMalloc(&d->qkv, qkv_n * sizeof(__half)) != cudaSuccess ||
@@ -704,10 +743,10 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
         auto it = table.find(dev);
         if (it != table.end()) s = it->second;
     }
-    const size_t need = (size_t)n_heads * kSplits * (head_dim + 2);
+    const size_t need = (size_t)n_heads * attn_splits((int)max_cache) * (head_dim + 2);
     if (!s || s->partial_floats < need) {
         AttnScratch* ns = new AttnScratch();
-        rcu_status st = alloc_attn_scratch(dev, (int)n_heads, (int)head_dim, ns);
+        rcu_status st = alloc_attn_scratch(dev, (int)n_heads, (int)head_dim, (int)max_cache, ns);
         if (st != RCU_OK) { delete ns; return st; }
         {
             std::lock_guard<std::mutex> lock(mu);
@@ -742,7 +781,7 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
 // the device), or a process that has already handed all free memory to its KV caches.  For them
 // the split-KV scratch (per-head partial results, the per-head completion counters, the RoPE table
 // and the position word) lives in a fixed array in the library's own device image instead of in
-// memory obtained at run time.  Every GPU that loads the library carries these 546 KiB until the
+// memory obtained at run time.  Every GPU that loads the library carries these 2.04 MiB until the
 // process exits.
 //
 // The array is shared by every call on a device and keeps what the previous call left in it: the
@@ -753,8 +792,9 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
 namespace {
 constexpr int kStaticMaxHeads = 64;
 constexpr int kStaticMaxHeadDim = 128;
-constexpr size_t kStaticPartialFloats = (size_t)kStaticMaxHeads * kSplits * (kStaticMaxHeadDim + 2);
-constexpr size_t kStaticPartialBytes = kStaticPartialFloats * sizeof(float);                      // 532480
+constexpr int kStaticMaxSplits = 64;                                                              // 64 heads of 128 dims up to 4096 cached positions
+constexpr size_t kStaticPartialFloats = (size_t)kStaticMaxHeads * kStaticMaxSplits * (kStaticMaxHeadDim + 2);
+constexpr size_t kStaticPartialBytes = kStaticPartialFloats * sizeof(float);                      // 2129920
 constexpr size_t kStaticCountersOff = kStaticPartialBytes;                                        // 64 x u32
 constexpr size_t kStaticRopeOff = kStaticCountersOff + 256;                                       // 256 x f32
 constexpr size_t kStaticPosOff = kStaticRopeOff + 256 * sizeof(float);
@@ -778,6 +818,9 @@ extern "C" rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, v
                 "attn_decode_static: n_heads %u exceeds the built-in scratch (at most %d heads); use rcu_attn_decode", n_heads, kStaticMaxHeads);
     RCU_REQUIRE(dev, head_dim <= (uint32_t)kStaticMaxHeadDim,
                 "attn_decode_static: head_dim %u exceeds the built-in scratch (at most %d); use rcu_attn_decode", head_dim, kStaticMaxHeadDim);
+    RCU_REQUIRE(dev, attn_splits((int)max_cache) <= kStaticMaxSplits,
+                "attn_decode_static: max_cache %u exceeds the built-in scratch (at most %d positions); use rcu_attn_decode", max_cache,
+                kStaticMaxSplits * kTile);
     RCU_REQUIRE(dev, n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attn_decode_static: n_heads must be a multiple of n_kv_heads");
     RCU_REQUIRE(dev, position < max_cache, "attn_decode_static: position %u outside the cache (%u)", position, max_cache);
     RCU_REQUIRE(dev, rope_dim % 2 == 0 && rope_dim <= head_dim && rope_dim <= 256, "attn_decode_static: bad rope_dim");
