@@ -18,6 +18,7 @@
 #include <cstdlib>
 
 #include "comm.cuh"
+#include "decode_persist.cuh"
 #include "gemv_q8_bulk.cuh"
 
 namespace {
@@ -438,6 +439,12 @@ struct rcu_decoder {
     // sharded across the GPUs of a node (null: single GPU).  cfg holds the whole model's sizes.
     rcu_comm* comm = nullptr;
     unsigned int* d_step = nullptr;       // steps taken, on the device: the exchanges' sequence numbers derive from it
+    // all layers as one persistent cooperative kernel (decode_persist.cuh); null when not in use
+    persist::LayerW* d_layers = nullptr;
+    unsigned int* d_bar = nullptr;
+    int persist_grid = 0;
+    size_t persist_smem = 0;
+    persist::Params pp;
     // captured step
     cudaGraphExec_t graph_exec = nullptr;
     const int32_t* cap_token = nullptr;
@@ -446,6 +453,107 @@ struct rcu_decoder {
 };
 
 namespace {
+
+template <int HD>
+rcu_status launch_persistent_hd(rcu_decoder* d) {
+    rcu_device* dev = d->dev;
+    RCU_CUDA(dev, cudaMemsetAsync(d->d_bar, 0, sizeof(unsigned int), dev->stream));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(d->persist_grid);
+    cfg.blockDim = dim3(gemvq8::kThreads);
+    cfg.dynamicSmemBytes = d->persist_smem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;      // every CTA resident at once: the grid barriers need it
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, persist::decode_layers_kernel<HD>, d->pp));
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
+rcu_status launch_persistent_layers(rcu_decoder* d) {
+    switch (d->cfg.head_dim) {
+        case 64: return launch_persistent_hd<64>(d);
+        case 96: return launch_persistent_hd<96>(d);
+        default: return launch_persistent_hd<128>(d);
+    }
+}
+
+// K split of a GEMV on the persistent grid: the rule of gemvq8::plan for a fixed number of warps.
+int persistent_ksplit(int n_units, int unit, int K, int grid) {
+    const long long groups = (n_units + 4 / unit - 1) / (4 / unit);
+    const long long warps = (long long)grid * gemvq8::kWarps;
+    int ks = 1;
+    while (ks < 8 && groups * ks * 2 <= warps && (K / (ks * 2)) >= 1024) ks *= 2;
+    return ks;
+}
+
+template <int HD>
+bool persistent_fit(rcu_decoder* d, size_t smem, int* ctas_per_sm) {
+    auto kern = persist::decode_layers_kernel<HD>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, gemvq8::kThreads, smem) != cudaSuccess) return false;
+    *ctas_per_sm = n;
+    return n >= 1;
+}
+
+// Sets up the persistent-kernel path when asked for (RCU_DECODE_PERSISTENT=1) and this model and device
+// allow it (Q8_0H weights, one GPU, cooperative launch, cache short enough for the merge step).  It is
+// not the default: with a grid barrier of about 2 us between phases it measures slower than the
+// kernel-per-phase step, whose kernels hand over through programmatic dependent launch.
+void setup_persistent(rcu_decoder* d) {
+    rcu_device* dev = d->dev;
+    const rcu_decoder_config& c = d->cfg;
+    const char* env = std::getenv("RCU_DECODE_PERSISTENT");
+    if (!env || std::atoi(env) == 0) return;
+    if (c.weight_dt != RCU_Q8_0H || d->comm) return;
+    if ((c.max_cache + persist::kTile - 1) / persist::kTile > persist::kMaxSplits) return;
+    int coop = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal) != cudaSuccess || !coop) return;
+    const int HD = (int)c.head_dim;
+    const size_t kmax = std::max(std::max((size_t)c.d_model, (size_t)c.ffn), (size_t)c.n_heads * HD);
+    const size_t attn_bytes = HD == 64 ? sizeof(persist::AttnShared<64>) : HD == 96 ? sizeof(persist::AttnShared<96>) : sizeof(persist::AttnShared<128>);
+    const size_t smem = ((kmax * 2 + gemvq8::kWarps * 4 * sizeof(float) + 15) & ~(size_t)15) + 2 * attn_bytes;
+    if (smem > (size_t)dev->smem_optin) return;
+    int per_sm = 0;
+    const bool ok = HD == 64 ? persistent_fit<64>(d, smem, &per_sm) : HD == 96 ? persistent_fit<96>(d, smem, &per_sm) : persistent_fit<128>(d, smem, &per_sm);
+    if (!ok) { cudaGetLastError(); return; }
+    per_sm = std::min(per_sm, 2);
+    const int grid = per_sm * dev->sm_count;
+    std::vector<persist::LayerW> host(c.n_layers);
+    const uint64_t D = c.d_model, F = c.ffn, Q = (uint64_t)(c.n_heads + 2 * c.n_kv_heads) * HD, A = (uint64_t)c.n_heads * HD;
+    auto scales = [](const void* w, uint64_t n) { return (const __half*)((const char*)w + align256(n)); };
+    for (uint32_t i = 0; i < c.n_layers; ++i) {
+        const rcu_decoder_layer& L = d->layers[i];
+        host[i] = persist::LayerW{(const int8_t*)L.qkv, scales(L.qkv, Q * D), (const int8_t*)L.o, scales(L.o, D * A),
+                                  (const int8_t*)L.gate_up, scales(L.gate_up, 2 * F * D), (const int8_t*)L.down, scales(L.down, D * F),
+                                  (const float*)L.attn_norm, (const float*)L.ffn_norm, (__half*)L.k_cache, (__half*)L.v_cache};
+    }
+    if (cudaMalloc(&d->d_layers, host.size() * sizeof(persist::LayerW)) != cudaSuccess || cudaMalloc(&d->d_bar, sizeof(unsigned int)) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    cudaMemcpyAsync(d->d_layers, host.data(), host.size() * sizeof(persist::LayerW), cudaMemcpyHostToDevice, dev->stream);
+    cudaStreamSynchronize(dev->stream);     // `host` goes out of scope
+    persist::Params& p = d->pp;
+    p.layers = d->d_layers;
+    p.n_layers = (int)c.n_layers; p.D = (int)D; p.H = (int)c.n_heads; p.Hkv = (int)c.n_kv_heads; p.ffn = (int)F;
+    p.max_cache = (int)c.max_cache; p.rope_dim = (int)c.rope_dim;
+    p.eps = c.rms_eps; p.scale = 1.0f / sqrtf((float)HD);
+    p.x = d->x; p.qkv = d->qkv; p.attn = d->attn; p.act = d->act;
+    p.d_pos = d->scratch.d_pos; p.rope_tab = d->scratch.rope_tab;
+    p.partial = d->scratch.partial; p.counters = d->scratch.counters;
+    p.bar = d->d_bar; p.status = dev->d_status;
+    p.ks_qkv = persistent_ksplit((int)Q, 1, (int)D, grid);
+    p.ks_o = persistent_ksplit((int)D, 1, (int)A, grid);
+    p.ks_gu = persistent_ksplit((int)F, 2, (int)D, grid);
+    p.ks_down = persistent_ksplit((int)D, 1, (int)F, grid);
+    d->persist_grid = grid;
+    d->persist_smem = smem;
+}
 
 rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev) {
     rcu_device* dev = d->dev;
@@ -468,22 +576,27 @@ rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_d
         if (st == RCU_OK) st = rcu_cast(dev, &x32, &xrow);
     }
     if (st != RCU_OK) return st;
-    for (uint32_t li = 0; li < c.n_layers; ++li) {
-        const rcu_decoder_layer& L = d->layers[li];
-        st = gemv(dev, c.weight_dt, L.qkv, gemvq8::RmsNormPrologueH{d->x, (const float*)L.attn_norm, c.rms_eps},
-                  gemvq8::PlainEpilogue<__half>{nullptr, d->qkv}, qkv_n, D);
+    if (d->persist_grid > 0) {
+        st = launch_persistent_layers(d);
         if (st != RCU_OK) return st;
-        AttnParams ap{d->qkv, (__half*)L.k_cache, (__half*)L.v_cache, H, Hkv, (int)c.max_cache, (int)c.rope_dim,
-                      d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters, d->attn};
-        st = launch_attn(dev, ap, HD, pdl_enabled());
-        if (st != RCU_OK) return st;
-        st = gemv(dev, c.weight_dt, L.o, gemvq8::PlainPrologue<__half>{d->attn}, gemvq8::ResidualEpilogueH{d->x, d->x}, D, H * HD);
-        if (st != RCU_OK) return st;
-        st = gemv(dev, c.weight_dt, L.gate_up, gemvq8::RmsNormPrologueH{d->x, (const float*)L.ffn_norm, c.rms_eps},
-                  gemvq8::SiluGateEpilogueH{d->act}, 2 * (int)c.ffn, D);
-        if (st != RCU_OK) return st;
-        st = gemv(dev, c.weight_dt, L.down, gemvq8::PlainPrologue<__half>{d->act}, gemvq8::ResidualEpilogueH{d->x, d->x}, D, (int)c.ffn);
-        if (st != RCU_OK) return st;
+    } else {
+        for (uint32_t li = 0; li < c.n_layers; ++li) {
+            const rcu_decoder_layer& L = d->layers[li];
+            st = gemv(dev, c.weight_dt, L.qkv, gemvq8::RmsNormPrologueH{d->x, (const float*)L.attn_norm, c.rms_eps},
+                      gemvq8::PlainEpilogue<__half>{nullptr, d->qkv}, qkv_n, D);
+            if (st != RCU_OK) return st;
+            AttnParams ap{d->qkv, (__half*)L.k_cache, (__half*)L.v_cache, H, Hkv, (int)c.max_cache, (int)c.rope_dim,
+                          d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters, d->attn};
+            st = launch_attn(dev, ap, HD, pdl_enabled());
+            if (st != RCU_OK) return st;
+            st = gemv(dev, c.weight_dt, L.o, gemvq8::PlainPrologue<__half>{d->attn}, gemvq8::ResidualEpilogueH{d->x, d->x}, D, H * HD);
+            if (st != RCU_OK) return st;
+            st = gemv(dev, c.weight_dt, L.gate_up, gemvq8::RmsNormPrologueH{d->x, (const float*)L.ffn_norm, c.rms_eps},
+                      gemvq8::SiluGateEpilogueH{d->act}, 2 * (int)c.ffn, D);
+            if (st != RCU_OK) return st;
+            st = gemv(dev, c.weight_dt, L.down, gemvq8::PlainPrologue<__half>{d->act}, gemvq8::ResidualEpilogueH{d->x, d->x}, D, (int)c.ffn);
+            if (st != RCU_OK) return st;
+        }
     }
     st = gemv(dev, c.weight_dt, d->lm_head, gemvq8::RmsNormPrologueH{d->x, (const float*)d->out_norm, c.rms_eps},
               gemvq8::PlainEpilogue<__half>{nullptr, (__half*)logits_dev}, (int)c.vocab, D);
@@ -618,6 +731,7 @@ rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, co
                          cudaMalloc(&d->act, act_n * sizeof(__half)) != cudaSuccess))
         st = rcu_fail(dev, RCU_ERR_OOM, "decoder: activation buffers");
     if (st != RCU_OK) { rcu_decoder_destroy(d); return st; }
+    setup_persistent(d);
     st = rcu_decoder_set_position(d, 0);
     if (st != RCU_OK) { rcu_decoder_destroy(d); return st; }
     *out = d;
@@ -647,6 +761,7 @@ rcu_status rcu_decoder_create_sharded(rcu_device* dev, rcu_comm* comm, const rcu
     rcu_status st = rcu_decoder_create(dev, &local, layers, tok_embd, out_norm, lm_head, &d);
     if (st != RCU_OK) return st;
     d->cfg = *cfg;                     // the step works from the whole model's sizes
+    d->persist_grid = 0;               // the sharded step runs kernel by kernel
     DevGuard g(dev->ordinal);
     if (cudaMalloc(&d->d_step, sizeof(unsigned int)) != cudaSuccess) {
         rcu_decoder_destroy(d);
@@ -673,6 +788,8 @@ void rcu_decoder_destroy(rcu_decoder* d) {
     cudaFree(d->attn);
     cudaFree(d->act);
     cudaFree(d->d_step);
+    cudaFree(d->d_layers);
+    cudaFree(d->d_bar);
     delete d;
 }
 

@@ -294,8 +294,9 @@ struct LLPush {
     __device__ __forceinline__ void put(int u, __half v) const {
         const uint32_t word = seq.tag() | (uint32_t)__half_as_ushort(v);
         local[u] = word;
-#pragma unroll 1
-        for (int p = 0; p < n_peers; ++p) peer[p][u] = word;
+#pragma unroll
+        for (int p = 0; p < kMaxPeers; ++p)      // unrolled with a predicate: the pointers stay in the parameter bank
+            if (p < n_peers) peer[p][u] = word;
     }
 };
 

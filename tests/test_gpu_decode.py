@@ -92,7 +92,8 @@ def test_decoder_matches_reference_graph(dev):
         assert int(got.argmax()) == int(ref.argmax())
         assert dec.position == 1025 + step
         tok = int(ref.argmax())
-    assert dec.kernels_per_step == 2 + 5 * 2 + 2
+    # all layers as one persistent kernel (rope table, embedding gather, layers, lm_head, arg-max), or five kernels per layer
+    assert dec.kernels_per_step in (5, 2 + 5 * 2 + 2)
     # caches hold the same appended rows
     for li in range(2):
         k_ref = ref_model.kv_cache[li].k_cache.to_numpy()[0, :, 1024:1027].astype(np.float32)
