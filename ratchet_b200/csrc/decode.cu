@@ -17,6 +17,8 @@
 #include <cmath>
 #include <cstdlib>
 
+#include <cooperative_groups.h>
+
 #include "comm.cuh"
 #include "decode_persist.cuh"
 #include "gemv_q8_bulk.cuh"
@@ -26,6 +28,7 @@ namespace {
 constexpr int kTile = 64;           // cache positions per CTA (split-KV): CTA s of a head owns positions [64 s, 64 s + 64)
 constexpr int kMaxSplits = 128;     // the merge step assigns one thread per split: max_cache <= 8192
 constexpr int kAttnThreads = 128;
+constexpr int kClusterCtas = 16;    // CTAs of one head in the cluster variant of the attention kernel
 
 struct AttnParams {
     const __half* qkv;
@@ -264,10 +267,246 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnParams p)
     if (tid == 0) p.counters[h] = 0;                 // ready for the next launch
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same attention with one thread-block cluster per head.
+//
+// Sixteen CTAs form the cluster of a head (grid = (H, 16), cluster dimension (1, 16)).  The 64-position
+// tiles of the cache go round-robin to the cluster's CTAs; a warp owns 16 positions of a tile and keeps
+// them in registers: the K rows as (position, half row) per lane, the V rows as four features per lane,
+// every load requested before anything is computed and nothing staged in shared memory.  Scores need one
+// shuffle, softmax statistics are per warp (online across tiles), the weighted V sum needs no
+// cross-lane reduction.  The four warps of a CTA merge through shared memory, the sixteen CTAs of the
+// head through distributed shared memory: each writes its (m, l, o) into the leader CTA's shared
+// memory, one cluster barrier, and the leader writes the head's output.  No global scratch, no
+// fence, no atomic ticket, no second pass over partial results in L2.
+// ------------------------------------------------------------------------------------------------
+template <int HD, bool CLUSTER>
+__global__ void __launch_bounds__(kAttnThreads) attn_cluster_kernel(AttnParams p) {
+    namespace cg = cooperative_groups;
+    constexpr int KV4 = HD / 16;                    // 16-byte K loads per lane: half a row
+    constexpr int VL = HD / 4;                      // lanes that hold V features (four each)
+    __shared__ float q_s[HD], k_s[HD], v_s[HD];
+    __shared__ float wm[4], wl[4];
+    __shared__ float wo[4][HD];
+    __shared__ float cl_m[kClusterCtas], cl_l[kClusterCtas];     // leader only: one slot per CTA of the cluster
+    __shared__ float cl_o[kClusterCtas][HD];
+
+    gemvq8::pdl_launch_dependents();
+    gemvq8::pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x;
+    // CLUSTER: tiles go round-robin to the 16 CTAs of the head's cluster.  Otherwise CTA y owns tile y
+    // alone and the head's CTAs merge through global memory (last one to finish, as attn_decode_kernel).
+    constexpr int kStride = CLUSTER ? kClusterCtas : (1 << 30);
+    const int rank = CLUSTER ? (int)cg::this_cluster().block_rank() : (int)blockIdx.y;
+    const int P = (int)*p.d_pos;
+    const int T = P + 1;
+    const int ntiles = (T + kTile - 1) / kTile;
+    if (!CLUSTER && rank >= ntiles) return;
+    const int group = p.H / p.Hkv;
+    const int kvh = h / group;
+    const __half* K = p.kc + (size_t)kvh * p.max_cache * HD;
+    const __half* V = p.vc + (size_t)kvh * p.max_cache * HD;
+    __half* Kw = p.kc + (size_t)kvh * p.max_cache * HD;
+    __half* Vw = p.vc + (size_t)kvh * p.max_cache * HD;
+    const int pos16 = lane >> 1, half = lane & 1;
+
+    // first tile's loads go out before RoPE (they do not depend on it)
+    uint4 kreg[KV4];
+    uint2 vreg[16];
+    auto request = [&](int tile) {
+        const int base = tile * kTile + warp * 16;
+        const int kp = base + pos16;
+        if (kp < P) {
+            const uint4* src = reinterpret_cast<const uint4*>(K + (size_t)kp * HD + half * (HD / 2));
+#pragma unroll
+            for (int v = 0; v < KV4; ++v) kreg[v] = ld_stream_v4(src + v);
+        }
+        if (lane < VL) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (base + j < P) vreg[j] = *reinterpret_cast<const uint2*>(V + (size_t)(base + j) * HD + 4 * lane);
+        }
+    };
+    int tile = rank;
+    if (tile < ntiles) request(tile);
+
+    const bool owns_new = CLUSTER ? (ntiles - 1) % kClusterCtas == rank : ntiles - 1 == rank;   // the CTA whose tile holds position P
+    rope_into<HD>(p.qkv + (size_t)h * HD, p.rope_tab, p.rope_dim, q_s);
+    if (owns_new) {
+        rope_into<HD>(p.qkv + (size_t)(p.H + kvh) * HD, p.rope_tab, p.rope_dim, k_s);
+        for (int i = tid; i < HD; i += kAttnThreads) v_s[i] = __half2float(p.qkv[(size_t)(p.H + p.Hkv + kvh) * HD + i]);
+    }
+    __syncthreads();
+    if (owns_new && h % group == 0) {
+        // Cache op (ops/cache.rs:73-103): the new row goes into the cache for later steps
+        for (int i = tid; i < HD; i += kAttnThreads) {
+            Kw[(size_t)P * HD + i] = __float2half_rn(k_s[i]);
+            Vw[(size_t)P * HD + i] = __float2half_rn(v_s[i]);
+        }
+    }
+
+    // running softmax state of this warp; o: four features per lane
+    float m_run = -INFINITY, l_run = 0.f;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+    for (; tile < ntiles; tile += kStride) {
+        const int base = tile * kTile + warp * 16;
+        const int kp = base + pos16;
+        // ---- scores of the warp's 16 positions
+        float dot = 0.f;
+        if (kp < T) {
+            const float* q = q_s + half * (HD / 2);
+            if (kp == P) {
+                const float* kk = k_s + half * (HD / 2);
+#pragma unroll 8
+                for (int i = 0; i < HD / 2; ++i) dot = fmaf(q[i], kk[i], dot);
+            } else {
+#pragma unroll
+                for (int v = 0; v < KV4; ++v) {
+                    const __half2* hp = reinterpret_cast<const __half2*>(&kreg[v]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(hp[j]);
+                        dot = fmaf(q[v * 8 + 2 * j], f.x, dot);
+                        dot = fmaf(q[v * 8 + 2 * j + 1], f.y, dot);
+                    }
+                }
+            }
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        const float sc = kp < T ? f16r(dot * p.scale) : -INFINITY;     // `.mul(scale).cast(f16)` (attn.rs:142-146)
+        const float m_tile = warp_max(sc);
+        if (m_tile > -INFINITY) {                                       // the warp has at least one position in this tile
+            const float m_new = fmaxf(m_run, m_tile);
+            const float corr = expf(m_run - m_new);                     // 0 on the first tile (m_run = -inf)
+            const float pe = kp < T ? expf(sc - m_new) : 0.f;
+            l_run = l_run * corr + 0.5f * warp_sum(pe);                 // every position sits in two lanes
+            o0 *= corr; o1 *= corr; o2 *= corr; o3 *= corr;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float pj = __shfl_sync(0xffffffffu, pe, 2 * j);
+                if (lane < VL && base + j < T) {
+                    float2 a, b;
+                    if (base + j == P) {
+                        a = make_float2(v_s[4 * lane], v_s[4 * lane + 1]);
+                        b = make_float2(v_s[4 * lane + 2], v_s[4 * lane + 3]);
+                    } else {
+                        a = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].x));
+                        b = __half22float2(*reinterpret_cast<const __half2*>(&vreg[j].y));
+                    }
+                    o0 = fmaf(pj, a.x, o0); o1 = fmaf(pj, a.y, o1);
+                    o2 = fmaf(pj, b.x, o2); o3 = fmaf(pj, b.y, o3);
+                }
+            }
+            m_run = m_new;
+        }
+        if (CLUSTER && tile + kClusterCtas < ntiles) request(tile + kClusterCtas);
+    }
+
+    // ---- the four warps of the CTA
+    if (lane == 0) { wm[warp] = m_run; wl[warp] = l_run; }
+    if (lane < VL) {
+        wo[warp][4 * lane] = o0; wo[warp][4 * lane + 1] = o1;
+        wo[warp][4 * lane + 2] = o2; wo[warp][4 * lane + 3] = o3;
+    }
+    __syncthreads();
+    const float Mc = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+    float e[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) e[w] = wm[w] > -INFINITY ? expf(wm[w] - Mc) : 0.f;
+    if (!CLUSTER) {
+        // ---- this CTA's partial to global memory; the last CTA of the head to finish merges
+        __shared__ unsigned int ticket;
+        __shared__ float wgt_s[kMaxSplits];
+        __shared__ float red[4];
+        const int max_splits = gridDim.y;
+        float* part = p.partial + ((size_t)h * max_splits + rank) * (HD + 2);
+        if (tid == 0) {
+            part[0] = Mc;
+            part[1] = wl[0] * e[0] + wl[1] * e[1] + wl[2] * e[2] + wl[3] * e[3];
+        }
+        for (int d = tid; d < HD; d += kAttnThreads) part[2 + d] = wo[0][d] * e[0] + wo[1][d] * e[1] + wo[2][d] * e[2] + wo[3][d] * e[3];
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) ticket = atomicAdd(&p.counters[h], 1u);
+        __syncthreads();
+        if (ticket != (unsigned int)ntiles - 1) return;
+        __threadfence();
+        const float* hp = p.partial + (size_t)h * max_splits * (HD + 2);
+        float mj = -INFINITY, lj = 0.f;
+        if (tid < ntiles) {
+            mj = __ldcg(hp + tid * (HD + 2));
+            lj = __ldcg(hp + tid * (HD + 2) + 1);
+        }
+        float M = warp_max(mj);
+        if (lane == 0) red[warp] = M;
+        __syncthreads();
+        M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        __syncthreads();
+        const float wj = tid < ntiles ? expf(mj - M) : 0.f;
+        if (tid < ntiles) wgt_s[tid] = wj;
+        float L = warp_sum(lj * wj);
+        if (lane == 0) red[warp] = L;
+        __syncthreads();
+        L = red[0] + red[1] + red[2] + red[3];
+        for (int d = tid; d < HD; d += kAttnThreads) {
+            float o = 0.f;
+#pragma unroll 8
+            for (int j = 0; j < ntiles; ++j) o = fmaf(__ldcg(hp + j * (HD + 2) + 2 + d), wgt_s[j], o);
+            const __half r = __float2half_rn(o / L);
+            if (p.ll.local) p.ll.put(h * HD + d, r);
+            else p.out[(size_t)h * HD + d] = r;
+        }
+        if (tid == 0) p.counters[h] = 0;
+        return;
+    }
+    // ---- into the leader's shared memory
+    cg::cluster_group cluster = cg::this_cluster();
+    float* lm = cluster.map_shared_rank(cl_m, 0);
+    float* ll_ = cluster.map_shared_rank(cl_l, 0);
+    float* lo = cluster.map_shared_rank(&cl_o[0][0], 0);
+    if (tid == 0) {
+        lm[rank] = Mc;
+        ll_[rank] = wl[0] * e[0] + wl[1] * e[1] + wl[2] * e[2] + wl[3] * e[3];
+    }
+    for (int d = tid; d < HD; d += kAttnThreads)
+        lo[rank * HD + d] = wo[0][d] * e[0] + wo[1][d] * e[1] + wo[2][d] * e[2] + wo[3][d] * e[3];
+    cluster.sync();
+    if (rank != 0) return;
+    float M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < kClusterCtas; ++c) M = fmaxf(M, cl_m[c]);
+    float L = 0.f;
+    float wgt[kClusterCtas];
+#pragma unroll
+    for (int c = 0; c < kClusterCtas; ++c) {
+        wgt[c] = cl_m[c] > -INFINITY ? expf(cl_m[c] - M) : 0.f;
+        L = fmaf(cl_l[c], wgt[c], L);
+    }
+    for (int d = tid; d < HD; d += kAttnThreads) {
+        float o = 0.f;
+#pragma unroll
+        for (int c = 0; c < kClusterCtas; ++c) o = fmaf(cl_o[c][d], wgt[c], o);
+        const __half r = __float2half_rn(o / L);
+        if (p.ll.local) p.ll.put(h * HD + d, r);     // sharded decoder: this rank's heads -> every rank
+        else p.out[(size_t)h * HD + d] = r;
+    }
+}
+
 __global__ void set_u32_kernel(uint32_t* p, uint32_t v);
 __global__ void argmax_advance_kernel(const __half* logits, int n, int32_t* out, uint32_t* d_pos);
 
-rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool overlap = false) {
+// Which attention kernel serves a step at `position` cached entries: 2 = one 16-CTA cluster per head with
+// tiles in registers (fastest while a CTA has at most two tiles, i.e. up to 2048 positions), 0 = one CTA
+// per tile staged in shared memory (more CTAs in flight for long caches), 1 = tiles in registers with the
+// global merge.  RCU_ATTN_KERNEL forces one.
+int attn_variant(uint32_t position) {
+    static const int forced = [] { const char* e = std::getenv("RCU_ATTN_KERNEL"); return e ? std::atoi(e) : -1; }();
+    if (forced >= 0) return forced;
+    return position + 1 <= 2u * kClusterCtas * kTile ? 2 : 0;
+}
+
+rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool overlap, int which) {
     if (attn_splits(p.max_cache) > kMaxSplits)
         return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "attn_decode: max_cache %d exceeds %d positions", p.max_cache, kMaxSplits * kTile);
     const size_t smem = 0;
@@ -293,11 +532,51 @@ rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool 
         cudaFuncSetAttribute(set_u32_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         carveout_set = true;
     }
+    if (head_dim != 64 && head_dim != 96 && head_dim != 128)
+        return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "attn_decode: head_dim %d (supported: 64, 96, 128)", head_dim);
+    static bool cluster_ok = true;
+    if (which == 1 || (which == 2 && cluster_ok)) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(attn_cluster_kernel<64, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(attn_cluster_kernel<96, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaFuncSetAttribute(attn_cluster_kernel<128, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            attr_set = true;
+        }
+        cudaLaunchConfig_t cc = cfg;
+        cudaLaunchAttribute ca[2];
+        int na = 0;
+        if (which == 2) {
+            cc.gridDim = dim3(p.H, kClusterCtas);
+            ca[na].id = cudaLaunchAttributeClusterDimension;
+            ca[na].val.clusterDim.x = 1;
+            ca[na].val.clusterDim.y = kClusterCtas;
+            ca[na].val.clusterDim.z = 1;
+            ++na;
+        }
+        if (overlap) ca[na++] = attr[0];
+        cc.attrs = ca;
+        cc.numAttrs = na;
+        cudaError_t e;
+        if (which == 2)
+            e = head_dim == 64 ? cudaLaunchKernelEx(&cc, attn_cluster_kernel<64, true>, p)
+                : head_dim == 96 ? cudaLaunchKernelEx(&cc, attn_cluster_kernel<96, true>, p)
+                                 : cudaLaunchKernelEx(&cc, attn_cluster_kernel<128, true>, p);
+        else
+            e = head_dim == 64 ? cudaLaunchKernelEx(&cc, attn_cluster_kernel<64, false>, p)
+                : head_dim == 96 ? cudaLaunchKernelEx(&cc, attn_cluster_kernel<96, false>, p)
+                                 : cudaLaunchKernelEx(&cc, attn_cluster_kernel<128, false>, p);
+        if (e == cudaSuccess) {
+            RCU_LAUNCH_CHECK(dev);
+            return RCU_OK;
+        }
+        cudaGetLastError();          // clusters of 16 not available here: use the staged kernel from now on
+        cluster_ok = false;
+    }
     switch (head_dim) {
         case 64: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, p)); break;
         case 96: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<96>, p)); break;
-        case 128: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, p)); break;
-        default: return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "attn_decode: head_dim %d (supported: 64, 96, 128)", head_dim);
+        default: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, p)); break;
     }
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
@@ -319,7 +598,19 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const __half* logi
 __global__ void __launch_bounds__(1024) argmax_advance_gathered_kernel(gemvq8::LLSource src, __half* logits_out, int n, int32_t* out,
                                                                         uint32_t* d_pos, unsigned int* d_step) {
     const uint32_t tag = src.seq.tag();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) logits_out[i] = gemvq8::ll_take(src.words, i, tag, src.status);
+    const int nvec = n >> 2;                     // n % 8 == 0 (checked at creation)
+    for (int i = threadIdx.x; i < nvec; i += 2 * blockDim.x) {
+        const bool second = i + (int)blockDim.x < nvec;
+        uint4 a = gemvq8::ll_load4(src.words + 4 * i);
+        uint4 b = a;
+        if (second) b = gemvq8::ll_load4(src.words + 4 * (i + blockDim.x));
+        gemvq8::ll_wait4(src.words, i, tag, src.status, a);
+        reinterpret_cast<uint2*>(logits_out)[i] = gemvq8::ll_pack4(a);
+        if (second) {
+            gemvq8::ll_wait4(src.words, i + blockDim.x, tag, src.status, b);
+            reinterpret_cast<uint2*>(logits_out)[i + blockDim.x] = gemvq8::ll_pack4(b);
+        }
+    }
     __syncthreads();
     argmax_advance_body(logits_out, n, out, d_pos);
     __syncthreads();          // every thread has read the step counter (through tag()) before it moves
@@ -450,6 +741,7 @@ struct rcu_decoder {
     const int32_t* cap_token = nullptr;
     void* cap_logits = nullptr;
     int32_t* cap_argmax = nullptr;
+    int cap_variant = -1;                 // attention kernel the captured step launches (it depends on the cached length)
 };
 
 namespace {
@@ -587,7 +879,7 @@ rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_d
             if (st != RCU_OK) return st;
             AttnParams ap{d->qkv, (__half*)L.k_cache, (__half*)L.v_cache, H, Hkv, (int)c.max_cache, (int)c.rope_dim,
                           d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters, d->attn};
-            st = launch_attn(dev, ap, HD, pdl_enabled());
+            st = launch_attn(dev, ap, HD, pdl_enabled(), attn_variant(d->position));
             if (st != RCU_OK) return st;
             st = gemv(dev, c.weight_dt, L.o, gemvq8::PlainPrologue<__half>{d->attn}, gemvq8::ResidualEpilogueH{d->x, d->x}, D, H * HD);
             if (st != RCU_OK) return st;
@@ -670,7 +962,7 @@ rcu_status run_sequence_sharded(rcu_decoder* d, const int32_t* token_dev, void* 
         AttnParams ap{d->qkv, (__half*)Lw.k_cache, (__half*)Lw.v_cache, Hl, Hkvl, (int)c.max_cache, (int)c.rope_dim,
                       d->scratch.d_pos, d->scratch.rope_tab, 1.0f / sqrtf((float)HD), d->scratch.partial, d->scratch.counters,
                       nullptr, make_push(1, (size_t)r * Hl * HD, per, 2u * li)};
-        st = launch_attn(dev, ap, HD, pdl_enabled());
+        st = launch_attn(dev, ap, HD, pdl_enabled(), attn_variant(d->position));
         if (st != RCU_OK) return st;
         {
             gemvq8::LLResidualEpilogueH epi{li == 0 ? d->x + (size_t)r * Dl : nullptr, words(cm->local, 0) + (size_t)r * Dl,
@@ -820,7 +1112,8 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
         st = d->comm ? run_sequence_sharded(d, token_dev, logits_dev, argmax_dev) : run_sequence(d, token_dev, logits_dev, argmax_dev);
         d->kernels_per_step = (uint32_t)(dev->launches - l0);
     } else {
-        if (!d->graph_exec || d->cap_token != token_dev || d->cap_logits != logits_dev || d->cap_argmax != argmax_dev) {
+        if (!d->graph_exec || d->cap_token != token_dev || d->cap_logits != logits_dev || d->cap_argmax != argmax_dev ||
+            d->cap_variant != attn_variant(d->position)) {
             if (d->graph_exec) { cudaGraphExecDestroy(d->graph_exec); d->graph_exec = nullptr; }
             cudaGraph_t graph = nullptr;
             const uint64_t l0 = dev->launches;
@@ -834,6 +1127,7 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
             cudaGraphDestroy(graph);
             if (e != cudaSuccess) return rcu_fail(dev, RCU_ERR_CUDA, "decoder: graph instantiation failed: %s", cudaGetErrorString(e));
             d->cap_token = token_dev; d->cap_logits = logits_dev; d->cap_argmax = argmax_dev;
+            d->cap_variant = attn_variant(d->position);
         }
         RCU_CUDA(dev, cudaGraphLaunch(d->graph_exec, dev->stream));
         dev->launches += d->kernels_per_step;
@@ -884,7 +1178,7 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
     RCU_LAUNCH_CHECK(dev);
     AttnParams ap{(const __half*)qkv, (__half*)k_cache, (__half*)v_cache, (int)n_heads, (int)n_kv_heads, (int)max_cache, (int)rope_dim,
                   s->d_pos, s->rope_tab, 1.0f / sqrtf((float)head_dim), s->partial, s->counters, (__half*)out};
-    return launch_attn(dev, ap, (int)head_dim);
+    return launch_attn(dev, ap, (int)head_dim, false, attn_variant(position));
 }
 
 }  // extern "C"
@@ -966,5 +1260,5 @@ extern "C" rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, v
     RCU_LAUNCH_CHECK(dev);
     AttnParams ap{(const __half*)qkv, (__half*)k_cache, (__half*)v_cache, (int)n_heads, (int)n_kv_heads, (int)max_cache, (int)rope_dim,
                   d_pos, rope_tab, 1.0f / sqrtf((float)head_dim), partial, counters, (__half*)out};
-    return launch_attn(dev, ap, (int)head_dim);
+    return launch_attn(dev, ap, (int)head_dim, false, attn_variant(position));
 }

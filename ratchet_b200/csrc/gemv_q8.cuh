@@ -300,14 +300,22 @@ struct LLPush {
     }
 };
 
-// Poll word `i` until it carries `tag`.  The wait is bounded in time (two seconds); a wait that runs
-// out, or finds that another one already did, records RCU_DEVFLAG_TIMEOUT and returns what is there.
-__device__ __forceinline__ __half ll_take(const uint32_t* words, int i, uint32_t tag, int* status) {
-    uint32_t w;
+// Four consecutive words at once (16-byte aligned): each word is still written by one indivisible
+// 4-byte store, so the vector load may see any mix of old and new words but never a torn one.
+__device__ __forceinline__ uint4 ll_load4(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool ll_ready4(const uint4& v, uint32_t tag) {
+    return (((v.x ^ tag) | (v.y ^ tag) | (v.z ^ tag) | (v.w ^ tag)) & 0xFFFF0000u) == 0u;
+}
+// Re-polls `v` (words 4 i .. 4 i + 3) until all four carry `tag`.  The wait is bounded in time (two
+// seconds); a wait that runs out, or finds that another one already did, records RCU_DEVFLAG_TIMEOUT and
+// goes on with what is there.
+__device__ __forceinline__ void ll_wait4(const uint32_t* words, int i, uint32_t tag, int* status, uint4& v) {
     unsigned long long t0 = 0;
-    for (unsigned int n = 0;; ++n) {
-        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(w) : "l"(words + i) : "memory");
-        if ((w & 0xFFFF0000u) == tag) break;
+    for (unsigned int n = 0; !ll_ready4(v, tag); ++n) {
         if ((n & 63u) == 63u) {
             if (*reinterpret_cast<volatile int*>(status) & RCU_DEVFLAG_TIMEOUT) break;
             unsigned long long t;
@@ -315,8 +323,12 @@ __device__ __forceinline__ __half ll_take(const uint32_t* words, int i, uint32_t
             if (t0 == 0) t0 = t;
             else if (t - t0 > 2000000000ull) { atomicOr(status, RCU_DEVFLAG_TIMEOUT); break; }
         }
+        v = ll_load4(words + 4 * i);
     }
-    return __ushort_as_half((unsigned short)(w & 0xFFFFu));
+}
+// the four f16 values of four words, packed
+__device__ __forceinline__ uint2 ll_pack4(const uint4& v) {
+    return make_uint2((v.x & 0xFFFFu) | (v.y << 16), (v.z & 0xFFFFu) | (v.w << 16));
 }
 
 struct LLSource {
@@ -325,12 +337,27 @@ struct LLSource {
     int* status;
 };
 
-// Prologues reading x from an exchange (the plain ones above read an ordinary f16 vector).
+// Prologues reading x from an exchange (the plain ones above read an ordinary f16 vector).  A thread
+// requests two groups of four words before it checks the first: a trip to L2 costs most of a
+// microsecond, and the words that are already there (usually all of them) need no second look.
 struct LLPlainPrologueH {
     LLSource src;
     __device__ __forceinline__ void stage(__half* xs, int K, float* /*scratch*/) const {
         const uint32_t tag = src.seq.tag();
-        for (int i = threadIdx.x; i < K; i += kThreads) xs[i] = ll_take(src.words, i, tag, src.status);
+        const int nvec = K >> 2;
+        uint2* dst = reinterpret_cast<uint2*>(xs);
+        for (int i = threadIdx.x; i < nvec; i += 2 * kThreads) {
+            const bool second = i + kThreads < nvec;
+            uint4 a = ll_load4(src.words + 4 * i);
+            uint4 b = a;
+            if (second) b = ll_load4(src.words + 4 * (i + kThreads));
+            ll_wait4(src.words, i, tag, src.status, a);
+            dst[i] = ll_pack4(a);
+            if (second) {
+                ll_wait4(src.words, i + kThreads, tag, src.status, b);
+                dst[i + kThreads] = ll_pack4(b);
+            }
+        }
     }
 };
 
@@ -338,14 +365,33 @@ struct LLRmsNormPrologueH {
     LLSource src;
     const float* gamma;
     float eps;
+    __device__ __forceinline__ static float sumsq4(const uint2& v, float s2) {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        s2 = fmaf(f0.x, f0.x, s2); s2 = fmaf(f0.y, f0.y, s2);
+        s2 = fmaf(f1.x, f1.x, s2); s2 = fmaf(f1.y, f1.y, s2);
+        return s2;
+    }
     __device__ __forceinline__ void stage(__half* xs, int K, float* scratch) const {
         const uint32_t tag = src.seq.tag();
+        const int nvec = K >> 2;
+        uint2* dst = reinterpret_cast<uint2*>(xs);
         float s2 = 0.f;
-        for (int i = threadIdx.x; i < K; i += kThreads) {
-            const __half h = ll_take(src.words, i, tag, src.status);
-            xs[i] = h;
-            const float v = __half2float(h);
-            s2 = fmaf(v, v, s2);
+        for (int i = threadIdx.x; i < nvec; i += 2 * kThreads) {
+            const bool second = i + kThreads < nvec;
+            uint4 a = ll_load4(src.words + 4 * i);
+            uint4 b = a;
+            if (second) b = ll_load4(src.words + 4 * (i + kThreads));
+            ll_wait4(src.words, i, tag, src.status, a);
+            const uint2 pa = ll_pack4(a);
+            dst[i] = pa;
+            s2 = sumsq4(pa, s2);
+            if (second) {
+                ll_wait4(src.words, i + kThreads, tag, src.status, b);
+                const uint2 pb = ll_pack4(b);
+                dst[i + kThreads] = pb;
+                s2 = sumsq4(pb, s2);
+            }
         }
         s2 = warp_sum(s2);
         if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = s2;

@@ -101,6 +101,32 @@ def test_decoder_matches_reference_graph(dev):
         assert rel_err(k_dev, k_ref) < 1e-2
 
 
+def test_decoder_across_the_attention_kernel_switch(dev):
+    """The attention kernel changes with the cached length (one cluster per head up to 2048 positions,
+    one CTA per 64-position tile beyond): a narrow one-layer model stepping from 2046 to 2050 cached
+    positions, from a stream of its own so that the steps replay (and re-capture) a CUDA graph."""
+    import torch
+    from ratchet_b200 import Device
+    stream = torch.cuda.Stream()
+    sdev = Device(0, stream=stream.cuda_stream)
+    try:
+        W = mb.phi3_weights(9, n_layers=1, d=512, n_heads=8, ffn=1024, vocab=4096, quant="q8h")
+        ref_model = mb.phi3_model(OTensor, None, W, 2046, np.float16)
+        dec = mb.phi3_decoder(sdev, W, 2046)
+        tok = 5
+        for step in range(5):
+            ref = ref_model.schedule(OTensor.from_data(np.array([[tok]], np.int32))).full().to_numpy().reshape(-1)
+            ref_model.kv_cache.update(1)
+            got = dec.step(tok).astype(np.float32).reshape(-1)
+            assert rel_err(got, ref) < 1e-2, f"step {step} (position {2046 + step})"
+            assert int(got.argmax()) == int(ref.argmax())
+            tok = int(ref.argmax())
+        assert dec.position == 2051
+        dec.close()
+    finally:
+        sdev.close()
+
+
 def test_decoder_greedy_loop_on_device(dev):
     """Greedy generation without a host round trip: the arg-max id feeds the next step on the device;
     the result equals stepping from the host with the logits' arg-max."""
