@@ -365,33 +365,29 @@ struct LLRmsNormPrologueH {
     LLSource src;
     const float* gamma;
     float eps;
-    __device__ __forceinline__ static float sumsq4(const uint2& v, float s2) {
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-        s2 = fmaf(f0.x, f0.x, s2); s2 = fmaf(f0.y, f0.y, s2);
-        s2 = fmaf(f1.x, f1.x, s2); s2 = fmaf(f1.y, f1.y, s2);
-        return s2;
-    }
     __device__ __forceinline__ void stage(__half* xs, int K, float* scratch) const {
         const uint32_t tag = src.seq.tag();
         const int nvec = K >> 2;
         uint2* dst = reinterpret_cast<uint2*>(xs);
-        float s2 = 0.f;
         for (int i = threadIdx.x; i < nvec; i += 2 * kThreads) {
             const bool second = i + kThreads < nvec;
             uint4 a = ll_load4(src.words + 4 * i);
             uint4 b = a;
             if (second) b = ll_load4(src.words + 4 * (i + kThreads));
             ll_wait4(src.words, i, tag, src.status, a);
-            const uint2 pa = ll_pack4(a);
-            dst[i] = pa;
-            s2 = sumsq4(pa, s2);
+            dst[i] = ll_pack4(a);
             if (second) {
                 ll_wait4(src.words, i + kThreads, tag, src.status, b);
-                const uint2 pb = ll_pack4(b);
-                dst[i + kThreads] = pb;
-                s2 = sumsq4(pb, s2);
+                dst[i + kThreads] = ll_pack4(b);
             }
+        }
+        asm volatile("bar.sync 15, %0;" ::"n"(kThreads) : "memory");
+        // the sum of squares runs over shared memory in the element order of RmsNormPrologueH, so that a
+        // sharded step normalises with exactly the factor of the single-GPU step
+        float s2 = 0.f;
+        for (int i = threadIdx.x; i < K; i += kThreads) {
+            const float v = __half2float(xs[i]);
+            s2 = fmaf(v, v, s2);
         }
         s2 = warp_sum(s2);
         if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = s2;
