@@ -1,0 +1,250 @@
+// f32 Linear on the tensor cores with f32-level accuracy (split-TF32):
+//   out[M, N] = X[M, K] . W[N, K]^T (+ bias), everything f32.
+//
+// ratchet runs f32 models (Phi-2 and Whisper checkpoints as shipped, ops/matmul/gemm.rs) and its CPU
+// device, the parity target, accumulates f32 products (cpu/gemm.rs); the bar for f32 ops is 1e-4.  A
+// TF32 tensor-core product keeps 10 mantissa bits per operand, which alone misses that bar, so each
+// operand is split into two TF32 values, x = hi + lo with hi = x truncated to TF32 and lo = x - hi
+// (exact in f32), and three products are accumulated in tensor memory:
+//   hi_a hi_b + hi_a lo_b + lo_a hi_b      (lo_a lo_b, below 2^-22 of the result, is dropped).
+// The tensor core adds into its f32 accumulator with truncation: every accumulating MMA loses up to
+// one unit in the last place of the running sum, always toward zero, which over K/8 k-steps measures
+// about 1.3e-8 * K of the result.  Two things keep that below the bar for the K of real layers (up to
+// 10240): the two small products go to an accumulator of their own (their sum is 2^-11 of the main one,
+// and so are its truncation errors), and the main products rotate over kMainAcc accumulators, which the
+// epilogue adds up with ordinary rounded f32 additions.
+//
+// Structure as gemm_tc.cu: TMA brings 128 x 32 (activations) and BN x 32 (weights) f32 tiles,
+// 128-byte swizzled, into a shared-memory ring; eight converting warps rewrite each raw tile in place
+// as its hi part and write the lo part to a twin tile at the same swizzled offsets (so no swizzle
+// arithmetic is needed); one thread issues twelve tcgen05.mma kind::tf32 (K = 8) per stage; four warps
+// read the f32 accumulators from tensor memory, add the bias and store.  Every wait is bounded.
+#include <cstdlib>
+
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int TK32 = 32;                 // K per stage: 32 f32 = 128 bytes = one swizzle row
+constexpr int kConvWarps = 8;
+constexpr int kMainAcc = 3;               // accumulators the hi x hi products rotate over; one more takes the small products
+constexpr int kThreadsF32 = kThreadsTc + kConvWarps * 32;
+
+// 32-bit instruction descriptor, kind::tf32: TF32 A and B (both K-major), f32 D, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
+    return (1u << 4)                      // D format f32
+           | (2u << 7) | (2u << 10)       // A, B format TF32
+           | (0u << 15) | (0u << 16)      // A, B K-major
+           | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreadsF32, 1)
+gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ bias,
+                   float* __restrict__ out, int M, int N, int K, int* status) {
+    constexpr int A_BYTES = TM * TK32 * 4;        // 16 KiB
+    constexpr int B_BYTES = BN * TK32 * 4;
+    constexpr int RAW = A_BYTES + B_BYTES;        // hi tiles (A then B); the lo tiles follow in the same order
+    constexpr int STAGE = 2 * RAW;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* raw_full = empty + STAGES;
+    uint64_t* accum_bar = raw_full + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * BN;
+    const int nk = (K + TK32 - 1) / TK32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], kConvWarps);
+            mbar_init(&empty[s], 1);
+            mbar_init(&raw_full[s], 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // (kMainAcc + 1) accumulators of BN f32 columns: 512 columns for BN = 128, 256 for BN = 64
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(4 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < nk; ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) break;
+                unsigned char* st = smem + s * STAGE;
+                mbar_expect_tx(&raw_full[s], RAW);
+                tma_load_2d(st, &xmap, it * TK32, m0, &raw_full[s]);
+                tma_load_2d(st + A_BYTES, &wmap, it * TK32, n0, &raw_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_tf32(TM, BN);
+            for (int it = 0; it < nk; ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, status)) break;
+                tc_fence_after();
+                unsigned char* st = smem + s * STAGE;
+                const uint64_t a_hi = umma_desc_sw128(st), b_hi = umma_desc_sw128(st + A_BYTES);
+                const uint64_t a_lo = umma_desc_sw128(st + RAW), b_lo = umma_desc_sw128(st + RAW + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TK32 / 8; ++k) {
+                    // 8 f32 = 32 bytes inside the 128-byte swizzle row: +2 in 16-byte units
+                    const int kk = it * (TK32 / 8) + k;
+                    const uint32_t corr = tmem_base + (uint32_t)(kMainAcc * BN);
+                    umma_tf32(corr, a_lo + 2 * k, b_hi + 2 * k, idesc, kk > 0 ? 1u : 0u);
+                    umma_tf32(corr, a_hi + 2 * k, b_lo + 2 * k, idesc, 1u);
+                    umma_tf32(tmem_base + (uint32_t)((kk % kMainAcc) * BN), a_hi + 2 * k, b_hi + 2 * k, idesc, kk >= kMainAcc ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);
+            }
+            umma_commit(accum_bar);
+        }
+    } else if (warp < 6) {
+        const int q = warp & 3;
+        const bool ok = mbar_wait(accum_bar, 0, abort_flag, status);
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                // main accumulators that were used (fewer than kMainAcc k-steps leave some untouched), then the small products
+                const int used = min(kMainAcc, nk * (TK32 / 8));
+                float v[32], t[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                for (int a = 1; a < used; ++a) {
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c), t);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += t[j];
+                }
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kMainAcc * BN + c), t);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += t[j];
+                if (row < M) {
+                    float* orow = out + (size_t)row * N + n0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int col = n0 + c + j;
+                        if (col + 4 <= N) {
+                            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            if (bias) {
+                                const float4 b = *reinterpret_cast<const float4*>(bias + col);
+                                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                            }
+                            *reinterpret_cast<float4*>(orow + j) = o;
+                        } else {
+                            for (int e = 0; e < 4 && col + e < N; ++e) orow[j + e] = v[j + e] + (bias ? bias[col + e] : 0.f);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // converting warps: raw tile -> hi (in place) and lo (twin tile, same offsets)
+        constexpr int CT = kConvWarps * 32;
+        constexpr int VECS = RAW / 16;
+        const int dt = threadIdx.x - kThreadsTc;
+        for (int it = 0; it < nk; ++it) {
+            const int s = it % STAGES;
+            // the lanes of a warp leave together (they meet again at __syncwarp below)
+            const bool arrived = __all_sync(0xffffffffu, mbar_wait(&raw_full[s], (it / STAGES) & 1, abort_flag, status));
+            if (!arrived) break;
+            uint4* hi = reinterpret_cast<uint4*>(smem + s * STAGE);
+            uint4* lo = reinterpret_cast<uint4*>(smem + s * STAGE + RAW);
+#pragma unroll 4
+            for (int i = dt; i < VECS; i += CT) {
+                const uint4 x = hi[i];
+                uint4 h, l;
+                h.x = x.x & 0xFFFFE000u; l.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(h.x));
+                h.y = x.y & 0xFFFFE000u; l.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(h.y));
+                h.z = x.z & 0xFFFFE000u; l.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(h.z));
+                h.w = x.w & 0xFFFFE000u; l.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(h.w));
+                hi[i] = h;
+                lo[i] = l;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(4 * BN) : "memory");
+    }
+}
+
+template <int BN>
+rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, void* out, int M, int N, int K) {
+    constexpr int STAGE = 2 * (TM * TK32 * 4 + BN * TK32 * 4);
+    constexpr int STAGES = (192 * 1024) / STAGE;
+    const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
+    auto kern = gemm_tc_f32_kernel<BN, STAGES>;
+    RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM);
+    kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (float*)out, M, N, K, dev->d_status);
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
+}
+
+// [rows, K] f32 row-major, box = box_rows x 32 elements, 128-byte swizzle
+bool make_map_f32_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    gemvq8::EncodeTiledFn fn = gemvq8::encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K * 4};
+    cuuint32_t box[2] = {(cuuint32_t)TK32, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K) {
+    if (act_dt != RCU_F32 || lhs_dt != RCU_F32) return false;
+    // small problems stay on the SIMT kernel; rows must be 16-byte multiples for the tensor maps
+    if (M < 32 || N < 64 || K < 32 || K % 4 != 0 || N % 4 != 0) return false;
+    if (M > 0x7fffffffull || N > 0x7fffffffull || K > 0x7fffffffull) return false;
+    static const bool off = [] { const char* e = std::getenv("RCU_GEMM_F32_TC"); return e && std::atoi(e) == 0; }();
+    return !off;
+}
+
+rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
+                                    uint64_t K) {
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(bias)) & 15)
+        return RCU_ERR_UNSUPPORTED;
+    DevGuard g(dev->ordinal);
+    const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128);
+    const int bn = tiles128 >= (uint64_t)dev->sm_count ? 128 : 64;
+    CUtensorMap xmap, wmap;
+    if (!make_map_f32_sw128(&xmap, x, M, K, TM) || !make_map_f32_sw128(&wmap, w, N, K, (uint32_t)bn))
+        return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu)", (unsigned long long)M,
+                        (unsigned long long)N, (unsigned long long)K);
+    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K)
+                     : launch_f32<64>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K);
+}

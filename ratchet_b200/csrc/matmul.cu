@@ -13,6 +13,10 @@ rcu_status rcu_gemv_dispatch(rcu_device* dev, int lhs_dt, const void* w, int act
 rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int act_dt, const void* x, const void* bias,
                                 void* y, uint64_t M, uint64_t N, uint64_t K);
 bool rcu_gemm_tc_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
+// f32 Linear on the tensor cores (split-TF32, f32-level accuracy)
+rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
+                                    uint64_t K);
+bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
 
 namespace {
 
@@ -233,6 +237,10 @@ rcu_status rcu_matmul(rcu_device* dev, const rcu_tensor* lhs, const rcu_tensor* 
     // Linear convention W[N,K] . x[M,K]^T -> [M,N]: tensor-core path when the shape qualifies
     if (!tl && tr && td && d.lstack == 1 && rcu_gemm_tc_eligible(lhs->dt, rhs->dt, d.rstack * d.n, d.m, d.k)) {
         st = rcu_gemm_tc_dispatch(dev, lhs->dt, lhs->data, rhs->dt, rhs->data, bptr, dst->data, d.rstack * d.n, d.m, d.k);
+        if (st != RCU_ERR_UNSUPPORTED) return st;
+    }
+    if (!tl && tr && td && d.lstack == 1 && rcu_gemm_tc_f32_eligible(lhs->dt, rhs->dt, d.rstack * d.n, d.m, d.k)) {
+        st = rcu_gemm_tc_f32_dispatch(dev, lhs->data, rhs->data, bptr, dst->data, d.rstack * d.n, d.m, d.k);
         if (st != RCU_ERR_UNSUPPORTED) return st;
     }
     const uint64_t numel = t_numel(lhs);

@@ -195,6 +195,11 @@ def _gemm(dev, rng, which):
         out = dev.empty(capi.F32, (M, N))
         return (lambda: dev.matmul(w, x, None, False, True, True, out)), (N * K + M * K + M * N) * 4, 2.0 * M * N * K
     M, N, K = GEMM_M, 8192, 3072
+    if which == "gemm_tc_f32":
+        w = dev.from_numpy((_rand_f16(rng, N * K).astype(np.float32) * 0.02).reshape(N, K))
+        x = dev.from_numpy(_rand_f16(rng, M * K).astype(np.float32).reshape(M, K))
+        out = dev.empty(capi.F32, (M, N))
+        return (lambda: dev.matmul(w, x, None, False, True, True, out)), (N * K + M * K + M * N) * 4, 2.0 * M * N * K
     x = dev.from_numpy(_rand_f16(rng, M * K).reshape(M, K))
     out = dev.empty(capi.F16, (M, N))
     if which == "gemm_tc_f16":
@@ -245,7 +250,8 @@ CASES = [
     Case("dequant_q4k", lambda d, r: _dequant(d, r, "dequant_q4k"), "dequant_q4k_kernel"),
     Case("gemv_f16", lambda d, r: _gemv(d, r, "gemv_f16"), "gemv_float_kernel"),
     Case("gemv_q8", lambda d, r: _gemv(d, r, "gemv_q8"), "gemv_q8_kernel"),
-    Case("gemm_simt_f32", lambda d, r: _gemm(d, r, "gemm_simt_f32"), "gemm_simt_kernel"),
+    Case("gemm_f32_phi2_mlp", lambda d, r: _gemm(d, r, "gemm_simt_f32"), "gemm_tc_f32_kernel (M=64, N=10240, K=2560)"),
+    Case("gemm_tc_f32", lambda d, r: _gemm(d, r, "gemm_tc_f32"), "gemm_tc_f32_kernel"),
     Case("gemm_tc_f16", lambda d, r: _gemm(d, r, "gemm_tc_f16"), "gemm_tc_kernel"),
     Case("gemm_tc_q8", lambda d, r: _gemm(d, r, "gemm_tc_q8"), "gemm_tc_kernel"),
     Case("gemm_tc_q4k", lambda d, r: _gemm(d, r, "gemm_tc_q4k"), "gemm_tc_kernel"),

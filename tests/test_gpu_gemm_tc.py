@@ -77,3 +77,20 @@ def test_config3_q4k_prefill_shape(dev):
     ref = orc.matmul(wd, x, None, False, True, True)
     y = dev.matmul(dev.from_quantized(buf, capi.Q4_KH, (N, K)), dev.from_numpy(x), None, False, True, True)
     check(y.to_numpy(), ref, 1e-2, "config 3, M=128")
+
+
+# f32 Linear on the tensor cores (split TF32): the f32 bar, 1e-4 of the result's scale
+F32_SHAPES = [(64, 10240, 2560), (128, 256, 256), (100, 200, 136), (37, 64, 36), (1500, 384, 384), (1500, 1536, 384), (300, 2560, 10240)]
+
+
+@pytest.mark.parametrize("M,N,K", F32_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_tc_f32(dev, M, N, K, with_bias):
+    g = np.random.Generator(np.random.PCG64(M * 3 + N + K))
+    w = (g.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = g.standard_normal((M, K)).astype(np.float32)
+    b = g.standard_normal(N).astype(np.float32) if with_bias else None
+    ref = orc.matmul(w, x, b, False, True, True)
+    y = dev.matmul(dev.from_numpy(w), dev.from_numpy(x), None if b is None else dev.from_numpy(b), False, True, True)
+    assert y.shape == (M, N)
+    check(y.to_numpy(), ref, 1e-4, f"f32 {M}x{N}x{K}")
