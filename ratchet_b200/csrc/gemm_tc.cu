@@ -367,7 +367,11 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
     }
     // tile width: enough CTAs to cover the SMs when M is small
     const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128);
-    const int bn = tiles128 >= (uint64_t)dev->sm_count ? 128 : 64;
+    int bn = tiles128 >= (uint64_t)dev->sm_count ? 128 : 64;
+    // f16 weights and enough 128 x 256 tiles for two CTAs on every SM: the wide tile halves the shared-memory
+    // reads per flop (a 128 x 128 x 16 MMA reads A and B at the full shared-memory rate)
+    static const int force_bn = [] { const char* e = getenv("RCU_GEMM_BN"); return e ? atoi(e) : 0; }();
+    if (lhs_dt == RCU_F16 && (force_bn == 256 || (force_bn == 0 && tiles128 / 2 >= 2ull * dev->sm_count))) bn = 256;
     CUtensorMap xmap, wmap;
     QuantArgs qa{nullptr, nullptr, nullptr};
     bool maps = make_map_f16_sw128(&xmap, x, M, K, TM);
@@ -396,7 +400,7 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
                       (unsigned long long)N, (unsigned long long)K);
 #define RCU_TC(BN_, WK_) launch_tc<BN_, WK_>(dev, xmap, wmap, qa, bias, y, (int)M, (int)N, (int)K)
     if (st == RCU_OK) {
-        if (wk == WK_F16) st = bn == 128 ? RCU_TC(128, WK_F16) : RCU_TC(64, WK_F16);
+        if (wk == WK_F16) st = bn == 256 ? RCU_TC(256, WK_F16) : bn == 128 ? RCU_TC(128, WK_F16) : RCU_TC(64, WK_F16);
         else if (wk == WK_Q8) st = bn == 128 ? RCU_TC(128, WK_Q8) : RCU_TC(64, WK_Q8);
         else st = bn == 128 ? RCU_TC(128, WK_Q4K) : RCU_TC(64, WK_Q4K);
     }
