@@ -312,6 +312,34 @@ int rcu_comm_world(const rcu_comm* comm);
 rcu_status rcu_gemv_q8_allgather(rcu_comm* comm, const rcu_tensor* w_shard, const rcu_tensor* x, const rcu_tensor* bias_shard,
                                  void** y_full);
 
+/* ------------------------------------------------------------------ GGUF files (host side)
+ * ratchet-loader/src/gguf/gguf.rs:422-509 (header, metadata, tensor infos; GGUF v1-v3) and
+ * gguf/dtype.rs:39-198 (transcode of ggml blocks into ratchet's segment layout).  The file is
+ * memory-mapped; nothing here touches a device.  Errors: rcu_gguf_last_error() (per thread). */
+typedef struct rcu_gguf rcu_gguf;
+typedef struct {
+    const char* name;      /* owned by the handle */
+    uint32_t rank;         /* 1..4 */
+    uint64_t shape[4];     /* ratchet order, outermost first (GGUF stores innermost first; gguf.rs:470) */
+    uint32_t ggml_type;    /* 0 F32, 1 F16, 8 Q8_0, 12 Q4_K; others can be listed but not transcoded */
+    uint64_t numel;
+    uint64_t file_bytes;   /* bytes of the tensor in the file (0 for unsupported types) */
+} rcu_gguf_tensor_info;
+rcu_status rcu_gguf_open(const char* path, rcu_gguf** out);
+void rcu_gguf_close(rcu_gguf* g);
+const char* rcu_gguf_last_error(void);
+uint32_t rcu_gguf_version(const rcu_gguf* g);
+uint64_t rcu_gguf_tensor_count(const rcu_gguf* g);
+int64_t rcu_gguf_find(const rcu_gguf* g, const char* name);            /* index or -1 */
+rcu_status rcu_gguf_tensor(const rcu_gguf* g, uint64_t index, rcu_gguf_tensor_info* out);
+rcu_status rcu_gguf_meta_u64(const rcu_gguf* g, const char* key, uint64_t* out);   /* integer and bool values */
+rcu_status rcu_gguf_meta_f64(const rcu_gguf* g, const char* key, double* out);
+rcu_status rcu_gguf_meta_str(const rcu_gguf* g, const char* key, char* buf, uint64_t buf_bytes);
+/* dtype `ratchet_from_gguf` picks (gguf.rs:113-156): Q8_0 / Q4_K take f16 scales on an f16-capable device. -1: unsupported. */
+int32_t rcu_gguf_target_dtype(uint32_t ggml_type, int f16_device);
+/* Writes tensor `index` as dtype `dt` in ratchet's layout into `host_out` (rcu_dtype_nbytes(dt, numel) bytes). */
+rcu_status rcu_gguf_transcode(const rcu_gguf* g, uint64_t index, int32_t dt, void* host_out, uint64_t out_bytes);
+
 #ifdef __cplusplus
 }
 #endif

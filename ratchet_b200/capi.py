@@ -56,6 +56,11 @@ class rcu_decoder_config(C.Structure):
                 ("rope_dim", C.c_uint32), ("rope_base", C.c_float), ("rms_eps", C.c_float), ("weight_dt", C.c_int32)]
 
 
+class rcu_gguf_tensor_info(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("rank", C.c_uint32), ("shape", C.c_uint64 * 4), ("ggml_type", C.c_uint32), ("numel", C.c_uint64),
+                ("file_bytes", C.c_uint64)]
+
+
 class rcu_decoder_layer(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("qkv", C.c_void_p), ("o", C.c_void_p), ("ffn_norm", C.c_void_p),
                 ("gate_up", C.c_void_p), ("down", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
@@ -133,6 +138,19 @@ SIGNATURES = {
     "rcu_lazy_to_host": (C.c_int, [_LZ, C.c_void_p, C.c_uint64]),
     "rcu_last_resolve_stats": (None, [_DEV, C.POINTER(rcu_resolve_stats)]),
     # fused decode step
+    # GGUF files (host side)
+    "rcu_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "rcu_gguf_close": (None, [C.c_void_p]),
+    "rcu_gguf_last_error": (C.c_char_p, []),
+    "rcu_gguf_version": (C.c_uint32, [C.c_void_p]),
+    "rcu_gguf_tensor_count": (C.c_uint64, [C.c_void_p]),
+    "rcu_gguf_find": (C.c_int64, [C.c_void_p, C.c_char_p]),
+    "rcu_gguf_tensor": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(rcu_gguf_tensor_info)]),
+    "rcu_gguf_meta_u64": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "rcu_gguf_meta_f64": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_double)]),
+    "rcu_gguf_meta_str": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_uint64]),
+    "rcu_gguf_target_dtype": (C.c_int32, [C.c_uint32, C.c_int]),
+    "rcu_gguf_transcode": (C.c_int, [C.c_void_p, C.c_uint64, C.c_int32, C.c_void_p, C.c_uint64]),
     "rcu_decoder_create": (C.c_int, [_DEV, C.POINTER(rcu_decoder_config), C.POINTER(rcu_decoder_layer), C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.POINTER(C.c_void_p)]),
     "rcu_decoder_create_sharded": (C.c_int, [_DEV, C.c_void_p, C.POINTER(rcu_decoder_config), C.POINTER(rcu_decoder_layer), C.c_void_p,
