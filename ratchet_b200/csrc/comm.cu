@@ -19,27 +19,6 @@
 namespace {
 using rcu_window::Window;
 using rcu_window::kSlots;
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;   // 2 s per wait, then RCU_DEVFLAG_TIMEOUT
-
-// lane p waits until peer p's flag for this slot reaches seq
-__global__ void wait_flags_kernel(const unsigned int* flags, int world, int self, unsigned int seq, int* status) {
-    const int p = threadIdx.x;
-    if (p >= world || p == self) return;
-    unsigned long long t0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    for (;;) {
-        unsigned int v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + p) : "memory");
-        if ((int)(v - seq) >= 0) return;
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        if (t - t0 > kWaitBudgetNs) {
-            atomicOr(status, RCU_DEVFLAG_TIMEOUT);
-            return;
-        }
-        __nanosleep(100);
-    }
-}
 }  // namespace
 
 extern "C" {
@@ -132,18 +111,18 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
         epi.n_peers++;
     }
     epi.seq = seq;
+    epi.my_flags = c->world > 1 ? c->local.flags(slot, c->world) : nullptr;
+    epi.world = c->world;
+    epi.self = c->rank;
+    epi.status = dev->d_status;
     const int8_t* qs = (const int8_t*)w_shard->data;
     const void* sc = (const char*)w_shard->data + align256(n_local * K);
     gemvq8::PlainPrologue<__half> pro{(const __half*)x->data};
     const bool pipe = n_local * K < ((uint64_t)128 << 20);
     rcu_status st = w_shard->dt == RCU_Q8_0H
-                        ? gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, false, 3, pipe)
-                        : gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, false, 3, pipe);
+                        ? gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe)
+                        : gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe);
     if (st != RCU_OK) return st;
-    if (c->world > 1) {
-        wait_flags_kernel<<<1, 32, 0, dev->stream>>>(c->local.flags(slot, c->world), c->world, c->rank, seq, dev->d_status);
-        RCU_LAUNCH_CHECK(dev);
-    }
     *y_full = c->local.slot(slot);
     return RCU_OK;
 }

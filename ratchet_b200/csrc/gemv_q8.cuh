@@ -239,6 +239,9 @@ struct PushEpilogueH {
     unsigned int* peer_flag[kMaxPeers];   // this rank's flag word on each peer
     int n_peers;
     unsigned int seq;              // value the flags take when this step's slice has landed
+    const unsigned int* my_flags;  // this rank's own flag words [world] for the slot: the last CTA also waits for the peers' slices
+    int world, self;
+    int* status;
     __device__ __forceinline__ void store(int u, const float* acc) const {
         float s = acc[0];
         if (bias) s += __half2float(bias[u]);
@@ -266,6 +269,25 @@ struct PushEpilogueH {
         if ((int)threadIdx.x < n_peers)
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag[threadIdx.x]), "r"(seq) : "memory");
         if (threadIdx.x == 0) *ticket = 0;
+        // The kernel ends only when every peer's slice has landed here, so whatever follows in the stream
+        // reads a complete vector without a separate wait launch.  Lane p polls peer p's flag (bounded:
+        // two seconds, then RCU_DEVFLAG_TIMEOUT).
+        const int p = threadIdx.x;
+        if (my_flags != nullptr && p < world && p != self) {
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            for (;;) {
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + p) : "memory");
+                if ((int)(v - seq) >= 0) break;
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                if (t - t0 > 2000000000ull) {
+                    atomicOr(status, RCU_DEVFLAG_TIMEOUT);
+                    break;
+                }
+            }
+        }
     }
 };
 
