@@ -199,8 +199,9 @@ __device__ __forceinline__ WarpMap map_warp(const Gemv& g) {
     const int rg = warp / g.ksplit, ks = warp % g.ksplit;
     const long long gw = (long long)blockIdx.x * RG + rg;
     const long long W = (long long)gridDim.x * RG;
-    m.u_begin = (int)((gw * g.n_units) / W);
-    m.u_end = (int)(((gw + 1) * g.n_units) / W);
+    const long long n_groups_all = (g.n_units + UPI - 1) / UPI;       // whole groups are dealt, as in gemvq8's kernels
+    m.u_begin = (int)((gw * n_groups_all) / W) * UPI;
+    m.u_end = min(g.n_units, (int)(((gw + 1) * n_groups_all) / W) * UPI);
     const int nchunks = (g.K + 511) >> 9;
     const int n_groups = (m.u_end - m.u_begin + UPI - 1) / UPI;
     m.ncg = (nchunks - ks + g.ksplit * UNROLL - 1) / (g.ksplit * UNROLL);

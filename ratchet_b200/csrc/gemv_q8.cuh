@@ -486,8 +486,11 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
     const int rg = warp / KSPLIT, ks = warp % KSPLIT;
     const long long gw = (long long)blockIdx.x * RG + rg;
     const long long W = (long long)gridDim.x * RG;
-    const int u_begin = (int)((gw * n_units) / W);
-    const int u_end = (int)(((gw + 1) * n_units) / W);
+    // whole groups of UPI units are dealt (balanced to one group), so only the last group of the matrix
+    // can be partial: a warp never spends an iteration on duplicated rows
+    const long long n_groups_all = (n_units + UPI - 1) / UPI;
+    const int u_begin = (int)((gw * n_groups_all) / W) * UPI;
+    const int u_end = min(n_units, (int)(((gw + 1) * n_groups_all) / W) * UPI);
     const int kblocks = K >> 5;
     const int nchunks = (K + 511) >> 9;
     const int kl = lane << 4;
@@ -590,8 +593,11 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
     const int rg = warp / KSPLIT, ks = warp % KSPLIT;
     const long long gw = (long long)blockIdx.x * RG + rg;
     const long long W = (long long)gridDim.x * RG;
-    const int u_begin = (int)((gw * n_units) / W);
-    const int u_end = (int)(((gw + 1) * n_units) / W);
+    // whole groups of UPI units are dealt (balanced to one group), so only the last group of the matrix
+    // can be partial: a warp never spends an iteration on duplicated rows
+    const long long n_groups_all = (n_units + UPI - 1) / UPI;
+    const int u_begin = (int)((gw * n_groups_all) / W) * UPI;
+    const int u_end = min(n_units, (int)(((gw + 1) * n_groups_all) / W) * UPI);
     const int kblocks = K >> 5;
     const int nchunks = (K + 511) >> 9;
     const int kl = lane << 4;
@@ -701,6 +707,20 @@ inline Plan plan(const rcu_device* dev, int n_units, int unit, int K, int ctas_p
     const long long warps_wanted = max_ctas * kWarps;
     int ksplit = 1;
     while (ksplit < 8 && groups * ksplit * 2 <= warps_wanted && (K / (ksplit * 2)) >= 1024) ksplit *= 2;
+    // Groups are dealt whole to the warp teams (kWarps / ksplit per CTA).  With only a few groups per team
+    // the team that gets one more sets the kernel's time: when that imbalance (rounds of the busiest team
+    // over the average) exceeds 6 %, take the K split that minimises it while every warp keeps two chunks.
+    auto imbalance = [&](int ks) {
+        const double teams = (double)max_ctas * (kWarps / ks);
+        const double avg = (double)groups / teams;
+        return avg <= 0.0 ? 1.0 : (double)((groups + (long long)teams - 1) / (long long)teams) / avg;
+    };
+    if (groups * ksplit > warps_wanted / 2 && imbalance(ksplit) > 1.06) {
+        int best = ksplit;
+        for (int ks = ksplit * 2; ks <= 8 && (K / (ks * 2)) >= 1024; ks *= 2)
+            if (imbalance(ks) < imbalance(best) - 0.01) best = ks;
+        ksplit = best;
+    }
     p.ksplit = ksplit;
     const long long ctas_needed = (groups * ksplit + kWarps - 1) / kWarps;
     p.grid = (int)(ctas_needed < max_ctas ? (ctas_needed < 1 ? 1 : ctas_needed) : max_ctas);
