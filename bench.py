@@ -319,6 +319,73 @@ def _q8h_weights(N, K, seed):
     return buf
 
 
+def _lazy_forward_us(torch, stream, build_and_resolve, iters):
+    """Average time of one forward through the lazy Tensor API (graph build on the host + resolve on the
+    device), CUDA events on the library's stream around `iters` forwards after three warm-ups."""
+    for _ in range(3):
+        build_and_resolve()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        build_and_resolve()
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def phi2_mlp_bench(dev, torch, stream):
+    """Config 1: Phi-2 MLP block in f32 through the lazy Tensor graph: x [1,64,2560] N(0,1), LayerNorm,
+    W1 [10240,2560] + b1, tanh-GELU, W2 [2560,10240] + b2, residual.  HBM-bound at M=64 (210 MB of weights)."""
+    from ratchet_b200 import Tensor, callers, nn
+    g = np.random.Generator(np.random.PCG64(0))
+    d, ffn = 2560, 10240
+    t = lambda a: Tensor.from_data(a, device=dev)
+    x = t(g.standard_normal((1, 64, d), dtype=np.float32))
+    blk = callers.Phi2MLPBlock(nn.LayerNorm(t(np.ones(d, np.float32)), t(np.zeros(d, np.float32)), 1e-5),
+                               nn.Linear(t(g.standard_normal((ffn, d), dtype=np.float32) * np.float32(0.02)), t(np.zeros(ffn, np.float32))),
+                               nn.Linear(t(g.standard_normal((d, ffn), dtype=np.float32) * np.float32(0.02)), t(np.zeros(d, np.float32))))
+    us = _lazy_forward_us(torch, stream, lambda: blk.schedule(x).resolve(), 50)
+    nbytes = 2 * ffn * d * 4 + 4 * 64 * d * 4
+    flops = 2.0 * 64 * d * ffn * 2
+    peak, kind = measured_peak()
+    return {"us_per_forward": us, "algorithmic_bytes": nbytes, "gbs": nbytes / us * 1e-3, "frac_of_hbm_peak": nbytes / us * 1e-3 / peak,
+            "peak_kind": f"of {kind}", "tflops": flops / us * 1e-6, "note": "weights (210 MB) exceed L2; lazy graph build + resolve each forward"}
+
+
+def whisper_encoder_bench(dev, torch, stream):
+    """Config 4: Whisper-tiny encoder forward in f32 through the lazy Tensor graph: mel [1,80,3000] U(-1,1),
+    conv stem, sinusoidal positions, 4 pre-LN blocks (d 384, 6 heads, MLP 1536), final LayerNorm;
+    weights N(0, 0.02)."""
+    from ratchet_b200 import Tensor, callers, capi, nn
+    g = np.random.Generator(np.random.PCG64(0))
+    d, H, mlp, n_ctx = 384, 6, 1536, 1500
+    t = lambda a: Tensor.from_data(np.ascontiguousarray(a, np.float32), device=dev)
+    w = lambda *shape: g.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+    inc = np.log(10000.0) / (d // 2 - 1)
+    ang = np.arange(n_ctx)[:, None] * np.exp(-inc * np.arange(d // 2))[None, :]
+    pos = np.concatenate([np.sin(ang), np.cos(ang)], 1)
+    dk = t(np.array([np.float32(d // H) ** np.float32(-0.25)], np.float32))
+    blocks = []
+    for _ in range(4):
+        mha = callers.WhisperMHA(nn.Linear(t(w(d, d)), t(w(d))), nn.Linear(t(w(d, d)), None), nn.Linear(t(w(d, d)), t(w(d))),
+                                 nn.Linear(t(w(d, d)), t(w(d))), H, dk)
+        blocks.append(callers.WhisperBlock(nn.LayerNorm(t(np.ones(d)), t(np.zeros(d)), 1e-5), mha,
+                                           nn.LayerNorm(t(np.ones(d)), t(np.zeros(d)), 1e-5),
+                                           callers.WhisperMLP(nn.Linear(t(w(mlp, d)), t(w(mlp))), nn.Linear(t(w(d, mlp)), t(w(d))))))
+    enc = callers.WhisperEncoder(t(w(d, 80, 3)), t(w(d)), t(w(d, d, 3)), t(w(d)), t(pos), blocks,
+                                 nn.LayerNorm(t(np.ones(d)), t(np.zeros(d)), 1e-5), capi.F32)
+    mel = t(g.uniform(-1.0, 1.0, (1, 80, 3000)))
+    l0 = dev.launches
+    enc.schedule(mel).resolve()
+    launches = dev.launches - l0
+    us = _lazy_forward_us(torch, stream, lambda: enc.schedule(mel).resolve(), 20)
+    # flops: conv stem + per block (4 projections, QK^T, PV, two MLP matmuls)
+    flops = 2.0 * 3000 * d * 80 * 3 + 2.0 * n_ctx * d * d * 3 + 4 * (2.0 * n_ctx * d * d * 4 + 2 * 2.0 * n_ctx * n_ctx * d + 2 * 2.0 * n_ctx * d * mlp)
+    return {"us_per_forward": us, "kernels_per_forward": int(launches), "tflops": flops / us * 1e-6,
+            "note": "f32 activations and weights; mixed launch- and compute-bound (241 MB of 1500x1500 score matrices per layer pass through L2)"}
+
+
 def phi3_decode_bytes(c):
     """Algorithmic HBM bytes of one decode step: Q8_0H weights (1 + 2/32 bytes per element) of every
     Linear + one embedding row, K and V rows of the populated cache, negligible activations."""
@@ -550,10 +617,19 @@ def run_ours(args):
     # release the GEMV weights before the other legs allocate theirs
     del dw
     extras = {}
+    legs = set(args.legs.split(","))
+    want = lambda name: "all" in legs or name in legs
     if world == 1 and not args.rows and not args.no_extras:
-        extras["gemv_sweep"] = gemv_sweep(dev, torch, stream)
-        extras["q4k_prefill_gemm"] = prefill_gemm_bench(dev, torch, stream)
-        extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
+        if want("sweep"):
+            extras["gemv_sweep"] = gemv_sweep(dev, torch, stream)
+        if want("prefill"):
+            extras["q4k_prefill_gemm"] = prefill_gemm_bench(dev, torch, stream)
+        if want("phi2"):
+            extras["phi2_mlp_f32"] = phi2_mlp_bench(dev, torch, stream)
+        if want("whisper"):
+            extras["whisper_tiny_encoder_f32"] = whisper_encoder_bench(dev, torch, stream)
+        if want("decode"):
+            extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
     if world > 1 and not args.rows and not args.no_extras:
         if comm is not None:            # the GEMV leg's window goes first: one exchange window per rank at a time
             dist.barrier()
@@ -582,6 +658,7 @@ def main():
                     help="profiling aid: run the same GEMV with this many rows instead of 65536 (no CPU baseline); "
                          "8192 rows = 134 MB of weights, still larger than L2, small enough for an ncu capture")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV sweep and the Phi-3 decode leg")
+    ap.add_argument("--legs", default="all", help="comma list of the extra legs to run at N=1: sweep, prefill, phi2, whisper, decode (default all)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

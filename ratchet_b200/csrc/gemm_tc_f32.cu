@@ -10,9 +10,9 @@
 // The tensor core adds into its f32 accumulator with truncation: every accumulating MMA loses up to
 // one unit in the last place of the running sum, always toward zero, which over K/8 k-steps measures
 // about 1.3e-8 * K of the result.  Two things keep that below the bar for the K of real layers (up to
-// 10240): the two small products go to an accumulator of their own (their sum is 2^-11 of the main one,
-// and so are its truncation errors), and the main products rotate over kMainAcc accumulators, which the
-// epilogue adds up with ordinary rounded f32 additions.
+// 10240): the two small products go to accumulators of their own (their sum is 2^-11 of the main one,
+// and so are its truncation errors), and the main products rotate over several accumulators (all 512
+// tensor-memory columns are used), which the epilogue adds up with ordinary rounded f32 additions.
 //
 // Structure as gemm_tc.cu: TMA brings 128 x 32 (activations) and BN x 32 (weights) f32 tiles,
 // 128-byte swizzled, into a shared-memory ring; eight converting warps rewrite each raw tile in place
@@ -29,7 +29,9 @@ using namespace tc;
 
 constexpr int TK32 = 32;                 // K per stage: 32 f32 = 128 bytes = one swizzle row
 constexpr int kConvWarps = 8;
-constexpr int kMainAcc = 3;               // accumulators the hi x hi products rotate over; one more takes the small products
+// accumulators: the hi x hi products rotate over `mains`, the small products over `corrs` (512 columns in all)
+__host__ __device__ constexpr int main_accs(int bn) { return bn == 64 ? 6 : 3; }
+__host__ __device__ constexpr int corr_accs(int bn) { return bn == 64 ? 2 : 1; }
 constexpr int kThreadsF32 = kThreadsTc + kConvWarps * 32;
 
 // 32-bit instruction descriptor, kind::tf32: TF32 A and B (both K-major), f32 D, M x N tile.
@@ -81,8 +83,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        // (kMainAcc + 1) accumulators of BN f32 columns: 512 columns for BN = 128, 256 for BN = 64
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(4 * BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -94,7 +95,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
         if (lane == 0) {
             for (int it = 0; it < nk; ++it) {
                 const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) break;
+                if (it >= STAGES && !mbar_wait_spin(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) break;
                 unsigned char* st = smem + s * STAGE;
                 mbar_expect_tx(&raw_full[s], RAW);
                 tma_load_2d(st, &xmap, it * TK32, m0, &raw_full[s]);
@@ -106,7 +107,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             constexpr uint32_t idesc = umma_idesc_tf32(TM, BN);
             for (int it = 0; it < nk; ++it) {
                 const int s = it % STAGES;
-                if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, status)) break;
+                if (!mbar_wait_spin(&full[s], (it / STAGES) & 1, abort_flag, status)) break;
                 tc_fence_after();
                 unsigned char* st = smem + s * STAGE;
                 const uint64_t a_hi = umma_desc_sw128(st), b_hi = umma_desc_sw128(st + A_BYTES);
@@ -115,10 +116,11 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 for (int k = 0; k < TK32 / 8; ++k) {
                     // 8 f32 = 32 bytes inside the 128-byte swizzle row: +2 in 16-byte units
                     const int kk = it * (TK32 / 8) + k;
-                    const uint32_t corr = tmem_base + (uint32_t)(kMainAcc * BN);
-                    umma_tf32(corr, a_lo + 2 * k, b_hi + 2 * k, idesc, kk > 0 ? 1u : 0u);
+                    constexpr int MAINS = main_accs(BN), CORRS = corr_accs(BN);
+                    const uint32_t corr = tmem_base + (uint32_t)((MAINS + kk % CORRS) * BN);
+                    umma_tf32(corr, a_lo + 2 * k, b_hi + 2 * k, idesc, kk >= CORRS ? 1u : 0u);
+                    umma_tf32(tmem_base + (uint32_t)((kk % MAINS) * BN), a_hi + 2 * k, b_hi + 2 * k, idesc, kk >= MAINS ? 1u : 0u);
                     umma_tf32(corr, a_hi + 2 * k, b_lo + 2 * k, idesc, 1u);
-                    umma_tf32(tmem_base + (uint32_t)((kk % kMainAcc) * BN), a_hi + 2 * k, b_hi + 2 * k, idesc, kk >= kMainAcc ? 1u : 0u);
                 }
                 umma_commit(&empty[s]);
             }
@@ -133,17 +135,20 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 // main accumulators that were used (fewer than kMainAcc k-steps leave some untouched), then the small products
-                const int used = min(kMainAcc, nk * (TK32 / 8));
+                constexpr int MAINS = main_accs(BN), CORRS = corr_accs(BN);
+                const int ksteps = nk * (TK32 / 8);
                 float v[32], t[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-                for (int a = 1; a < used; ++a) {
+                for (int a = 1; a < min(MAINS, ksteps); ++a) {
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c), t);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] += t[j];
                 }
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kMainAcc * BN + c), t);
+                for (int a = 0; a < min(CORRS, ksteps); ++a) {
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((MAINS + a) * BN + c), t);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += t[j];
+                    for (int j = 0; j < 32; ++j) v[j] += t[j];
+                }
                 if (row < M) {
                     float* orow = out + (size_t)row * N + n0 + c;
 #pragma unroll
@@ -171,7 +176,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
         for (int it = 0; it < nk; ++it) {
             const int s = it % STAGES;
             // the lanes of a warp leave together (they meet again at __syncwarp below)
-            const bool arrived = __all_sync(0xffffffffu, mbar_wait(&raw_full[s], (it / STAGES) & 1, abort_flag, status));
+            const bool arrived = __all_sync(0xffffffffu, mbar_wait_spin(&raw_full[s], (it / STAGES) & 1, abort_flag, status));
             if (!arrived) break;
             uint4* hi = reinterpret_cast<uint4*>(smem + s * STAGE);
             uint4* lo = reinterpret_cast<uint4*>(smem + s * STAGE + RAW);
@@ -194,7 +199,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(4 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
     }
 }
 

@@ -69,6 +69,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of the phase (try_wait may suspend the thread for a hardware-chosen time slice
+// before it answers; a pipeline whose stages hand over through several barriers pays that on every hop).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded busy wait for latency-critical hand-overs; same contract as mbar_wait
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* status) {
+    unsigned long long t0 = 0;
+    for (unsigned i = 0;; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 1000000000ull) break;
+        }
+    }
+    *abort_flag = 1;
+    atomicOr(status, RCU_DEVFLAG_TIMEOUT);
+    return false;
+}
 // bounded wait; returns false if it gave up (or another thread of the CTA already did)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int* status) {
     unsigned long long t0 = 0;

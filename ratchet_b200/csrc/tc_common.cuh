@@ -12,6 +12,7 @@ using gemvq8::mbar_arrive;
 using gemvq8::mbar_expect_tx;
 using gemvq8::mbar_init;
 using gemvq8::mbar_wait;
+using gemvq8::mbar_wait_spin;
 using gemvq8::smem_u32;
 using gemvq8::tma_load_2d;
 
