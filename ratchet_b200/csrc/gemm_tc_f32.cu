@@ -71,6 +71,8 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * BN;
     const int nk = (K + TK32 - 1) / TK32;
+    const int batch = blockIdx.z;            // independent problems (attention heads): third coordinate of both maps
+    out += (size_t)batch * M * N;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -98,8 +100,8 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 if (it >= STAGES && !mbar_wait_spin(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) break;
                 unsigned char* st = smem + s * STAGE;
                 mbar_expect_tx(&raw_full[s], RAW);
-                tma_load_2d(st, &xmap, it * TK32, m0, &raw_full[s]);
-                tma_load_2d(st + A_BYTES, &wmap, it * TK32, n0, &raw_full[s]);
+                tma_load_3d(st, &xmap, it * TK32, m0, batch, &raw_full[s]);
+                tma_load_3d(st + A_BYTES, &wmap, it * TK32, n0, batch, &raw_full[s]);
             }
         }
     } else if (warp == 1) {
@@ -204,27 +206,28 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 }
 
 template <int BN>
-rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, void* out, int M, int N, int K) {
+rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, void* out, int M, int N, int K,
+                      int batches) {
     constexpr int STAGE = 2 * (TM * TK32 * 4 + BN * TK32 * 4);
     constexpr int STAGES = (192 * 1024) / STAGE;
     const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
     auto kern = gemm_tc_f32_kernel<BN, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM);
+    dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batches);
     kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (float*)out, M, N, K, dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
 
-// [rows, K] f32 row-major, box = box_rows x 32 elements, 128-byte swizzle
-bool make_map_f32_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+// [batches, rows, K] f32 row-major, box = 1 x box_rows x 32 elements, 128-byte swizzle
+bool make_map_f32_sw128(CUtensorMap* map, const void* base, uint64_t batches, uint64_t rows, uint64_t K, uint32_t box_rows) {
     gemvq8::EncodeTiledFn fn = gemvq8::encode_tiled_fn();
     if (!fn) return false;
-    cuuint64_t dims[2] = {K, rows};
-    cuuint64_t strides[1] = {K * 4};
-    cuuint32_t box[2] = {(cuuint32_t)TK32, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    cuuint64_t dims[3] = {K, rows, batches};
+    cuuint64_t strides[2] = {K * 4, rows * K * 4};
+    cuuint32_t box[3] = {(cuuint32_t)TK32, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -240,16 +243,18 @@ bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, ui
 }
 
 rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
-                                    uint64_t K) {
+                                    uint64_t K, uint64_t batches) {
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(bias)) & 15)
         return RCU_ERR_UNSUPPORTED;
+    // tensor-map strides are multiples of 16 bytes; the grid's z extent is limited
+    if (batches < 1 || batches > 65535 || (batches > 1 && ((M * K) % 4 != 0 || (N * K) % 4 != 0 || (M * N) % 4 != 0 || bias))) return RCU_ERR_UNSUPPORTED;
     DevGuard g(dev->ordinal);
-    const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128);
+    const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128) * batches;
     const int bn = tiles128 >= (uint64_t)dev->sm_count ? 128 : 64;
     CUtensorMap xmap, wmap;
-    if (!make_map_f32_sw128(&xmap, x, M, K, TM) || !make_map_f32_sw128(&wmap, w, N, K, (uint32_t)bn))
-        return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu)", (unsigned long long)M,
-                        (unsigned long long)N, (unsigned long long)K);
-    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K)
-                     : launch_f32<64>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K);
+    if (!make_map_f32_sw128(&xmap, x, batches, M, K, TM) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
+        return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu x%llu)", (unsigned long long)M,
+                        (unsigned long long)N, (unsigned long long)K, (unsigned long long)batches);
+    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K, (int)batches)
+                     : launch_f32<64>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K, (int)batches);
 }

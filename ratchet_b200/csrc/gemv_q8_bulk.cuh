@@ -135,6 +135,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
                  "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
                  : "memory");
 }
+// 3-D tile (x = innermost, y = row, z = batch) -> shared, completion on `bar`
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+                 : "memory");
+}
 
 template <class ScaleT, class Prologue, class Epilogue>
 __global__ void __launch_bounds__(kBulkThreads, 1)

@@ -15,7 +15,7 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
 bool rcu_gemm_tc_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
 // f32 Linear on the tensor cores (split-TF32, f32-level accuracy)
 rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
-                                    uint64_t K);
+                                    uint64_t K, uint64_t batches);
 bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
 
 namespace {
@@ -240,7 +240,27 @@ rcu_status rcu_matmul(rcu_device* dev, const rcu_tensor* lhs, const rcu_tensor* 
         if (st != RCU_ERR_UNSUPPORTED) return st;
     }
     if (!tl && tr && td && d.lstack == 1 && rcu_gemm_tc_f32_eligible(lhs->dt, rhs->dt, d.rstack * d.n, d.m, d.k)) {
-        st = rcu_gemm_tc_f32_dispatch(dev, lhs->data, rhs->data, bptr, dst->data, d.rstack * d.n, d.m, d.k);
+        st = rcu_gemm_tc_f32_dispatch(dev, lhs->data, rhs->data, bptr, dst->data, d.rstack * d.n, d.m, d.k, 1);
+        if (st != RCU_ERR_UNSUPPORTED) return st;
+    }
+    // Batched f32 products of the attention kind, A[b, M, K] . B[b, K, N] (or B given as [b, N, K] with
+    // trans_rhs): the tensor-core kernel wants both operands K-major, so an untransposed B is transposed
+    // into pooled scratch first (it is the small operand of these products).
+    if (!tl && !td && !bias && d.lstack == d.rstack && d.dstack == d.lstack && rcu_gemm_tc_f32_eligible(lhs->dt, rhs->dt, d.m, d.n, d.k)) {
+        const void* wptr = rhs->data;
+        void* scratch = nullptr;
+        st = RCU_OK;
+        if (!tr) {
+            st = rcu_alloc(dev, d.rstack * d.k * d.n * 4, &scratch);
+            if (st != RCU_OK) return st;
+            rcu_tensor src{RCU_F32, 3, {d.rstack, d.k, d.n, 1}, rhs->data};
+            rcu_tensor tdst{RCU_F32, 3, {d.rstack, d.n, d.k, 1}, scratch};
+            const uint32_t perm[3] = {0, 2, 1};
+            st = rcu_permute(dev, &src, perm, &tdst);
+            wptr = scratch;
+        }
+        if (st == RCU_OK) st = rcu_gemm_tc_f32_dispatch(dev, wptr, lhs->data, nullptr, dst->data, d.m, d.n, d.k, d.lstack);
+        if (scratch) rcu_free(dev, scratch);     // the pool reuses blocks in stream order
         if (st != RCU_ERR_UNSUPPORTED) return st;
     }
     const uint64_t numel = t_numel(lhs);

@@ -15,6 +15,7 @@ using gemvq8::mbar_wait;
 using gemvq8::mbar_wait_spin;
 using gemvq8::smem_u32;
 using gemvq8::tma_load_2d;
+using gemvq8::tma_load_3d;
 
 constexpr int TM = 128;          // tokens per tile (UMMA M)
 constexpr int TK = 64;           // K per stage: 64 f16 = 128 bytes = one swizzle row

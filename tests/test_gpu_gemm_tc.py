@@ -94,3 +94,16 @@ def test_gemm_tc_f32(dev, M, N, K, with_bias):
     y = dev.matmul(dev.from_numpy(w), dev.from_numpy(x), None if b is None else dev.from_numpy(b), False, True, True)
     assert y.shape == (M, N)
     check(y.to_numpy(), ref, 1e-4, f"f32 {M}x{N}x{K}")
+
+
+# batched f32 products of the attention kind (whisper/mha.rs:82-86): A[b,M,K] . B[b,K,N], and B given transposed
+@pytest.mark.parametrize("b,M,K,N,tr", [(6, 1500, 64, 1500, False), (6, 1500, 1500, 64, False), (3, 100, 36, 72, False),
+                                        (2, 130, 64, 200, True), (1, 64, 128, 64, False)])
+def test_gemm_tc_f32_batched(dev, b, M, K, N, tr):
+    g = np.random.Generator(np.random.PCG64(b * 1000 + M + K + N))
+    a = g.standard_normal((b, M, K)).astype(np.float32)
+    w = (g.standard_normal((b, N, K) if tr else (b, K, N)) * 0.1).astype(np.float32)
+    ref = orc.matmul(a, w, None, False, tr, False)
+    y = dev.matmul(dev.from_numpy(a), dev.from_numpy(w), None, False, tr, False)
+    assert y.shape == (b, M, N)
+    check(y.to_numpy(), ref, 1e-4, f"batched f32 {b}x{M}x{K}x{N} tr={tr}")
