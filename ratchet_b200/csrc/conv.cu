@@ -7,7 +7,15 @@
 //
 // A CTA computes a 64 (Cout) x 64 (Lout) output tile; input channels are consumed 8 at a time
 // through shared memory (input window and filter slab), each thread owning a 4 x 4 register tile.
+//
+// f32 problems large enough for the tensor cores take another route: the input is unfolded into
+// col[Lout, 3*Cin] (col[l, 3*ci + t] = x[ci, l*stride + t - pad], zero outside the input) and the product
+// y[Cout, Lout] = w[Cout, 3*Cin] . col^T runs on the split-TF32 tcgen05 GEMM with the bias added per row.
 #include "common.cuh"
+
+rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
+                                    uint64_t K, uint64_t batches, const void* bias_rows);
+bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
 
 namespace {
 
@@ -77,6 +85,33 @@ conv1d_k3_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __re
     }
 }
 
+// Unfold one batch of x [Cin, Lin] into col [Lout, 3*Cin].  A CTA takes 32 output positions x 32 input
+// channels: the input window goes through shared memory so that both the reads (along the length) and
+// the writes (96 consecutive floats per output position) are coalesced.
+template <int STRIDE>
+__global__ void __launch_bounds__(256)
+unfold_k3_kernel(const float* __restrict__ x, float* __restrict__ col, int Cin, int Lin, int Lout, int pad) {
+    constexpr int WIN = 31 * STRIDE + 3;
+    __shared__ float win[32][WIN + 1];
+    const int l0 = blockIdx.x * 32, ci0 = blockIdx.y * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = l0 * STRIDE - pad;
+    for (int r = warp; r < 32; r += 8) {
+        const int ci = ci0 + r;
+        for (int p = lane; p < WIN; p += 32) {
+            const int pos = p0 + p;
+            win[r][p] = (ci < Cin && pos >= 0 && pos < Lin) ? x[(size_t)ci * Lin + pos] : 0.f;
+        }
+    }
+    __syncthreads();
+    const int K = 3 * Cin;
+    const int width = min(32, Cin - ci0) * 3;
+    for (int idx = threadIdx.x; idx < 32 * 96; idx += 256) {
+        const int l = idx / 96, t = idx - l * 96;
+        if (l0 + l < Lout && t < width) col[(size_t)(l0 + l) * K + ci0 * 3 + t] = win[t / 3][l * STRIDE + t % 3];
+    }
+}
+
 }  // namespace
 
 extern "C" rcu_status rcu_conv1d(rcu_device* dev, const rcu_tensor* x, const rcu_tensor* w, const rcu_tensor* bias,
@@ -97,6 +132,23 @@ extern "C" rcu_status rcu_conv1d(rcu_device* dev, const rcu_tensor* x, const rcu
     dim3 grid((unsigned)((Lout + TLO - 1) / TLO), (unsigned)((Cout + TCO - 1) / TCO), (unsigned)B);
     RCU_REQUIRE(dev, grid.y <= 65535 && grid.z <= 65535, "conv1d: too many channels / batches");
     const void* bp = bias ? bias->data : nullptr;
+    if (rcu_gemm_tc_f32_eligible(w->dt, x->dt, Cout, Lout, 3 * Cin) && Cin <= 65535ull * 32 && Lin <= 0x3fffffffull) {
+        void* col = nullptr;
+        rcu_status st = rcu_alloc(dev, Lout * 3 * Cin * 4, &col);
+        if (st != RCU_OK) return st;
+        const dim3 ugrid((unsigned)((Lout + 31) / 32), (unsigned)((Cin + 31) / 32));
+        for (uint64_t b = 0; b < B && st == RCU_OK; ++b) {
+            const float* xb = (const float*)x->data + b * Cin * Lin;
+            if (stride == 1) unfold_k3_kernel<1><<<ugrid, 256, 0, dev->stream>>>(xb, (float*)col, (int)Cin, (int)Lin, (int)Lout, (int)padding);
+            else unfold_k3_kernel<2><<<ugrid, 256, 0, dev->stream>>>(xb, (float*)col, (int)Cin, (int)Lin, (int)Lout, (int)padding);
+            st = rcu_gemm_tc_f32_dispatch(dev, col, w->data, nullptr, (float*)dst->data + b * Cout * Lout, Cout, Lout, 3 * Cin, 1, bp);
+        }
+        rcu_free(dev, col);       // the pool reuses blocks in stream order
+        if (st != RCU_ERR_UNSUPPORTED) {
+            if (st == RCU_OK) RCU_LAUNCH_CHECK(dev);
+            return st;
+        }
+    }
 #define RCU_CONV(T, S) conv1d_k3_kernel<T, S><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (const T*)w->data, (const T*)bp, (T*)dst->data, (int)Cin, (int)Lin, (int)Cout, (int)Lout, (int)padding)
     if (x->dt == RCU_F32) { if (stride == 1) RCU_CONV(float, 1); else RCU_CONV(float, 2); }
     else if (x->dt == RCU_F16) { if (stride == 1) RCU_CONV(__half, 1); else RCU_CONV(__half, 2); }

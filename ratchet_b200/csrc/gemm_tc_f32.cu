@@ -54,6 +54,7 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreadsF32, 1)
 gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ bias,
+                   const float* __restrict__ bias_rows,
                    float* __restrict__ out, int M, int N, int K, int* status) {
     constexpr int A_BYTES = TM * TK32 * 4;        // 16 KiB
     constexpr int B_BYTES = BN * TK32 * 4;
@@ -153,6 +154,11 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 }
                 if (row < M) {
                     float* orow = out + (size_t)row * N + n0 + c;
+                    if (bias_rows) {                 // one value per output row (the transposed product of conv1d)
+                        const float br = bias_rows[row];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] += br;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         const int col = n0 + c + j;
@@ -206,15 +212,15 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 }
 
 template <int BN>
-rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, void* out, int M, int N, int K,
-                      int batches) {
+rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, const void* bias_rows, void* out,
+                      int M, int N, int K, int batches) {
     constexpr int STAGE = 2 * (TM * TK32 * 4 + BN * TK32 * 4);
     constexpr int STAGES = (192 * 1024) / STAGE;
     const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
     auto kern = gemm_tc_f32_kernel<BN, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batches);
-    kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (float*)out, M, N, K, dev->d_status);
+    kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (const float*)bias_rows, (float*)out, M, N, K, dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -243,18 +249,22 @@ bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, ui
 }
 
 rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
-                                    uint64_t K, uint64_t batches) {
+                                    uint64_t K, uint64_t batches, const void* bias_rows) {
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(bias)) & 15)
         return RCU_ERR_UNSUPPORTED;
     // tensor-map strides are multiples of 16 bytes; the grid's z extent is limited
-    if (batches < 1 || batches > 65535 || (batches > 1 && ((M * K) % 4 != 0 || (N * K) % 4 != 0 || (M * N) % 4 != 0 || bias))) return RCU_ERR_UNSUPPORTED;
+    if (batches < 1 || batches > 65535 || (batches > 1 && ((M * K) % 4 != 0 || (N * K) % 4 != 0 || (M * N) % 4 != 0 || bias || bias_rows))) return RCU_ERR_UNSUPPORTED;
     DevGuard g(dev->ordinal);
-    const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128) * batches;
-    const int bn = tiles128 >= (uint64_t)dev->sm_count ? 128 : 64;
+    // Tile width by whole waves over the SMs (one CTA per SM): a k-block of the 128-wide tile moves 1.35x
+    // the shared-memory bytes of the 64-wide one (the kernel's bound) for twice the columns.
+    const uint64_t mt = (M + TM - 1) / TM, sms = (uint64_t)dev->sm_count;
+    const uint64_t waves128 = (mt * ((N + 127) / 128) * batches + sms - 1) / sms;
+    const uint64_t waves64 = (mt * ((N + 63) / 64) * batches + sms - 1) / sms;
+    const int bn = (double)waves128 * 1.35 < (double)waves64 ? 128 : 64;
     CUtensorMap xmap, wmap;
     if (!make_map_f32_sw128(&xmap, x, batches, M, K, TM) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
         return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu x%llu)", (unsigned long long)M,
                         (unsigned long long)N, (unsigned long long)K, (unsigned long long)batches);
-    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K, (int)batches)
-                     : launch_f32<64>(dev, xmap, wmap, bias, y, (int)M, (int)N, (int)K, (int)batches);
+    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches)
+                     : launch_f32<64>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches);
 }

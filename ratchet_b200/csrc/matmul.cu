@@ -15,7 +15,7 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
 bool rcu_gemm_tc_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
 // f32 Linear on the tensor cores (split-TF32, f32-level accuracy)
 rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
-                                    uint64_t K, uint64_t batches);
+                                    uint64_t K, uint64_t batches, const void* bias_rows = nullptr);
 bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
 
 namespace {

@@ -418,6 +418,21 @@ def test_conv1d(dev, cin, lin, cout, stride):
     assert_close(got.to_numpy(), ref, 1e-4, "conv1d")
 
 
+@pytest.mark.parametrize("batch,cin,lin,cout,stride,pad", [(2, 36, 260, 40, 1, 1), (3, 68, 519, 100, 2, 1), (1, 32, 66, 32, 1, 0)])
+def test_conv1d_unfolded_batches(dev, batch, cin, lin, cout, stride, pad):
+    # shapes that take the unfold + tensor-core product: ragged channel tiles, several batches, no padding
+    g = rng(17)
+    x = g.standard_normal((batch, cin, lin)).astype(np.float32)
+    w = (g.standard_normal((cout, cin, 3)) * 0.05).astype(np.float32)
+    b = g.standard_normal(cout).astype(np.float32)
+    ref = orc.conv1d_k3(x, w, b, stride, pad)
+    got = dev.conv1d(dev.from_numpy(x), dev.from_numpy(w), dev.from_numpy(b), stride, pad)
+    assert got.shape == ref.shape
+    assert_close(got.to_numpy(), ref, 1e-4, "conv1d unfolded")
+    nb = dev.conv1d(dev.from_numpy(x), dev.from_numpy(w), None, stride, pad)
+    assert_close(nb.to_numpy(), orc.conv1d_k3(x, w, None, stride, pad), 1e-4, "conv1d unfolded, no bias")
+
+
 def test_allocator_reuses_blocks(dev):
     from ratchet_b200 import capi
     a = dev.empty(capi.F32, (123457,))
