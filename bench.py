@@ -353,15 +353,35 @@ def phi2_mlp_bench(dev, torch, stream):
             "peak_kind": f"of {kind}", "tflops": flops / us * 1e-6, "note": "weights (210 MB) exceed L2; lazy graph build + resolve each forward"}
 
 
-def whisper_encoder_bench(dev, torch, stream):
-    """Config 4: Whisper-tiny encoder forward in f32 through the lazy Tensor graph: mel [1,80,3000] U(-1,1),
+def _q8f_random(N, K, seed):
+    """Q8_0F buffer (f32 scales) of random int8 codes with scales that give weights of N(0, 0.02)-like size."""
+    from ratchet_b200 import capi
+    rng = np.random.Generator(np.random.PCG64(seed))
+    buf = np.zeros(capi.dtype_nbytes(capi.Q8_0F, N * K), np.uint8)
+    buf[: N * K].view(np.int8)[:] = rng.integers(-127, 128, N * K, dtype=np.int8)
+    off = capi.dtype_segments(capi.Q8_0F, N * K)[1]
+    buf[off: off + (N * K // 32) * 4].view(np.float32)[:] = (np.abs(rng.standard_normal(N * K // 32)) * 0.0002 + 0.0003).astype(np.float32)
+    return buf
+
+
+def whisper_encoder_bench(dev, torch, stream, quantised=False):
+    """Config 4: Whisper-tiny encoder forward through the lazy Tensor graph: mel [1,80,3000] U(-1,1),
     conv stem, sinusoidal positions, 4 pre-LN blocks (d 384, 6 heads, MLP 1536), final LayerNorm;
-    weights N(0, 0.02)."""
+    f32 activations; weights N(0, 0.02) in f32, or (quantised) the Linear weights as Q8_0F buffers."""
     from ratchet_b200 import Tensor, callers, capi, nn
     g = np.random.Generator(np.random.PCG64(0))
     d, H, mlp, n_ctx = 384, 6, 1536, 1500
-    t = lambda a: Tensor.from_data(np.ascontiguousarray(a, np.float32), device=dev)
-    w = lambda *shape: g.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+    seeds = iter(range(1000, 2000))
+
+    def w(*shape):
+        if quantised and len(shape) == 2:
+            return None, shape
+        return g.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+
+    def t(a):   # Linear weights come as (None, shape) when they are to be quantised
+        if isinstance(a, tuple):
+            return Tensor.from_quantized(_q8f_random(a[1][0], a[1][1], next(seeds)), capi.Q8_0F, a[1], dev)
+        return Tensor.from_data(np.ascontiguousarray(a, np.float32), device=dev)
     inc = np.log(10000.0) / (d // 2 - 1)
     ang = np.arange(n_ctx)[:, None] * np.exp(-inc * np.arange(d // 2))[None, :]
     pos = np.concatenate([np.sin(ang), np.cos(ang)], 1)
@@ -383,7 +403,8 @@ def whisper_encoder_bench(dev, torch, stream):
     # flops: conv stem + per block (4 projections, QK^T, PV, two MLP matmuls)
     flops = 2.0 * 3000 * d * 80 * 3 + 2.0 * n_ctx * d * d * 3 + 4 * (2.0 * n_ctx * d * d * 4 + 2 * 2.0 * n_ctx * n_ctx * d + 2 * 2.0 * n_ctx * d * mlp)
     return {"us_per_forward": us, "kernels_per_forward": int(launches), "tflops": flops / us * 1e-6,
-            "note": "f32 activations and weights; mixed launch- and compute-bound (241 MB of 1500x1500 score matrices per layer pass through L2)"}
+            "note": ("f32 activations, Q8_0F Linear weights (dequantised into pooled scratch, then the f32 tensor-core GEMM)" if quantised else
+                     "f32 activations and weights") + "; mixed launch- and compute-bound (241 MB of 1500x1500 score matrices per layer pass through L2)"}
 
 
 def phi3_decode_bytes(c):
@@ -628,6 +649,7 @@ def run_ours(args):
             extras["phi2_mlp_f32"] = phi2_mlp_bench(dev, torch, stream)
         if want("whisper"):
             extras["whisper_tiny_encoder_f32"] = whisper_encoder_bench(dev, torch, stream)
+            extras["whisper_tiny_encoder_q8_0f"] = whisper_encoder_bench(dev, torch, stream, quantised=True)
         if want("decode"):
             extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
     if world > 1 and not args.rows and not args.no_extras:

@@ -27,6 +27,11 @@ namespace {
 
 using namespace tc;
 
+// kind::tf32 reads the upper 19 bits of each 32-bit operand word: the raw f32 tile already is the hi
+// operand (x & 0xFFFFE000), so only the lo tile has to be written.  1 = also store the masked words.
+#ifndef RCU_TF32_WRITE_HI
+#define RCU_TF32_WRITE_HI 0
+#endif
 constexpr int TK32 = 32;                 // K per stage: 32 f32 = 128 bytes = one swizzle row
 constexpr int kConvWarps = 8;
 // accumulators: the hi x hi products rotate over `mains`, the small products over `corrs` (512 columns in all)
@@ -55,7 +60,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreadsF32, 1)
 gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ bias,
                    const float* __restrict__ bias_rows,
-                   float* __restrict__ out, int M, int N, int K, int* status) {
+                   float* __restrict__ out, int M, int N, int K, int kb_per_split, int* status) {
     constexpr int A_BYTES = TM * TK32 * 4;        // 16 KiB
     constexpr int B_BYTES = BN * TK32 * 4;
     constexpr int RAW = A_BYTES + B_BYTES;        // hi tiles (A then B); the lo tiles follow in the same order
@@ -71,9 +76,14 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * BN;
-    const int nk = (K + TK32 - 1) / TK32;
-    const int batch = blockIdx.z;            // independent problems (attention heads): third coordinate of both maps
-    out += (size_t)batch * M * N;
+    // blockIdx.z is either the problem of a batch (attention heads: third coordinate of both maps) or, when
+    // kb_per_split > 0, the slice of K this CTA sums: slice z covers k-blocks [z * kb_per_split, ...) of the
+    // one problem and writes its partial result to slab z of `out`.
+    const int nk_all = (K + TK32 - 1) / TK32;
+    const int kb0 = kb_per_split > 0 ? (int)blockIdx.z * kb_per_split : 0;
+    const int nk = kb_per_split > 0 ? min(kb_per_split, nk_all - kb0) : nk_all;
+    const int batch = kb_per_split > 0 ? 0 : (int)blockIdx.z;
+    out += (size_t)blockIdx.z * M * N;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -101,8 +111,8 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 if (it >= STAGES && !mbar_wait_spin(&empty[s], ((it / STAGES) - 1) & 1, abort_flag, status)) break;
                 unsigned char* st = smem + s * STAGE;
                 mbar_expect_tx(&raw_full[s], RAW);
-                tma_load_3d(st, &xmap, it * TK32, m0, batch, &raw_full[s]);
-                tma_load_3d(st + A_BYTES, &wmap, it * TK32, n0, batch, &raw_full[s]);
+                tma_load_3d(st, &xmap, (kb0 + it) * TK32, m0, batch, &raw_full[s]);
+                tma_load_3d(st + A_BYTES, &wmap, (kb0 + it) * TK32, n0, batch, &raw_full[s]);
             }
         }
     } else if (warp == 1) {
@@ -191,12 +201,14 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 #pragma unroll 4
             for (int i = dt; i < VECS; i += CT) {
                 const uint4 x = hi[i];
-                uint4 h, l;
-                h.x = x.x & 0xFFFFE000u; l.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(h.x));
-                h.y = x.y & 0xFFFFE000u; l.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(h.y));
-                h.z = x.z & 0xFFFFE000u; l.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(h.z));
-                h.w = x.w & 0xFFFFE000u; l.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(h.w));
-                hi[i] = h;
+                uint4 l;
+                l.x = __float_as_uint(__uint_as_float(x.x) - __uint_as_float(x.x & 0xFFFFE000u));
+                l.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(x.y & 0xFFFFE000u));
+                l.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(x.z & 0xFFFFE000u));
+                l.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xFFFFE000u));
+#if RCU_TF32_WRITE_HI
+                hi[i] = make_uint4(x.x & 0xFFFFE000u, x.y & 0xFFFFE000u, x.z & 0xFFFFE000u, x.w & 0xFFFFE000u);
+#endif
                 lo[i] = l;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -211,16 +223,38 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     }
 }
 
+// out = sum of the `splits` partial results (in slab order) + bias per column / per row
+__global__ void __launch_bounds__(256)
+sum_splits_kernel(const float4* __restrict__ part, int splits, size_t slab4, const float* __restrict__ bias,
+                  const float* __restrict__ bias_rows, float4* __restrict__ out, int N4) {
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < slab4; i += (size_t)gridDim.x * 256) {
+        float4 a = part[i];
+        for (int s = 1; s < splits; ++s) {
+            const float4 b = part[(size_t)s * slab4 + i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (bias) {
+            const float4 b = reinterpret_cast<const float4*>(bias)[i % N4];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        if (bias_rows) {
+            const float b = bias_rows[i / N4];
+            a.x += b; a.y += b; a.z += b; a.w += b;
+        }
+        out[i] = a;
+    }
+}
+
 template <int BN>
 rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, const void* bias_rows, void* out,
-                      int M, int N, int K, int batches) {
+                      int M, int N, int K, int batches, int kb_per_split) {
     constexpr int STAGE = 2 * (TM * TK32 * 4 + BN * TK32 * 4);
     constexpr int STAGES = (192 * 1024) / STAGE;
     const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
     auto kern = gemm_tc_f32_kernel<BN, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batches);
-    kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (const float*)bias_rows, (float*)out, M, N, K, dev->d_status);
+    kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (const float*)bias_rows, (float*)out, M, N, K, kb_per_split, dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -265,6 +299,30 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
     if (!make_map_f32_sw128(&xmap, x, batches, M, K, TM) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
         return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu x%llu)", (unsigned long long)M,
                         (unsigned long long)N, (unsigned long long)K, (unsigned long long)batches);
-    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches)
-                     : launch_f32<64>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches);
+    // A grid that fills less than half of the SMs with a long K splits K over blockIdx.z: every slice
+    // writes a partial result to pooled scratch and one pass sums the slices in order (deterministic).
+    const uint64_t tiles = mt * ((N + bn - 1) / bn), nk = (K + TK32 - 1) / TK32;
+    constexpr uint64_t kMinBlocksPerSplit = 24;
+    uint64_t splits = 1;
+    if (batches == 1 && tiles * 2 <= sms) splits = std::min<uint64_t>(sms / tiles, nk / kMinBlocksPerSplit);
+    if (splits > 1 && M * N % 4 == 0) {
+        const uint64_t kbps = (nk + splits - 1) / splits;
+        splits = (nk + kbps - 1) / kbps;
+        void* part = nullptr;
+        rcu_status st = rcu_alloc(dev, splits * M * N * 4, &part);
+        if (st != RCU_OK) return st;
+        st = bn == 128 ? launch_f32<128>(dev, xmap, wmap, nullptr, nullptr, part, (int)M, (int)N, (int)K, (int)splits, (int)kbps)
+                       : launch_f32<64>(dev, xmap, wmap, nullptr, nullptr, part, (int)M, (int)N, (int)K, (int)splits, (int)kbps);
+        if (st == RCU_OK) {
+            const size_t slab4 = (size_t)(M * N / 4);
+            const int grid = (int)std::min<size_t>((slab4 + 255) / 256, (size_t)dev->sm_count * 8);
+            sum_splits_kernel<<<grid, 256, 0, dev->stream>>>((const float4*)part, (int)splits, slab4, (const float*)bias, (const float*)bias_rows,
+                                                             (float4*)y, (int)(N / 4));
+            RCU_LAUNCH_CHECK(dev);
+        }
+        rcu_free(dev, part);      // the pool reuses blocks in stream order
+        return st;
+    }
+    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches, 0)
+                     : launch_f32<64>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches, 0);
 }

@@ -243,6 +243,21 @@ rcu_status rcu_matmul(rcu_device* dev, const rcu_tensor* lhs, const rcu_tensor* 
         st = rcu_gemm_tc_f32_dispatch(dev, lhs->data, rhs->data, bptr, dst->data, d.rstack * d.n, d.m, d.k, 1);
         if (st != RCU_ERR_UNSUPPORTED) return st;
     }
+    // Quantised weights with f32 activations (Q8_0F / Q4_KF Linear, the quantised Whisper graphs): the
+    // weights are dequantised once into pooled scratch (bit-exact, as the CPU path does for every
+    // quantised op) and the product runs on the f32 tensor-core kernel.
+    if (!tl && tr && td && d.lstack == 1 && (lhs->dt == RCU_Q8_0F || lhs->dt == RCU_Q4_KF) && rhs->dt == RCU_F32 &&
+        rcu_gemm_tc_f32_eligible(RCU_F32, RCU_F32, d.rstack * d.n, d.m, d.k)) {
+        void* wf = nullptr;
+        st = rcu_alloc(dev, d.m * d.k * 4, &wf);
+        if (st != RCU_OK) return st;
+        rcu_tensor wsrc{lhs->dt, 2, {d.m, d.k, 1, 1}, lhs->data};
+        rcu_tensor wdst{RCU_F32, 2, {d.m, d.k, 1, 1}, wf};
+        st = rcu_dequantize(dev, &wsrc, &wdst);
+        if (st == RCU_OK) st = rcu_gemm_tc_f32_dispatch(dev, wf, rhs->data, bptr, dst->data, d.rstack * d.n, d.m, d.k, 1);
+        rcu_free(dev, wf);      // the pool reuses blocks in stream order
+        if (st != RCU_ERR_UNSUPPORTED) return st;
+    }
     // Batched f32 products of the attention kind, A[b, M, K] . B[b, K, N] (or B given as [b, N, K] with
     // trans_rhs): the tensor-core kernel wants both operands K-major, so an untransposed B is transposed
     // into pooled scratch first (it is the small operand of these products).
