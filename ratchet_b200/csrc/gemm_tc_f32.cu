@@ -15,10 +15,14 @@
 // tensor-memory columns are used), which the epilogue adds up with ordinary rounded f32 additions.
 //
 // Structure as gemm_tc.cu: TMA brings 128 x 32 (activations) and BN x 32 (weights) f32 tiles,
-// 128-byte swizzled, into a shared-memory ring; eight converting warps rewrite each raw tile in place
-// as its hi part and write the lo part to a twin tile at the same swizzled offsets (so no swizzle
-// arithmetic is needed); one thread issues twelve tcgen05.mma kind::tf32 (K = 8) per stage; four warps
-// read the f32 accumulators from tensor memory, add the bias and store.  Every wait is bounded.
+// 128-byte swizzled, into a shared-memory ring; the raw tile serves as the hi operand (the tensor core
+// reads only the upper 19 bits of a word) and eight converting warps write the lo part to a twin tile at
+// the same swizzled offsets (so no swizzle arithmetic is needed); one thread issues twelve tcgen05.mma
+// kind::tf32 (K = 8) per stage; four warps read the f32 accumulators from tensor memory, add the bias
+// and store.  The kernel is bound by shared-memory bandwidth (TMA fill, lo pass, three operand reads per
+// k-step), so the tile width is chosen by whole waves and short grids split K over blockIdx.z with an
+// ordered sum of the slices.  blockIdx.z otherwise indexes independent problems (attention heads).
+// Every wait is bounded.
 #include <cstdlib>
 
 #include "tc_common.cuh"
@@ -27,11 +31,8 @@ namespace {
 
 using namespace tc;
 
-// kind::tf32 reads the upper 19 bits of each 32-bit operand word: the raw f32 tile already is the hi
-// operand (x & 0xFFFFE000), so only the lo tile has to be written.  1 = also store the masked words.
-#ifndef RCU_TF32_WRITE_HI
-#define RCU_TF32_WRITE_HI 0
-#endif
+// kind::tf32 reads the upper 19 bits of each 32-bit operand word (the parity tests hold only if it does):
+// the raw f32 tile already is the hi operand x & 0xFFFFE000, so only the lo tile x - hi is written.
 constexpr int TK32 = 32;                 // K per stage: 32 f32 = 128 bytes = one swizzle row
 constexpr int kConvWarps = 8;
 // accumulators: the hi x hi products rotate over `mains`, the small products over `corrs` (512 columns in all)
@@ -187,7 +188,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             }
         }
     } else {
-        // converting warps: raw tile -> hi (in place) and lo (twin tile, same offsets)
+        // converting warps: raw tile (= hi as the tensor core reads it) -> lo (twin tile, same offsets)
         constexpr int CT = kConvWarps * 32;
         constexpr int VECS = RAW / 16;
         const int dt = threadIdx.x - kThreadsTc;
@@ -206,9 +207,6 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 l.y = __float_as_uint(__uint_as_float(x.y) - __uint_as_float(x.y & 0xFFFFE000u));
                 l.z = __float_as_uint(__uint_as_float(x.z) - __uint_as_float(x.z & 0xFFFFE000u));
                 l.w = __float_as_uint(__uint_as_float(x.w) - __uint_as_float(x.w & 0xFFFFE000u));
-#if RCU_TF32_WRITE_HI
-                hi[i] = make_uint4(x.x & 0xFFFFE000u, x.y & 0xFFFFE000u, x.z & 0xFFFFE000u, x.w & 0xFFFFE000u);
-#endif
                 lo[i] = l;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -17,6 +17,8 @@ bool rcu_gemm_tc_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64
 rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
                                     uint64_t K, uint64_t batches, const void* bias_rows = nullptr);
 bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
+rcu_status rcu_gemv_q4k_dispatch(rcu_device* dev, int lhs_dt, const void* w, int act_dt, const void* x, const void* bias, void* y,
+                                 uint64_t N, uint64_t K);
 
 namespace {
 
@@ -231,7 +233,8 @@ rcu_status rcu_matmul(rcu_device* dev, const rcu_tensor* lhs, const rcu_tensor* 
 
     // GEMV: rhs squeezes to a vector and lhs is not transposed (mod.rs:717-718)
     const bool rhs_vector = d.rstack == 1 && d.n == 1;
-    if (rhs_vector && !tl && d.lstack == 1 && d.dstack == 1 && lhs->dt != RCU_BF16 && !dt_is_q4k(lhs->dt)) {
+    if (rhs_vector && !tl && d.lstack == 1 && d.dstack == 1 && lhs->dt != RCU_BF16) {
+        if (dt_is_q4k(lhs->dt)) return rcu_gemv_q4k_dispatch(dev, lhs->dt, lhs->data, rhs->dt, rhs->data, bptr, dst->data, d.m, d.k);
         return rcu_gemv_dispatch(dev, lhs->dt, lhs->data, rhs->dt, rhs->data, bptr, dst->data, d.m, d.k);
     }
     // Linear convention W[N,K] . x[M,K]^T -> [M,N]: tensor-core path when the shape qualifies

@@ -181,6 +181,9 @@ def _gemv(dev, rng, which):
     if which == "gemv_f16":
         w = dev.from_numpy((_rand_f16(rng, N * K).astype(np.float32) * 0.02).astype(np.float16).reshape(N, K))
         nbytes = N * K * 2
+    elif which == "gemv_q4k":
+        w = dev.from_quantized(_q4k_buffer(rng, N * K), capi.Q4_KH, (N, K))
+        nbytes = N * K // 2 + N * K // 256 * 16
     else:
         w = dev.from_quantized(_q8_buffer(rng, N * K, capi.Q8_0H), capi.Q8_0H, (N, K))
         nbytes = N * K + N * K // 16
@@ -250,6 +253,7 @@ CASES = [
     Case("dequant_q4k", lambda d, r: _dequant(d, r, "dequant_q4k"), "dequant_q4k_kernel"),
     Case("gemv_f16", lambda d, r: _gemv(d, r, "gemv_f16"), "gemv_float_kernel"),
     Case("gemv_q8", lambda d, r: _gemv(d, r, "gemv_q8"), "gemv_q8_kernel"),
+    Case("gemv_q4k", lambda d, r: _gemv(d, r, "gemv_q4k"), "gemv_q4k_kernel"),
     Case("gemm_f32_phi2_mlp", lambda d, r: _gemm(d, r, "gemm_simt_f32"), "gemm_tc_f32_kernel (M=64, N=10240, K=2560)"),
     Case("gemm_tc_f32", lambda d, r: _gemm(d, r, "gemm_tc_f32"), "gemm_tc_f32_kernel"),
     Case("gemm_tc_f16", lambda d, r: _gemm(d, r, "gemm_tc_f16"), "gemm_tc_kernel"),

@@ -109,6 +109,30 @@ def test_gemv_q8(dev, pair, N, K):
         assert_matmul_close(y.to_numpy().reshape(-1), ref, 1e-2 if half_x else 1e-4, f"gemv {pair} {N}x{K}")
 
 
+# Q4_K weights with a vector: no kernel in the reference (`(gemv, q4)` is todo!, ops/matmul/mod.rs:746); the
+# meaning is the dequantised product, as for every quantised op
+@pytest.mark.parametrize("pair", ["Q4_KF/F32", "Q4_KH/F16"])
+@pytest.mark.parametrize("N,K", [(1, 256), (5, 512), (33, 768), (1000, 1024), (3072, 3072), (3071, 1280), (8192, 3072), (40, 16384)])
+def test_gemv_q4k(dev, pair, N, K):
+    from ratchet_b200 import capi
+    g = rng(N * 17 + K)
+    half = pair.startswith("Q4_KH")
+    w = (g.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = g.standard_normal((1, K)).astype(np.float16 if half else np.float32)
+    bias = g.standard_normal(N).astype(x.dtype)
+    buf = orc.quantize_q4k(w, half)
+    wd = orc.dequantize_q4k(buf, (N, K), half)
+    dw = dev.from_quantized(buf, capi.Q4_KH if half else capi.Q4_KF, (N, K))
+    for b in (None, bias):
+        ref = orc.matmul(wd, x, b, False, True, True)
+        y = dev.matmul(dw, dev.from_numpy(x), None if b is None else dev.from_numpy(b), False, True, True)
+        assert y.shape == (1, N) and y.dt == (capi.F16 if half else capi.F32)
+        assert_matmul_close(y.to_numpy(), ref, 1e-2 if half else 1e-4, f"gemv {pair} {N}x{K}")
+    # a zero vector gives the bias (the activation scale is guarded)
+    y0 = dev.matmul(dw, dev.from_numpy(np.zeros_like(x)), dev.from_numpy(bias), False, True, True)
+    assert np.array_equal(y0.to_numpy().reshape(-1), bias)
+
+
 @pytest.mark.parametrize("dt", ["f32", "f16"])
 @pytest.mark.parametrize("N,K", [(1, 1), (3, 7), (64, 100), (500, 1024), (3072, 3072), (96, 1025)])
 def test_gemv_float(dev, dt, N, K):
