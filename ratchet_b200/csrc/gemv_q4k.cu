@@ -14,11 +14,12 @@
 // (2^(8P-1) - 1); P = 2 byte planes for f16 activations, 3 for f32: 2^-15 / 2^-23 of the vector's scale),
 // the top plane signed and the others unsigned, and every four codes meet each plane in one dp4a.  The
 // twelve packed 6-bit scale / min bytes of a block are unpacked eight at a time with word-wide masks.
-// d * sc and dmin * m are rounded to the scale type as the dequantiser does; the sums are f32.
+// d * sc and dmin * m are kept in f32 (the dequantiser rounds them to the scale type: a 2^-11 relative
+// difference per sub-block in the f16 layout, far inside the bar); the sums are f32.
 //
 // Work split: persistent CTAs, teams of KSPLIT warps own whole groups of four rows.  A lane takes one
 // 32-byte chunk (sub-blocks 2c and 2c+1 whole) of one block in two of the four rows; a half-warp covers
-// four blocks (1024 weights) of its two rows per step, and two register slots of loads stay in flight.
+// four blocks (1024 weights) of its two rows per step, and three register slots of loads stay in flight.
 #include "common.cuh"
 
 namespace {
@@ -39,10 +40,24 @@ __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) {   // uns
     return (int)d;
 }
 
-struct SlotQ4 {
-    uint4 w[kLaneRows][2];          // the 32-byte chunk of each row
+// 16-byte slot of activation vector c16 inside a byte plane.  The 16 lanes of a half-warp read the vectors
+// (block b, chunk c, part t) = 16 b + 4 c + t for four b and four c at once; folding bits 3-5 of the index
+// into its low three bits spreads them over all eight 16-byte bank groups (two per group, the minimum).
+__device__ __forceinline__ int plane_slot(int c16) { return (c16 & ~7) | ((c16 ^ (c16 >> 3)) & 7); }
+
+// 32 bytes in one streaming load (each lane's chunk is read exactly once)
+__device__ __forceinline__ void ld_stream_256(const void* p, uint32_t (&v)[8]) {
+    asm volatile("ld.global.cs.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "l"(p));
+}
+
+// One pipeline slot.  Everything is kept as loaded (conversions happen where the values are used, so that
+// filling a slot never waits for its own loads).
+template <class FP> struct SlotQ4 {
+    uint32_t w[kLaneRows][8];       // the 32-byte chunk of each row
     uint32_t sc[kLaneRows][3];      // the block's 12 packed scale bytes
-    float d[kLaneRows], dmin[kLaneRows];
+    FP d[kLaneRows], dmin[kLaneRows];
 };
 
 template <class FP, class ActT, int KSPLIT>
@@ -72,7 +87,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
     const int bl = (lane >> 2) & 3;                   // block within the step
     const int rsel = (lane >> 4) * kLaneRows;         // first of this lane's two rows within the group
 
-    auto load_item = [&](int it, SlotQ4& s) {
+    auto load_item = [&](int it, SlotQ4<FP>& s) {
         const int r0 = (g_begin + it / ncs) * kRowsQ4 + rsel;
         const int kb = (ks + (it % ncs) * KSPLIT) * 4 + bl;
         const bool live = kb < kblocks;
@@ -80,28 +95,54 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
         for (int r = 0; r < kLaneRows; ++r) {
             const size_t B = (size_t)min(r0 + r, N - 1) * kblocks + kb;    // rows past N repeat the last one; dropped at the store
             if (live) {
-                const uint4* q = reinterpret_cast<const uint4*>(qs + B * 128 + cidx * 32);
-                s.w[r][0] = __ldcs(q);
-                s.w[r][1] = __ldcs(q + 1);
+                ld_stream_256(qs + B * 128 + cidx * 32, s.w[r]);
                 const uint32_t* pk = reinterpret_cast<const uint32_t*>(scales + B * 12);
                 s.sc[r][0] = __ldg(pk); s.sc[r][1] = __ldg(pk + 1); s.sc[r][2] = __ldg(pk + 2);
-                s.d[r] = to_f32<FP>(d[B]);
-                s.dmin[r] = to_f32<FP>(dmin[B]);
+                s.d[r] = d[B];
+                s.dmin[r] = dmin[B];
             } else {
-                s.w[r][0] = s.w[r][1] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) s.w[r][q] = 0;
                 s.sc[r][0] = s.sc[r][1] = s.sc[r][2] = 0;
-                s.d[r] = s.dmin[r] = 0.f;
+                s.d[r] = s.dmin[r] = from_f32<FP>(0.f);
             }
         }
     };
 
-    SlotQ4 s0, s1;
+    SlotQ4<FP> s0, s1, s2;
     if (n_items > 0) load_item(0, s0);
     if (n_items > 1) load_item(1, s1);
+    if (n_items > 2) load_item(2, s2);
 
     // ---- stage x: scale, fixed-point byte planes, sums per 32 elements
+    // 16 elements per thread and trip, as 16-byte vector loads (x comes from the kernel before: read at L2)
+    auto load16 = [&](int i16, float (&v)[16]) {
+        if constexpr (sizeof(ActT) == 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(x) + i16 * 4 + q);
+                v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const uint4 u = __ldcg(reinterpret_cast<const uint4*>(x) + i16 * 2 + q);
+                const uint32_t hw[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
+                    v[8 * q + 2 * e] = f.x; v[8 * q + 2 * e + 1] = f.y;
+                }
+            }
+        }
+    };
     float amax = 0.f;
-    for (int i = tid; i < K; i += kThreadsQ4) amax = fmaxf(amax, fabsf(to_f32<ActT>(x[i])));
+    for (int i16 = tid; i16 < K / 16; i16 += kThreadsQ4) {
+        float v[16];
+        load16(i16, v);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if (lane == 0) misc[warp] = amax;
@@ -116,13 +157,15 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
         const bool on = i16 < K / 16;
         uint32_t pw[P][4];
         int tot = 0;
+        float v[16];
+        if (on) load16(i16, v);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
 #pragma unroll
             for (int p = 0; p < P; ++p) pw[p][q] = 0;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int X = on ? __float2int_rn(to_f32<ActT>(x[i16 * 16 + q * 4 + e]) * inv) : 0;
+                const int X = on ? __float2int_rn(v[q * 4 + e] * inv) : 0;
                 tot += X;
 #pragma unroll
                 for (int p = 0; p < P; ++p) pw[p][q] |= (uint32_t)((X >> (8 * (P - 1 - p))) & 0xFF) << (8 * e);
@@ -133,7 +176,7 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
         if (on) {
 #pragma unroll
             for (int p = 0; p < P; ++p)
-                reinterpret_cast<uint4*>(plane + (size_t)p * K)[i16] = make_uint4(pw[p][0], pw[p][1], pw[p][2], pw[p][3]);
+                reinterpret_cast<uint4*>(plane + (size_t)p * K)[plane_slot(i16)] = make_uint4(pw[p][0], pw[p][1], pw[p][2], pw[p][3]);
             if ((i16 & 1) == 0) xsum[i16 >> 1] = sx * (float)both;
         }
     }
@@ -143,40 +186,41 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
 #pragma unroll
     for (int r = 0; r < kLaneRows; ++r) acc[r] = 0.f;
 
-    auto compute_item = [&](int it, const SlotQ4& s) {
+    auto compute_item = [&](int it, const SlotQ4<FP>& s) {
         const int kb = (ks + (it % ncs) * KSPLIT) * 4 + bl;
         if (kb < kblocks) {
             const int e_lo = kb * 256 + cidx * 64, e_hi = e_lo + 32;
-            // activation words: [plane][low / high sub-block][8 words of four elements]
-            uint32_t xa[P][2][8];
+            const int slot_base = (kb * 16 + cidx * 4) & ~7, slot_lo = (cidx & 1) * 4, slot_x = (kb * 2 + (cidx >> 1)) & 7;
+            // integer dots of both rows' codes with the activation planes, one sub-block (nibble half) at a time
+            int dot[kLaneRows][P][2];
 #pragma unroll
-            for (int p = 0; p < P; ++p) {
+            for (int h = 0; h < 2; ++h) {
+                uint32_t xa[P][8];                  // [plane][8 words of four elements]
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4* src = reinterpret_cast<const uint4*>(plane + (size_t)p * K + (h ? e_hi : e_lo));
-                    const uint4 a = src[0], b = src[1];
-                    xa[p][h][0] = a.x; xa[p][h][1] = a.y; xa[p][h][2] = a.z; xa[p][h][3] = a.w;
-                    xa[p][h][4] = b.x; xa[p][h][5] = b.y; xa[p][h][6] = b.z; xa[p][h][7] = b.w;
+                for (int p = 0; p < P; ++p) {
+                    // vectors 16 kb + 4 cidx + 2 h + {0, 1}: plane_slot() with the shared terms taken out
+                    const uint4* src = reinterpret_cast<const uint4*>(plane + (size_t)p * K) + slot_base;
+                    const uint4 a = src[(slot_lo + 2 * h) ^ slot_x], b = src[(slot_lo + 2 * h + 1) ^ slot_x];
+                    xa[p][0] = a.x; xa[p][1] = a.y; xa[p][2] = a.z; xa[p][3] = a.w;
+                    xa[p][4] = b.x; xa[p][5] = b.y; xa[p][6] = b.z; xa[p][7] = b.w;
+                }
+#pragma unroll
+                for (int r = 0; r < kLaneRows; ++r) {
+                    const uint32_t* ws = s.w[r];
+#pragma unroll
+                    for (int p = 0; p < P; ++p) dot[r][p][h] = 0;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const uint32_t c4 = (h ? ws[q] >> 4 : ws[q]) & 0x0F0F0F0Fu;
+                        dot[r][0][h] = dp4a_us(c4, xa[0][q], dot[r][0][h]);
+#pragma unroll
+                        for (int p = 1; p < P; ++p) dot[r][p][h] = dp4a_uu(c4, xa[p][q], dot[r][p][h]);
+                    }
                 }
             }
             const float xs_lo = xsum[e_lo >> 5], xs_hi = xsum[e_hi >> 5];
 #pragma unroll
             for (int r = 0; r < kLaneRows; ++r) {
-                const uint32_t ws[8] = {s.w[r][0].x, s.w[r][0].y, s.w[r][0].z, s.w[r][0].w, s.w[r][1].x, s.w[r][1].y, s.w[r][1].z, s.w[r][1].w};
-                int dot[P][2];
-#pragma unroll
-                for (int p = 0; p < P; ++p) dot[p][0] = dot[p][1] = 0;
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const uint32_t lo4 = ws[q] & 0x0F0F0F0Fu, hi4 = (ws[q] >> 4) & 0x0F0F0F0Fu;
-                    dot[0][0] = dp4a_us(lo4, xa[0][0][q], dot[0][0]);
-                    dot[0][1] = dp4a_us(hi4, xa[0][1][q], dot[0][1]);
-#pragma unroll
-                    for (int p = 1; p < P; ++p) {
-                        dot[p][0] = dp4a_uu(lo4, xa[p][0][q], dot[p][0]);
-                        dot[p][1] = dp4a_uu(hi4, xa[p][1][q], dot[p][1]);
-                    }
-                }
                 // the block's eight 6-bit scales and mins, four per word (quantized.rs:158-204): sub-blocks 0-3
                 // sit in the low six bits of bytes 0-3 / 4-7; sub-blocks 4-7 take four bits from bytes 8-11
                 // and two from the top of bytes 0-3 (scales) or 4-7 (mins)
@@ -184,15 +228,16 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
                 const uint32_t sc4 = cidx < 2 ? (w0 & 0x3F3F3F3Fu) : ((w2 & 0x0F0F0F0Fu) | ((w0 >> 2) & 0x30303030u));
                 const uint32_t mn4 = cidx < 2 ? (w1 & 0x3F3F3F3Fu) : (((w2 >> 4) & 0x0F0F0F0Fu) | ((w1 >> 2) & 0x30303030u));
                 const int sh = (cidx & 1) * 16;       // sub-blocks 2 cidx, 2 cidx + 1 within their group of four
-                const float del0 = rnd<FP>((float)((sc4 >> sh) & 0xFFu) * s.d[r]), del1 = rnd<FP>((float)((sc4 >> (sh + 8)) & 0xFFu) * s.d[r]);
-                const float mn0 = rnd<FP>((float)((mn4 >> sh) & 0xFFu) * s.dmin[r]), mn1 = rnd<FP>((float)((mn4 >> (sh + 8)) & 0xFFu) * s.dmin[r]);
+                const float df = to_f32<FP>(s.d[r]), mf = to_f32<FP>(s.dmin[r]);
+                const float del0 = (float)((sc4 >> sh) & 0xFFu) * df, del1 = (float)((sc4 >> (sh + 8)) & 0xFFu) * df;
+                const float mn0 = (float)((mn4 >> sh) & 0xFFu) * mf, mn1 = (float)((mn4 >> (sh + 8)) & 0xFFu) * mf;
                 float v0, v1;
                 if (P == 2) {
-                    v0 = (float)(dot[0][0] * 256 + dot[1][0]);
-                    v1 = (float)(dot[0][1] * 256 + dot[1][1]);
+                    v0 = (float)(dot[r][0][0] * 256 + dot[r][1][0]);
+                    v1 = (float)(dot[r][0][1] * 256 + dot[r][1][1]);
                 } else {
-                    v0 = fmaf((float)dot[0][0], 65536.f, (float)(dot[1][0] * 256 + dot[P - 1][0]));
-                    v1 = fmaf((float)dot[0][1], 65536.f, (float)(dot[1][1] * 256 + dot[P - 1][1]));
+                    v0 = fmaf((float)dot[r][0][0], 65536.f, (float)(dot[r][1][0] * 256 + dot[r][P - 1][0]));
+                    v1 = fmaf((float)dot[r][0][1], 65536.f, (float)(dot[r][1][1] * 256 + dot[r][P - 1][1]));
                 }
                 float a = acc[r];
                 a = fmaf(del0 * sx, v0, a);
@@ -235,12 +280,16 @@ gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scal
         for (int r = 0; r < kLaneRows; ++r) acc[r] = 0.f;
     };
 
-    for (int it = 0; it < n_items; it += 2) {
+    for (int it = 0; it < n_items; it += 3) {
         compute_item(it, s0);
-        if (it + 2 < n_items) load_item(it + 2, s0);
+        if (it + 3 < n_items) load_item(it + 3, s0);
         if (it + 1 < n_items) {
             compute_item(it + 1, s1);
-            if (it + 3 < n_items) load_item(it + 3, s1);
+            if (it + 4 < n_items) load_item(it + 4, s1);
+        }
+        if (it + 2 < n_items) {
+            compute_item(it + 2, s2);
+            if (it + 5 < n_items) load_item(it + 5, s2);
         }
     }
 }
@@ -255,9 +304,22 @@ rcu_status launch_q4k(rcu_device* dev, const void* w, const void* x, const void*
     const long long max_ctas = (long long)dev->sm_count * 2;
     const long long groups = (N + kRowsQ4 - 1) / kRowsQ4;
     const int nchunks = ((K >> 8) + 3) >> 2;
-    // enough warps in flight when N is small: split a row group's chunk steps over 2-8 warps
+    // enough warps in flight when N is small: split a row group's steps over 2-8 warps; with only a few
+    // groups per team the team that gets one more sets the kernel's time, so when that imbalance exceeds
+    // 6 % take the split that minimises it
     int ksplit = 1;
     while (ksplit < 8 && groups * ksplit * 2 <= max_ctas * kWarpsQ4 && nchunks >= ksplit * 2) ksplit *= 2;
+    auto imbalance = [&](int ks) {
+        const long long teams = max_ctas * (kWarpsQ4 / ks);
+        const double avg = (double)groups / (double)teams;
+        return avg <= 0.0 ? 1.0 : (double)((groups + teams - 1) / teams) / avg;
+    };
+    if (groups * ksplit > max_ctas * kWarpsQ4 / 2 && imbalance(ksplit) > 1.06) {
+        int best = ksplit;
+        for (int ks = ksplit * 2; ks <= 8 && nchunks >= ks * 2; ks *= 2)
+            if (imbalance(ks) < imbalance(best) - 0.01) best = ks;
+        ksplit = best;
+    }
     const long long ctas_needed = (groups * ksplit + kWarpsQ4 - 1) / kWarpsQ4;
     const int grid = (int)std::max<long long>(1, std::min(ctas_needed, max_ctas));
 #define RCU_Q4K_CASE(KS)                                                                                                   \
@@ -286,6 +348,8 @@ rcu_status rcu_gemv_q4k_dispatch(rcu_device* dev, int lhs_dt, const void* w, int
                                  uint64_t N, uint64_t K) {
     if (K % 256 != 0) return rcu_fail(dev, RCU_ERR_INVALID_ARG, "gemv: Q4_K rows must hold whole 256-element blocks (K=%llu)", (unsigned long long)K);
     if (N > 0x7fffffffull || K > 0x7fffffffull) return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "gemv: dimension exceeds 2^31");
+    if ((reinterpret_cast<uintptr_t>(w) & 31) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return rcu_fail(dev, RCU_ERR_INVALID_ARG, "gemv: Q4_K weights must be 32-byte aligned and the vector 16-byte aligned");
     DevGuard g(dev->ordinal);
     if (lhs_dt == RCU_Q4_KF && act_dt == RCU_F32) return launch_q4k<float, float>(dev, w, x, bias, y, (int)N, (int)K);
     if (lhs_dt == RCU_Q4_KH && act_dt == RCU_F16) return launch_q4k<__half, __half>(dev, w, x, bias, y, (int)N, (int)K);
