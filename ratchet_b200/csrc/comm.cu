@@ -120,8 +120,8 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
     gemvq8::PlainPrologue<__half> pro{(const __half*)x->data};
     const bool pipe = n_local * K < ((uint64_t)128 << 20);
     rcu_status st = w_shard->dt == RCU_Q8_0H
-                        ? gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe)
-                        : gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe);
+                        ? gemvq8::launch<__half, __half, 2>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe)
+                        : gemvq8::launch<float, __half, 2>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe);
     if (st != RCU_OK) return st;
     *y_full = c->local.slot(slot);
     return RCU_OK;

@@ -121,11 +121,13 @@ GemvPlan plan_gemv(const rcu_device* dev, int N, int K, int rows_per_warp, int c
 }
 
 // Inner-product variant for f16 activations: 0 = packed f16 with the mixed-precision fma,
-// 1 = widen to f32 once per chunk.  RCU_GEMV_MODE selects it at run time (tuning aid).
+// 1 = widen to f32 once per chunk, 2 (default) = dp4a on 16-bit fixed-point planes in the plain kernel
+// (measured 6.5-6.7 TB/s sustained on the 1.2 GB shape against 5.8-6.4 for mode 0, whose operand
+// conversions saturate the XU pipe).  RCU_GEMV_MODE selects it at run time (tuning aid).
 int q8_mode() {
     static int mode = [] {
         const char* e = std::getenv("RCU_GEMV_MODE");
-        return e ? std::atoi(e) : 0;
+        return e ? std::atoi(e) : 2;
     }();
     return mode;
 }
@@ -152,6 +154,9 @@ rcu_status launch_q8(rcu_device* dev, const int8_t* qs, const void* scales, cons
     // short streams (tens of MB) gain from the pre-loaded, double-buffered variant; long ones from occupancy
     const bool pipe = (size_t)N * K < (size_t)128 << 20;
     if (q8_mode() == 1) return gemvq8::launch<ScaleT, ActT, 1>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
+    if constexpr (sizeof(ActT) == 2) {
+        if (q8_mode() == 2) return gemvq8::launch<ScaleT, ActT, 2>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
+    }
     return gemvq8::launch<ScaleT, ActT, 0>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
 }
 

@@ -133,6 +133,79 @@ template <class ActT> struct Dot16<ActT, 1> {
     }
 };
 template <> struct Dot16<float, 0> : Dot16<float, 1> {};
+
+// MODE 2 (f16 activations): the staged vector is re-expressed once per CTA as 16-bit fixed point,
+// x = sx * X with sx = max|x| / 32767, kept as a signed high-byte plane and an unsigned low-byte plane
+// (2^-15 of the vector's scale, below f16's own 2^-11 per element).  Sixteen int8 codes then meet the
+// planes in eight dp4a and one int -> float conversion, against sixteen mixed-precision fma with their
+// operand conversions in MODE 0; the caller multiplies the finished sums by sx.
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {   // signed bytes of a x unsigned bytes of b
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+template <> struct Dot16<__half, 2> {
+    uint4 h, l;
+    __device__ __forceinline__ void load(const unsigned char* planes, int K, int k) {
+        h = *reinterpret_cast<const uint4*>(planes + k);
+        l = *reinterpret_cast<const uint4*>(planes + K + k);
+    }
+    __device__ __forceinline__ float dot(const uint4& w) const {
+        int dh = dp4a_ss(w.x, h.x, 0), dl = dp4a_su(w.x, l.x, 0);
+        dh = dp4a_ss(w.y, h.y, dh); dl = dp4a_su(w.y, l.y, dl);
+        dh = dp4a_ss(w.z, h.z, dh); dl = dp4a_su(w.z, l.z, dl);
+        dh = dp4a_ss(w.w, h.w, dh); dl = dp4a_su(w.w, l.w, dl);
+        return (float)(dh * 256 + dl);
+    }
+};
+
+// Build the two byte planes of MODE 2 from the staged f16 vector (all kThreads threads; K % 16 == 0).
+// Returns sx.  `scratch` is kWarps floats of shared memory; ends with a CTA barrier.
+__device__ __forceinline__ float stage_fixed_planes(const __half* xs, unsigned char* planes, int K, float* scratch) {
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < K / 8; i += kThreads) {
+        const uint4 u = reinterpret_cast<const uint4*>(xs)[i];
+        const uint32_t hw[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    __syncthreads();                                  // scratch may still be read by the prologue's reduction
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = scratch[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) amax = fmaxf(amax, scratch[w]);
+    const float inv = amax > 0.f ? 32767.f / amax : 0.f;
+    for (int i = threadIdx.x; i < K / 8; i += kThreads) {
+        const uint4 u = reinterpret_cast<const uint4*>(xs)[i];
+        const uint32_t hw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t hi[2] = {0, 0}, lo[2] = {0, 0};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
+            const int X0 = __float2int_rn(f.x * inv), X1 = __float2int_rn(f.y * inv);
+            const int j = 2 * e;
+            hi[j >> 2] |= (uint32_t)((X0 >> 8) & 0xFF) << (8 * (j & 3));
+            lo[j >> 2] |= (uint32_t)(X0 & 0xFF) << (8 * (j & 3));
+            hi[j >> 2] |= (uint32_t)((X1 >> 8) & 0xFF) << (8 * ((j + 1) & 3));
+            lo[j >> 2] |= (uint32_t)(X1 & 0xFF) << (8 * ((j + 1) & 3));
+        }
+        reinterpret_cast<uint2*>(planes)[i] = make_uint2(hi[0], hi[1]);
+        reinterpret_cast<uint2*>(planes + K)[i] = make_uint2(lo[0], lo[1]);
+    }
+    __syncthreads();
+    return amax / 32767.f;
+}
 template <class ScaleT> __device__ __forceinline__ float ld_scale(const ScaleT* p);
 template <> __device__ __forceinline__ float ld_scale<float>(const float* p) { return __ldg(p); }
 template <> __device__ __forceinline__ float ld_scale<__half>(const __half* p) {
@@ -479,6 +552,10 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
     pdl_wait();
     pro.stage(xs, K, red);
     __syncthreads();
+    // MODE 2: fixed-point byte planes of x behind the reduction scratch (the launcher sizes shared memory for them)
+    unsigned char* planes = smem_raw + (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float);
+    float sx = 1.f;
+    if constexpr (MODE == 2) sx = stage_fixed_planes(reinterpret_cast<const __half*>(xs), planes, K, red);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -531,13 +608,14 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
                 if (!live[u]) continue;
                 const int k = ((c0 + u * KSPLIT) << 9) + kl;
                 Dot16<ActT, MODE> d16;
-                d16.load(xs, k);
+                if constexpr (MODE == 2) d16.load(planes, K, k);
+                else d16.load(xs, k);
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(d16.dot(w[u][r]), sc[u][r], acc[r]);
             }
         }
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
+        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]) * sx;
 
         if (KSPLIT > 1) {
             if (lane == 0) {
@@ -638,7 +716,7 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
         for (int u = 0; u < UNROLL; ++u) {
             const int k = ((c0 + u * KSPLIT) << 9) + kl;
             if (k < K) {
-                Dot16<ActT, MODE> d16;
+                Dot16<ActT, MODE == 2 ? 0 : MODE> d16;   // the fixed-point planes exist in the plain kernel only
                 d16.load(xs, k);
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(d16.dot(s.w[u][r]), s.sc[u][r], acc[r]);
@@ -737,7 +815,7 @@ rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const P
     constexpr int UNIT = Epilogue::UNIT;
     const int n_units = N / UNIT;
     const Plan p = plan(dev, n_units, UNIT, K, ctas_per_sm);
-    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float);
+    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float) + (MODE == 2 && !pipelined ? 2 * (size_t)K : 0);
     if (smem > (size_t)dev->smem_optin) return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "gemv: K=%d does not fit the activation stage", K);
 #define RCU_GEMV_Q8_CASE(KS)                                                                                  \
     case KS: {                                                                                                \

@@ -116,17 +116,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
     atomicOr(status, RCU_DEVFLAG_TIMEOUT);
     return false;
 }
-// signed x signed and signed x unsigned 4-way byte dot products with 32-bit accumulate
-__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
+// dp4a_ss / dp4a_su (signed x signed, signed x unsigned byte dot products) come from gemv_q8.cuh
 // 2-D tile: global (tensor map, element coordinates x = innermost, y = row) -> shared, completion in
 // bytes on `bar`.  x * element size must be a multiple of 16 bytes (here x = kc * 256 u32 / kc * 32 scales).
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
