@@ -679,9 +679,11 @@ rcu_status gemv(rcu_device* dev, int weight_dt, const void* w, const Pro& pro, c
     }
     if (weight_dt == RCU_Q8_0H) {
         if (mode == 1) return gemvq8::launch<__half, __half, 1>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
+        if (mode == 2) return gemvq8::launch<__half, __half, 2>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
         return gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
     }
     if (mode == 1) return gemvq8::launch<float, __half, 1>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
+    if (mode == 2) return gemvq8::launch<float, __half, 2>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
     return gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
 }
 

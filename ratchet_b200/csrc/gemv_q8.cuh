@@ -17,6 +17,8 @@
 //     block scale per 16 elements, warp-shuffle reduction at the end;
 //   * small N: KSPLIT warps share a unit range and split K, combined through shared memory.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace gemvq8 {
@@ -205,6 +207,53 @@ __device__ __forceinline__ float stage_fixed_planes(const __half* xs, unsigned c
     }
     __syncthreads();
     return amax / 32767.f;
+}
+
+// Variant for the short kernels of a decode step: every 16 activations get a scale of their own (their
+// max / 32767), so building the planes needs no reduction over the CTA, only the barrier after it.
+struct Dot16Local {
+    uint4 h, l;
+    float s;
+    __device__ __forceinline__ void load(const unsigned char* planes, int K, int k) {
+        h = *reinterpret_cast<const uint4*>(planes + k);
+        l = *reinterpret_cast<const uint4*>(planes + K + k);
+        s = reinterpret_cast<const float*>(planes + 2 * (size_t)K)[k >> 4];
+    }
+    __device__ __forceinline__ float dot(const uint4& w) const {
+        int dh = dp4a_ss(w.x, h.x, 0), dl = dp4a_su(w.x, l.x, 0);
+        dh = dp4a_ss(w.y, h.y, dh); dl = dp4a_su(w.y, l.y, dl);
+        dh = dp4a_ss(w.z, h.z, dh); dl = dp4a_su(w.z, l.z, dl);
+        dh = dp4a_ss(w.w, h.w, dh); dl = dp4a_su(w.w, l.w, dl);
+        return (float)(dh * 256 + dl) * s;
+    }
+};
+
+// planes: [K signed high bytes][K unsigned low bytes][K / 16 f32 scales]; all kThreads threads; ends with a CTA barrier
+__device__ __forceinline__ void stage_fixed_planes_local(const __half* xs, unsigned char* planes, int K) {
+    for (int i = threadIdx.x; i < K / 16; i += kThreads) {
+        const uint4 u0 = reinterpret_cast<const uint4*>(xs)[2 * i], u1 = reinterpret_cast<const uint4*>(xs)[2 * i + 1];
+        const uint32_t hw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        float v[16];
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
+            v[2 * e] = f.x; v[2 * e + 1] = f.y;
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+        const float inv = amax > 0.f ? 32767.f / amax : 0.f;
+        uint32_t hi[4] = {0, 0, 0, 0}, lo[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const int X = __float2int_rn(v[e] * inv);
+            hi[e >> 2] |= (uint32_t)((X >> 8) & 0xFF) << (8 * (e & 3));
+            lo[e >> 2] |= (uint32_t)(X & 0xFF) << (8 * (e & 3));
+        }
+        reinterpret_cast<uint4*>(planes)[i] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        reinterpret_cast<uint4*>(planes + K)[i] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        reinterpret_cast<float*>(planes + 2 * (size_t)K)[i] = amax / 32767.f;
+    }
+    __syncthreads();
 }
 template <class ScaleT> __device__ __forceinline__ float ld_scale(const ScaleT* p);
 template <> __device__ __forceinline__ float ld_scale<float>(const float* p) { return __ldg(p); }
@@ -664,6 +713,8 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
     extern __shared__ __align__(16) unsigned char smem_raw[];
     ActT* xs = reinterpret_cast<ActT*>(smem_raw);
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)K * sizeof(ActT));  // [kWarps][ROWS]
+    // MODE 2: fixed-point byte planes of x (with 16-element scales) behind the reduction scratch
+    unsigned char* planes = smem_raw + (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -716,8 +767,9 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
         for (int u = 0; u < UNROLL; ++u) {
             const int k = ((c0 + u * KSPLIT) << 9) + kl;
             if (k < K) {
-                Dot16<ActT, MODE == 2 ? 0 : MODE> d16;   // the fixed-point planes exist in the plain kernel only
-                d16.load(xs, k);
+                typename std::conditional<MODE == 2, Dot16Local, Dot16<ActT, MODE == 2 ? 0 : MODE>>::type d16;
+                if constexpr (MODE == 2) d16.load(planes, K, k);
+                else d16.load(xs, k);
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) acc[r] = fmaf(d16.dot(s.w[u][r]), s.sc[u][r], acc[r]);
             }
@@ -762,6 +814,7 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
     pdl_wait();
     pro.stage(xs, K, red);
     __syncthreads();
+    if constexpr (MODE == 2) stage_fixed_planes_local(reinterpret_cast<const __half*>(xs), planes, K);
 
     for (int it = 0; it < n_items; it += 2) {
         compute_item(it, s0);
@@ -815,7 +868,7 @@ rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const P
     constexpr int UNIT = Epilogue::UNIT;
     const int n_units = N / UNIT;
     const Plan p = plan(dev, n_units, UNIT, K, ctas_per_sm);
-    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float) + (MODE == 2 && !pipelined ? 2 * (size_t)K : 0);
+    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float) + (MODE == 2 ? 2 * (size_t)K + (pipelined ? (size_t)K / 4 : 0) : 0);
     if (smem > (size_t)dev->smem_optin) return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "gemv: K=%d does not fit the activation stage", K);
 #define RCU_GEMV_Q8_CASE(KS)                                                                                  \
     case KS: {                                                                                                \
