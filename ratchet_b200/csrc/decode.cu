@@ -650,10 +650,12 @@ __device__ __forceinline__ void argmax_advance_body(const __half* logits, int n,
     if (threadIdx.x == 0) *d_pos += 1;
 }
 
+// Inner product of the step's GEMVs: 2 (default) = dp4a on fixed-point activation planes with 16-element
+// scales, 0 = packed f16 with the mixed-precision fma, 1 = f32 FFMA (RCU_GEMV_MODE, tuning aid).
 int q8_mode() {
     static int mode = [] {
         const char* e = std::getenv("RCU_GEMV_MODE");
-        return e ? std::atoi(e) : 0;
+        return e ? std::atoi(e) : 2;
     }();
     return mode;
 }
