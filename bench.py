@@ -108,36 +108,46 @@ class ClockSampler:
                 "samples": len(window)}
 
 
-def make_weights(N, K, seed):
-    """Synthetic Q8_0F weight buffer for W[N,K] ~ N(0, 0.02), built blockwise with numpy in the
-    layout of ratchet-core/src/quant.rs:19-49 (same arithmetic as the oracle's quantiser, which the
-    tests compare bit for bit; done here in numpy so the benchmark does not depend on the oracle)."""
-    from ratchet_b200 import capi
+UNIQUE_ROWS = 4096
+
+
+def unique_rows(K, seed):
+    """The 4096 distinct rows W ~ N(0, 0.02) every benchmark matrix is made of (the values do not affect the
+    timing; repeating them keeps host-side generation of a 1 Gi-element matrix to seconds and lets the
+    oracle check every output row against 4096 reference values)."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    total = capi.dtype_nbytes(capi.Q8_0F, N * K)
-    buf = np.zeros(total, np.uint8)
-    qs = buf[: N * K].view(np.int8).reshape(N, K)
-    d_off = capi.dtype_segments(capi.Q8_0F, N * K)[1]
-    ds = buf[d_off: d_off + (N * K // 32) * 4].view(np.float32).reshape(N, K // 32)
-    # 4096 distinct random rows, repeated down the matrix: the values do not affect the timing and
-    # this keeps host-side generation of the 1 Gi-element matrix to a few seconds.
-    uniq = min(N, 4096)
-    rows = max(1, (1 << 24) // K)
-    for r0 in range(0, uniq, rows):
-        r1 = min(uniq, r0 + rows)
-        w = (rng.standard_normal((r1 - r0, K), dtype=np.float32) * np.float32(0.02)).reshape(r1 - r0, K // 32, 32)
-        d = (np.abs(w).max(-1) / np.float32(127.0)).astype(np.float32)
-        with np.errstate(divide="ignore", invalid="ignore"):
-            v = w / d[..., None]
-        v = np.where(np.isfinite(v), v, 0)
-        q = np.where(v >= 0, np.floor(v + np.float32(0.5)), np.ceil(v - np.float32(0.5)))
-        qs[r0:r1] = q.astype(np.int8).reshape(r1 - r0, K)
-        ds[r0:r1] = d
-    for r0 in range(uniq, N, uniq):
-        r1 = min(N, r0 + uniq)
-        qs[r0:r1] = qs[: r1 - r0]
-        ds[r0:r1] = ds[: r1 - r0]
+    return rng.standard_normal((UNIQUE_ROWS, K), dtype=np.float32) * np.float32(0.02)
+
+
+def make_weights(N, K, seed):
+    """Synthetic Q8_0F weight buffer for W[N,K]: `unique_rows(K, seed)` quantised by the library's own
+    quantiser (rcu_quantize, ratchet-core/src/quant.rs:19-99) and repeated down the matrix."""
+    from ratchet_b200 import capi
+    uniq = min(N, UNIQUE_ROWS)
+    small = capi.quantize(unique_rows(K, seed)[:uniq])
+    if uniq == N:
+        return small
+    off_small = capi.dtype_segments(capi.Q8_0F, uniq * K)[1]
+    off = capi.dtype_segments(capi.Q8_0F, N * K)[1]
+    buf = np.zeros(capi.dtype_nbytes(capi.Q8_0F, N * K), np.uint8)
+    reps, rest = divmod(N, uniq)
+    buf[: reps * uniq * K].reshape(reps, uniq * K)[:] = small[: uniq * K]
+    buf[off: off + reps * uniq * K // 8].reshape(reps, uniq * K // 8)[:] = small[off_small: off_small + uniq * K // 8]
+    if rest:
+        buf[reps * uniq * K: N * K] = small[: rest * K]
+        buf[off + reps * uniq * K // 8: off + N * K // 8] = small[off_small: off_small + rest * K // 8]
     return buf
+
+
+def parity_report(got, ref, rtol, atol):
+    """Max absolute / relative error and the count outside the reference's all_close criterion
+    |a - b| <= atol + rtol * |b| (ratchet-core/src/tensor.rs:1039-1043)."""
+    got = np.asarray(got, np.float64).reshape(-1)
+    ref = np.asarray(ref, np.float64).reshape(-1)
+    err = np.abs(got - ref)
+    scale = float(np.sqrt(np.mean(ref * ref)))
+    return {"max_abs": float(err.max()), "max_rel_to_rms": float(err.max() / (scale + 1e-30)),
+            "outside_allclose": int((err > atol + rtol * np.abs(ref)).sum()), "rtol": rtol, "atol": atol, "checked": int(ref.size)}
 
 
 def run_reference(args):
@@ -147,6 +157,8 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import oracle as orc
+    # all host cores, whatever the launcher exported (torchrun sets OMP_NUM_THREADS=1 for its workers)
+    orc.set_num_threads(os.cpu_count() or 1)
     K, N = K_HEAD, N_HEAD
     rows = 2048   # 32 MiB of int8 weights per step: a bounded sample of the 65536 rows
     buf_full_rows = rows
@@ -175,6 +187,7 @@ def run_reference(args):
 
 def cpu_baseline_sample(K, N):
     from oracle import oracle as orc
+    orc.set_num_threads(os.cpu_count() or 1)
     rows = 2048
     rng = np.random.Generator(np.random.PCG64(1))
     wq = orc.quantize_q8(rng.standard_normal((rows, K), dtype=np.float32) * np.float32(0.02))
@@ -474,6 +487,24 @@ def phi3_decode_bench(dev, torch, stream, steps, warmup, rank=0, world=1, dist=N
     for _ in range(warmup):
         step()
     barrier()
+    job_profile = None
+    if world == 1 and os.environ.get("RCU_BENCH_JOB_PROFILE"):
+        # per-job time table of the data-flow kernel (device time stamps of its first CTA), median of five steps
+        runs = []
+        for _ in range(5):
+            dec.position = c["kv_prior"]
+            raw = dec.profile_step(tok_dev.data_ptr()).astype(np.int64)
+            cyc = raw[-24:].reshape(6, 4)
+            runs.append(np.diff(raw[:-24]))
+        med = np.median(np.stack(runs), 0)           # [stage, work] per job
+        names = ["qkv", "attention", "o", "gate_up", "down"]
+        per_layer = med[: 10 * c["n_layers"]].reshape(c["n_layers"], 5, 2)
+        job_profile = {"us_per_layer_median": {n: {"input_wait_and_stage": float(np.median(per_layer[:, i, 0])) / 1e3,
+                                                   "items_and_tail": float(np.median(per_layer[:, i, 1])) / 1e3} for i, n in enumerate(names)},
+                       "layer_us_median": float(np.median(per_layer.sum((1, 2)))) / 1e3,
+                       "lm_head_us": float(med[-2:].sum()) / 1e3, "kernel_us": float(med.sum()) / 1e3,
+                       "first_warp_cycles_per_step": {k: dict(zip(["slot_wait", "multiply", "store", "request"], [int(v) for v in cyc[i]]))
+                                                      for i, k in enumerate(["qkv", "attention", "o", "gate_up", "down", "lm_head"])}}
     l0 = dev.launches
     ms = _time_loop(torch, stream, step, steps)
     launches = (dev.launches - l0) // steps
@@ -499,6 +530,8 @@ def phi3_decode_bench(dev, torch, stream, steps, warmup, rank=0, world=1, dist=N
            "roofline_frac": b / ms / 1e6 / (peak * world), "roofline_tokens_per_s": world * peak * 1e9 / b, "peak_kind": f"of {kind}",
            "parallelism": "single GPU" if world == 1 else f"every Linear row-sharded x{world}, attention by heads, 4 fused all-gathers per layer (peer stores over NVLink)",
            "config": {"model": "phi-3-mini shape, random Q8_0H weights", **c, "steps": steps}}
+    if job_profile is not None:
+        res["job_profile"] = job_profile
     dec.close()
     if comm is not None:
         dist.barrier()
@@ -527,7 +560,7 @@ def run_ours(args):
 
     K, N = K_HEAD, (args.rows or N_HEAD)
     n_local = N // world
-    wq = make_weights(n_local, K, seed=1000 + rank)
+    wq = make_weights(n_local, K, seed=1000)      # every shard is the same 4096 rows repeated (n_local is a multiple of 4096 up to 8 GPUs)
     dw = dev.from_quantized(wq, capi.Q8_0F, (n_local, K))
     del wq
     rng = np.random.Generator(np.random.PCG64(7))
@@ -600,6 +633,22 @@ def run_ours(args):
     e2e_s = (time.perf_counter() - t0) / args.steps
     clocks = sampler.stop(mark0, max(mark1, mark0 + 1)) if rank == 0 else None
 
+    # What was timed is checked, outside the timed region: one more step, the gathered output of all ranks
+    # against the oracle on the 4096 distinct rows (every row of every shard repeats one of them).
+    parity = None
+    out = step()
+    dev.sync()
+    y_all = np.empty(N, np.float16)
+    dev.d2h(y_all, by.ptr if out is None else out.ptr, N * 2)
+    if rank == 0:
+        from oracle import oracle as orc
+        uniq = min(n_local, UNIQUE_ROWS)
+        ref = orc.gemv_q8(orc.quantize_q8(unique_rows(K, 1000)[:uniq]), uniq, K, False, x_host_np.reshape(-1)).astype(np.float32)
+        ref_all = np.tile(ref, N // uniq + 1)[:N] if n_local % uniq == 0 else None
+        if ref_all is not None:
+            parity = parity_report(y_all.astype(np.float32), ref_all, rtol=1e-2, atol=1e-2 * float(np.sqrt(np.mean(ref * ref))))
+            parity["against"] = "CPU oracle (dequantise + f32 matmul), every output row of every rank"
+
     t = torch.tensor([ms, kernel_ms, e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -622,6 +671,7 @@ def run_ours(args):
             "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": N * 2,
                     "note": "weights stay resident (loaded once, as ratchet loads a model); activation H2D and result D2H each step"},
             "gpu_launches": int(launches),
+            "parity": parity,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "gemv_q8_kernel",

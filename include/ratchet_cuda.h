@@ -86,6 +86,19 @@ const char* rcu_last_error(rcu_device* dev);
 uint64_t rcu_launch_count(rcu_device* dev);
 int rcu_sm_count(rcu_device* dev);
 
+/* Debug switches of a device (also read from the environment when the device is created: RCU_NO_REUSE=1,
+ * RCU_PROFILE=1).  RCU_DEBUG_NO_REUSE: the lazy resolver gives every tensor a buffer of its own and runs nothing
+ * in place (the reference's RATCHET_DEBUG, gpu/buffer_allocator/allocator.rs:121).  RCU_DEBUG_PROFILE: the lazy
+ * resolver brackets every node with an event pair and blocks at the end of each resolve, filling a per-op table
+ * (the reference's `gpu-profiling` feature, gpu/profiler.rs:95-237, executable.rs:140-179). */
+#define RCU_DEBUG_NO_REUSE 1u
+#define RCU_DEBUG_PROFILE 2u
+rcu_status rcu_set_debug(rcu_device* dev, uint32_t flags);
+/* The per-op table as text — kernel key (op and operand dtype), count, total microseconds, share, GB/s over the
+ * operands' bytes — sorted by time.  Returns the bytes needed (with the terminator); writes at most `capacity`.
+ * reset != 0 clears the table. */
+uint64_t rcu_profile_report(rcu_device* dev, char* buf, uint64_t capacity, int reset);
+
 /* ------------------------------------------------------------------ storage (storage/gpu_buffer.rs) */
 /* BufferAllocator / BufferPool: pooled device memory (gpu/pools/buffer_pool.rs:80-94 rounds sizes
  * up to 4 B with a 16 B minimum; this pool rounds to 256 B size classes and caches freed blocks). */
@@ -96,12 +109,20 @@ rcu_status rcu_pool_trim(rcu_device* dev);
 /* bytes currently handed out / bytes held by the pool (allocator.rs:330-337 logs the same) */
 void rcu_pool_stats(rcu_device* dev, uint64_t* in_use, uint64_t* reserved);
 /* GPUBuffer::from_bytes (storage/gpu_buffer.rs:49-60) and to_cpu (200-218). d2h blocks. */
+/* h2d from pageable memory returns when the source has been read; from pinned memory it is fully
+ * asynchronous: the source must stay untouched until the next rcu_sync / rcu_d2h on this device. */
 rcu_status rcu_h2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
 rcu_status rcu_d2h(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
 rcu_status rcu_d2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
 rcu_status rcu_memset(rcu_device* dev, void* dst, int value, uint64_t nbytes);
-/* device.poll(Wait) (tensor.rs:856) */
+/* device.poll(Wait) (tensor.rs:856).  Also reports what kernels flagged since the last check:
+ * RCU_ERR_BOUNDS (an index outside its tensor) or RCU_ERR_TIMEOUT (a bounded device-side wait gave up). */
 rcu_status rcu_sync(rcu_device* dev);
+/* Every device-side wait (on a peer's data, on another CTA, on an asynchronous copy) gives up after this
+ * long, raises the time-out flag and lets its kernel run to the end, so the context stays usable; default
+ * two seconds.  The reference has no counterpart (its only wait is device.poll).  Applies to kernels
+ * launched after the call. */
+rcu_status rcu_set_wait_limit_ns(rcu_device* dev, uint64_t nanoseconds);
 
 /* ------------------------------------------------------------------ layouts (dtype/blocks.rs) */
 /* DType::segments total: bytes of the single buffer that holds `numel` elements of `dt`. */
@@ -115,6 +136,14 @@ int32_t rcu_activation_dtype(int32_t dt);
 /* dequantize (quant.rs:132-164) on the device: bit-exact with the CPU routine. src is Q8_0F/H or
  * Q4_KF/H, dst is F32 (…F) or F16 (…H) of the same shape. */
 rcu_status rcu_dequantize(rcu_device* dev, const rcu_tensor* src, rcu_tensor* dst);
+/* quantize (quant.rs:19-99) on the host: `src` holds `numel` f32 (dt = RCU_Q8_0F) or f16 (dt = RCU_Q8_0H)
+ * values, `host_out` receives the ratchet buffer (rcu_dtype_nbytes(dt, numel) bytes, padding zeroed).  Bit for
+ * bit the reference's output, including its corner cases (all-zero blocks, NaN, Rust's saturating casts).
+ * numel must be a multiple of 32.  The Q4_K arms of the reference emit an absmax layout that nothing
+ * consumes: RCU_ERR_UNSUPPORTED (Q4_K buffers come from rcu_gguf_transcode).  Touches no device. */
+rcu_status rcu_quantize(int32_t dt, const void* src, uint64_t numel, void* host_out, uint64_t out_bytes);
+/* The same on the device: src F32 -> dst Q8_0F, src F16 -> dst Q8_0H, same shape; same bits as rcu_quantize. */
+rcu_status rcu_quantize_device(rcu_device* dev, const rcu_tensor* src, rcu_tensor* dst);
 
 /* Matmul (ops/matmul/mod.rs:381-545; Tensor::gemm tensor.rs:409-419).  dst dtype = rhs dtype.
  * Allowed (lhs, rhs) pairs: (F32,F32) (F16,F16) (Q8_0F,F32) (Q8_0H,F16) (Q4_KF,F32) (Q4_KH,F16)
@@ -182,7 +211,8 @@ rcu_status rcu_lazy_from_host(rcu_device* dev, int32_t dt, uint32_t rank, const 
                               uint64_t nbytes, rcu_lazy** out);
 /* Tensor::zeros */
 rcu_status rcu_lazy_zeros(rcu_device* dev, int32_t dt, uint32_t rank, const uint64_t* shape, rcu_lazy** out);
-/* A resolved leaf over device memory the caller owns (never freed by the library). */
+/* A resolved leaf over device memory the caller owns (never freed by the library).  `dev` may be NULL for a
+ * graph that is only built and inspected (rcu_lazy_execution_order) and never resolved. */
 rcu_status rcu_lazy_wrap(rcu_device* dev, const rcu_tensor* t, rcu_lazy** out);
 void rcu_lazy_retain(rcu_lazy* t);
 void rcu_lazy_release(rcu_lazy* t);
@@ -208,6 +238,11 @@ rcu_status rcu_lazy_index_select(rcu_lazy* src, rcu_lazy* ids, uint32_t dim, rcu
 rcu_status rcu_lazy_cache(rcu_lazy* cache, rcu_lazy* src, uint32_t dim, uint32_t offset, rcu_lazy** out);
 rcu_status rcu_lazy_index_write(rcu_lazy* dst, rcu_lazy* src, const uint64_t* start, rcu_lazy** out);
 
+/* Tensor::id (tensor.rs:100-104): process-wide unique, increasing with creation. */
+uint64_t rcu_lazy_id(const rcu_lazy* t);
+/* Tensor::execution_order (tensor.rs:696-740): ids of every node `t` depends on, `t` last, in the order resolve
+ * runs them.  *n_nodes receives the count; at most `capacity` ids are written.  Touches no device. */
+rcu_status rcu_lazy_execution_order(rcu_lazy* t, uint64_t* ids, uint32_t capacity, uint32_t* n_nodes);
 /* Tensor::resolve: run every unresolved node `t` depends on.  Asynchronous on the device stream. */
 rcu_status rcu_lazy_resolve(rcu_lazy* t);
 /* Tensor::to(Device::CPU): resolve if needed, copy to host, block. */
@@ -270,6 +305,16 @@ uint32_t rcu_decoder_position(const rcu_decoder* dec);
 rcu_status rcu_decoder_step(rcu_decoder* dec, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev);
 /* Kernels per step of the captured graph (profiling aid). */
 uint32_t rcu_decoder_kernels_per_step(const rcu_decoder* dec);
+/* Profiling aid in the spirit of the reference's per-op timestamps (gpu/profiler.rs:95-237): runs one step
+ * like rcu_decoder_step (no arg-max), outside the CUDA graph, and returns the device clock (nanoseconds) at
+ * which the first CTA of the data-flow kernel began each of its jobs and had that job's input vector staged
+ * (for attention: had its own tiles folded) — per layer: qkv, attention, o, gate/up, down; then lm_head — plus
+ * one final stamp at its end: 2 n_jobs + 1 values; then, for each of the six job kinds (qkv, attention, o,
+ * gate/up, down, lm_head), four sums of SM clock cycles spent by the grid's first warp waiting for a ring slot,
+ * multiplying, storing results and requesting the next items: 24 more values.  Blocks until the step is done.
+ * RCU_ERR_INVALID_ARG if the decoder runs kernel by kernel (shapes the data-flow kernel does not take). */
+rcu_status rcu_decoder_profile_step(rcu_decoder* dec, const int32_t* token_dev, void* logits_dev, uint64_t* stamps_ns,
+                                    uint32_t capacity, uint32_t* n_stamps);
 
 /* Decode attention for one layer, standalone (the kernel rcu_decoder_step uses): RoPE on q and k
  * (ops/rope.rs), append k/v at `position` (ops/cache.rs), softmax(q.K^T * scale).V over

@@ -31,6 +31,7 @@ BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3}
 UNARY_OPS = {"gelu": 0, "tanh": 1, "exp": 2, "log": 3, "sin": 4, "cos": 5, "abs": 6, "sqrt": 7, "relu": 8, "floor": 9,
              "ceil": 10, "neg": 11, "silu": 12, "sigmoid": 13}
 LAYER_NORM, RMS_NORM, GROUP_NORM = 0, 1, 2
+DEBUG_NO_REUSE, DEBUG_PROFILE = 1, 2
 REDUCE_SUM, REDUCE_MAX, REDUCE_MEAN = 0, 1, 2
 
 
@@ -80,6 +81,8 @@ SIGNATURES = {
     "rcu_last_error": (C.c_char_p, [_DEV]),
     "rcu_launch_count": (C.c_uint64, [_DEV]),
     "rcu_sm_count": (C.c_int, [_DEV]),
+    "rcu_set_debug": (C.c_int, [_DEV, C.c_uint32]),
+    "rcu_profile_report": (C.c_uint64, [_DEV, C.c_char_p, C.c_uint64, C.c_int]),
     "rcu_alloc": (C.c_int, [_DEV, C.c_uint64, C.POINTER(C.c_void_p)]),
     "rcu_free": (C.c_int, [_DEV, C.c_void_p]),
     "rcu_pool_trim": (C.c_int, [_DEV]),
@@ -89,10 +92,13 @@ SIGNATURES = {
     "rcu_d2d": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
     "rcu_memset": (C.c_int, [_DEV, C.c_void_p, C.c_int, C.c_uint64]),
     "rcu_sync": (C.c_int, [_DEV]),
+    "rcu_set_wait_limit_ns": (C.c_int, [_DEV, C.c_uint64]),
     "rcu_dtype_nbytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
     "rcu_dtype_segments": (C.c_int, [C.c_int32, C.c_uint64, _u64p]),
     "rcu_activation_dtype": (C.c_int32, [C.c_int32]),
     "rcu_dequantize": (C.c_int, [_DEV, _T, _T]),
+    "rcu_quantize": (C.c_int, [C.c_int32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "rcu_quantize_device": (C.c_int, [_DEV, _T, _T]),
     "rcu_matmul": (C.c_int, [_DEV, _T, _T, _T, C.c_int, C.c_int, C.c_int, _T]),
     "rcu_matmul_dst_shape": (C.c_int, [_T, _T, C.c_int, C.c_int, C.c_int, _T]),
     "rcu_binary": (C.c_int, [_DEV, C.c_int, _T, _T, _T]),
@@ -134,6 +140,8 @@ SIGNATURES = {
     "rcu_lazy_index_select": (C.c_int, [_LZ, _LZ, C.c_uint32, C.POINTER(_LZ)]),
     "rcu_lazy_cache": (C.c_int, [_LZ, _LZ, C.c_uint32, C.c_uint32, C.POINTER(_LZ)]),
     "rcu_lazy_index_write": (C.c_int, [_LZ, _LZ, _u64p, C.POINTER(_LZ)]),
+    "rcu_lazy_id": (C.c_uint64, [_LZ]),
+    "rcu_lazy_execution_order": (C.c_int, [_LZ, _u64p, C.c_uint32, _u32p]),
     "rcu_lazy_resolve": (C.c_int, [_LZ]),
     "rcu_lazy_to_host": (C.c_int, [_LZ, C.c_void_p, C.c_uint64]),
     "rcu_last_resolve_stats": (None, [_DEV, C.POINTER(rcu_resolve_stats)]),
@@ -160,6 +168,7 @@ SIGNATURES = {
     "rcu_decoder_position": (C.c_uint32, [C.c_void_p]),
     "rcu_decoder_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "rcu_decoder_kernels_per_step": (C.c_uint32, [C.c_void_p]),
+    "rcu_decoder_profile_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, _u64p, C.c_uint32, _u32p]),
     "rcu_attn_decode_static": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                          C.c_uint32, C.c_float, C.c_uint32, C.c_void_p]),
     "rcu_comm_create": (C.c_int, [_DEV, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
@@ -200,6 +209,20 @@ def dtype_segments(dt: int, numel: int):
     off = (C.c_uint64 * 4)()
     n = lib().rcu_dtype_segments(dt, numel, off)
     return [off[i] for i in range(n)]
+
+
+def quantize(x: np.ndarray) -> np.ndarray:
+    """``quantize`` of ratchet-core/src/quant.rs:51-99 on the host: f32 input -> Q8_0F buffer, f16 input ->
+    Q8_0H buffer (a uint8 array in ratchet's segment layout)."""
+    x = np.ascontiguousarray(x)
+    if x.dtype not in (np.float32, np.float16):
+        raise RatchetCudaError(ERR_INVALID_ARG, f"quantize: {x.dtype} input (f32 or f16 expected)")
+    dt = Q8_0H if x.dtype == np.float16 else Q8_0F
+    out = np.empty(dtype_nbytes(dt, x.size), np.uint8)
+    st = lib().rcu_quantize(dt, x.ctypes.data_as(C.c_void_p), x.size, out.ctypes.data_as(C.c_void_p), out.size)
+    if st != OK:
+        raise RatchetCudaError(st, f"rcu_quantize({DTYPE_NAMES[dt]}, numel={x.size})")
+    return out
 
 
 def activation_dtype(dt: int) -> int:

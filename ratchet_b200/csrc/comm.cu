@@ -1,6 +1,6 @@
-// Row-sharded Linear across the GPUs of one node: peer-mapped output buffers and a GEMV whose last
-// CTA pushes its output slice to every peer (gemvq8::PushEpilogueH), so the all-gather that follows
-// a column-parallel Linear costs no extra collective launch.
+// Row-sharded Linear across the GPUs of one node: peer-mapped output buffers and a GEMV whose warps
+// push their finished rows to every peer as they go (gemvq8::GatherEpilogueH), so the all-gather that
+// follows a column-parallel Linear costs no extra collective launch.
 //
 // The reference has no multi-device path (gpu/device.rs:15-16 pins the ordinal to 0); this is the
 // sharding its Linear (ratchet-nn/src/linear.rs:17-24) admits: the rows of W[N,K] are independent,
@@ -8,13 +8,14 @@
 // buffer and the only exchange is the gather of the output slices.
 //
 // One process per GPU.  Each rank allocates one "window" (comm.cuh): full-size output slots (this
-// entry point alternates between the first two by step parity) followed by a flag array of `world`
-// words per slot and the ticket words.  Windows are exported as CUDA IPC handles, exchanged by the
+// entry point rotates through the first three) followed by an array of `world` arrival counters per
+// slot and the ticket / use-count words.  Windows are exported as CUDA IPC handles, exchanged by the
 // host framework, and opened by every peer.  Data moves with plain peer stores issued by the producing
 // GPU into the consumer's own HBM (all later reads are local); completion is a system-scope release
-// store of the step number into the consumer's flag word, which the consumer acquires with a bounded
-// spin.  No TMA, no multicast.
+// increment of the consumer's arrival counter, one per producing CTA, which the consumer acquires with a
+// bounded spin.  No TMA, no multicast.
 #include "comm.cuh"
+#include "ring.cuh"
 
 namespace {
 using rcu_window::Window;
@@ -96,32 +97,40 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
         RCU_REQUIRE(dev, p == c->rank || c->opened[p], "gemv_allgather: peer %d has not been imported", p);
     DevGuard g(dev->ordinal);
     RCU_REQUIRE(dev, !c->bound, "gemv_allgather: this window belongs to a sharded decoder");
-    const unsigned int seq = ++c->seq;
-    const int slot = (int)(seq & 1u);
-    gemvq8::PushEpilogueH epi;
+    // Three output slots in rotation: a result stays valid until the call after next, and a peer that is one
+    // call ahead writes a slot nobody reads any more.
+    const int slot = (int)(c->seq++ % 3u);
+    gemvq8::GatherEpilogueH epi;
     epi.bias = bias_shard ? (const __half*)bias_shard->data : nullptr;
     epi.y_local = reinterpret_cast<__half*>(c->local.slot(slot)) + (size_t)c->rank * n_local;
-    epi.slice_elems = (int)n_local;
-    epi.ticket = c->local.ticket(c->world);
+    epi.ticket = c->local.ticket(c->world, 0);
+    epi.uses = c->local.ticket(c->world, 1 + slot);
     epi.n_peers = 0;
     for (int p = 0; p < c->world; ++p) {
         if (p == c->rank) continue;
         epi.peer_dst[epi.n_peers] = reinterpret_cast<__half*>(c->peers[p].slot(slot)) + (size_t)c->rank * n_local;
-        epi.peer_flag[epi.n_peers] = c->peers[p].flags(slot, c->world) + c->rank;
+        epi.peer_count[epi.n_peers] = c->peers[p].flags(slot, c->world) + c->rank;
         epi.n_peers++;
     }
-    epi.seq = seq;
-    epi.my_flags = c->world > 1 ? c->local.flags(slot, c->world) : nullptr;
+    epi.my_counts = c->local.flags(slot, c->world);
     epi.world = c->world;
     epi.self = c->rank;
     epi.status = dev->d_status;
     const int8_t* qs = (const int8_t*)w_shard->data;
     const void* sc = (const char*)w_shard->data + align256(n_local * K);
-    gemvq8::PlainPrologue<__half> pro{(const __half*)x->data};
-    const bool pipe = n_local * K < ((uint64_t)128 << 20);
-    rcu_status st = w_shard->dt == RCU_Q8_0H
-                        ? gemvq8::launch<__half, __half, 2>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe)
-                        : gemvq8::launch<float, __half, 2>(dev, qs, sc, pro, epi, (int)n_local, (int)K, true, 3, pipe);
+    // Every rank must launch the same grid (a CTA counts once on every peer): the choice of kernel and its grid
+    // depend on the shard's shape and the device alone.
+    rcu_status st = RCU_ERR_UNSUPPORTED;
+    if (K >= 2048) {
+        ringq8::PlainPlanes<ringq8::VecSource> rpro{{(const __half*)x->data}};
+        st = w_shard->dt == RCU_Q8_0H ? ringq8::launch<__half>(dev, qs, sc, rpro, epi, (int)n_local, (int)K, false)
+                                      : ringq8::launch<float>(dev, qs, sc, rpro, epi, (int)n_local, (int)K, false);
+    }
+    if (st == RCU_ERR_UNSUPPORTED) {
+        gemvq8::PlainPrologue<__half> pro{(const __half*)x->data};
+        st = w_shard->dt == RCU_Q8_0H ? gemvq8::launch<__half, __half, 2>(dev, qs, sc, pro, epi, (int)n_local, (int)K, false, 3, true)
+                                      : gemvq8::launch<float, __half, 2>(dev, qs, sc, pro, epi, (int)n_local, (int)K, false, 3, true);
+    }
     if (st != RCU_OK) return st;
     *y_full = c->local.slot(slot);
     return RCU_OK;

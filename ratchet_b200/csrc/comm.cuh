@@ -1,16 +1,17 @@
 // Peer-mapped exchange windows shared by the sharded GEMV entry point and the sharded decoder.
 //
-// One process per GPU.  Each rank allocates one window: kSlots full-size slots followed by one flag
-// array of `world` words per slot and four counter words (tickets).  Windows are exported as CUDA IPC
-// handles, exchanged by the host framework, and opened by every peer.  Data moves with plain peer
-// stores issued by the producing GPU into the consumer's own HBM (all later reads are local);
-// completion is a system-scope release store of a sequence number into the consumer's flag word,
-// which the consumer acquires with a bounded spin.  No TMA, no multicast.
+// One process per GPU.  Each rank allocates one window: kSlots full-size slots followed by an array of
+// `world` arrival counters per slot and four more words (a ticket and the use counts of the GEMV's three
+// slots).  Windows are exported as CUDA IPC handles, exchanged by the host framework, and opened by every
+// peer.  Data moves with plain peer stores issued by the producing GPU into the consumer's own HBM (all
+// later reads are local).  The row-sharded GEMV signals completion with system-scope release increments
+// of the consumer's arrival counters; the sharded decoder's exchanges carry their sequence number inside
+// every word.  Either way the consumer's wait is a bounded spin.  No TMA, no multicast.
 #pragma once
 #include "gemv_q8.cuh"
 
 namespace rcu_window {
-constexpr int kSlots = 3;
+constexpr int kSlots = 6;       // x (two, alternating), qkv, head outputs, MLP activations, logits: one per vector of a decode layer
 
 struct Window {
     char* base = nullptr;

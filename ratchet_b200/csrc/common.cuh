@@ -37,9 +37,13 @@ struct rcu_device {
     uint64_t launches = 0;
     std::string last_error;
     rcu_pool pool;
-    int* d_status = nullptr;     // device-side status word: bounds / timeout flags raised by kernels
+    int* d_status = nullptr;     // device-side status block: [0] bounds / timeout flags raised by kernels, [2..3] wait limit in ns (u64)
+    uint64_t wait_limit_ns = 2000000000ull;
     int* h_status = nullptr;     // pinned host mirror
     rcu_resolve_stats last_resolve = {};   // counters of the last lazy-graph resolve (graph.cu)
+    uint32_t debug_flags = 0;    // RCU_DEBUG_* (rcu_set_debug; RCU_NO_REUSE / RCU_PROFILE in the environment at creation)
+    struct OpTime { uint64_t count = 0; double us = 0.0; uint64_t bytes = 0; };
+    std::map<std::string, OpTime> op_times;   // per-op timing table of the lazy resolver (RCU_DEBUG_PROFILE)
     void* comm = nullptr;        // communicator state, owned by comm.cu
     // per-device resources created lazily by individual ops; run at rcu_device_destroy
     std::vector<std::pair<void (*)(void*), void*>> cleanup;
@@ -117,6 +121,7 @@ inline int grid_for(uint64_t work_items, int per_block, int max_blocks) {
 
 // status-word bits raised by kernels
 enum { RCU_DEVFLAG_BOUNDS = 1, RCU_DEVFLAG_TIMEOUT = 2 };
+constexpr size_t kStatusBlockBytes = 16;
 
 // ------------------------------------------------------------------------------------------------
 // Device-side numeric helpers
@@ -144,6 +149,12 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// How long a device-side wait may last before it gives up, in nanoseconds (rcu_set_wait_limit_ns); kept in
+// the device's status block next to the flag word every waiting kernel already holds a pointer to.
+__device__ __forceinline__ unsigned long long rcu_wait_limit(const int* status) {
+    return *reinterpret_cast<const volatile unsigned long long*>(status + 2);
 }
 
 // streaming 16-byte load that does not allocate in L1 (weights are read exactly once)

@@ -20,8 +20,7 @@
 #include <cooperative_groups.h>
 
 #include "comm.cuh"
-#include "decode_persist.cuh"
-#include "gemv_q8_bulk.cuh"
+#include "decode_flow.cuh"
 
 namespace {
 
@@ -650,16 +649,6 @@ __device__ __forceinline__ void argmax_advance_body(const __half* logits, int n,
     if (threadIdx.x == 0) *d_pos += 1;
 }
 
-// Inner product of the step's GEMVs: 2 (default) = dp4a on fixed-point activation planes with 16-element
-// scales, 0 = packed f16 with the mixed-precision fma, 1 = f32 FFMA (RCU_GEMV_MODE, tuning aid).
-int q8_mode() {
-    static int mode = [] {
-        const char* e = std::getenv("RCU_GEMV_MODE");
-        return e ? std::atoi(e) : 2;
-    }();
-    return mode;
-}
-
 // Programmatic dependent launch between the kernels of a step (RCU_NO_PDL=1 turns it off).
 bool pdl_enabled() {
     static bool on = std::getenv("RCU_NO_PDL") == nullptr;
@@ -670,23 +659,9 @@ template <class Pro, class Epi>
 rcu_status gemv(rcu_device* dev, int weight_dt, const void* w, const Pro& pro, const Epi& epi, int N, int K) {
     const int8_t* qs = (const int8_t*)w;
     const void* sc = (const char*)w + align256((uint64_t)N * K);
-    const int mode = q8_mode();
     const bool ov = pdl_enabled();
-    static const int ctas = [] { const char* e = std::getenv("RCU_DECODE_CTAS"); const int n = e ? std::atoi(e) : 3; return n < 1 ? 1 : (n > 3 ? 3 : n); }();
-    // shared-memory ring fed by TMA tile copies: opt-in with RCU_GEMV_BULK=1 (the register kernel measures faster on cold weights)
-    static const bool bulk = std::getenv("RCU_GEMV_BULK") != nullptr;
-    if (bulk && gemvq8::bulk_eligible(qs, K, (size_t)dev->smem_optin, weight_dt == RCU_Q8_0H ? 2 : 4)) {
-        if (weight_dt == RCU_Q8_0H) return gemvq8::launch_bulk<__half>(dev, qs, sc, pro, epi, N, K, ov);
-        return gemvq8::launch_bulk<float>(dev, qs, sc, pro, epi, N, K, ov);
-    }
-    if (weight_dt == RCU_Q8_0H) {
-        if (mode == 1) return gemvq8::launch<__half, __half, 1>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
-        if (mode == 2) return gemvq8::launch<__half, __half, 2>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
-        return gemvq8::launch<__half, __half, 0>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
-    }
-    if (mode == 1) return gemvq8::launch<float, __half, 1>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
-    if (mode == 2) return gemvq8::launch<float, __half, 2>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
-    return gemvq8::launch<float, __half, 0>(dev, qs, sc, pro, epi, N, K, ov, ctas, true);
+    if (weight_dt == RCU_Q8_0H) return gemvq8::launch<__half, __half, 2>(dev, qs, sc, pro, epi, N, K, ov, 2, true);
+    return gemvq8::launch<float, __half, 2>(dev, qs, sc, pro, epi, N, K, ov, 2, true);
 }
 
 // per-device scratch for the standalone attention entry point
@@ -696,6 +671,7 @@ struct AttnScratch {
     float* rope_tab = nullptr;
     uint32_t* d_pos = nullptr;
     size_t partial_floats = 0;
+    int heads = 0;                 // entries of `counters`
 };
 
 void free_attn_scratch(void* p) {
@@ -707,8 +683,9 @@ void free_attn_scratch(void* p) {
     delete s;
 }
 
-rcu_status alloc_attn_scratch(rcu_device* dev, int H, int head_dim, int max_cache, AttnScratch* s) {
-    s->partial_floats = (size_t)H * attn_splits(max_cache) * (head_dim + 2);
+rcu_status alloc_attn_scratch(rcu_device* dev, int H, size_t partial_floats, AttnScratch* s) {
+    s->partial_floats = partial_floats;
+    s->heads = H;
     RCU_CUDA(dev, cudaMalloc(&s->partial, s->partial_floats * sizeof(float)));
     RCU_CUDA(dev, cudaMalloc(&s->counters, (size_t)H * sizeof(unsigned int)));
     RCU_CUDA(dev, cudaMalloc(&s->rope_tab, 256 * sizeof(float)));
@@ -734,12 +711,15 @@ struct rcu_decoder {
     // sharded across the GPUs of a node (null: single GPU).  cfg holds the whole model's sizes.
     rcu_comm* comm = nullptr;
     unsigned int* d_step = nullptr;       // steps taken, on the device: the exchanges' sequence numbers derive from it
-    // all layers as one persistent cooperative kernel (decode_persist.cuh); null when not in use
-    persist::LayerW* d_layers = nullptr;
-    unsigned int* d_bar = nullptr;
-    int persist_grid = 0;
-    size_t persist_smem = 0;
-    persist::Params pp;
+    // all layers and the lm_head as one persistent data-flow kernel (decode_flow.cuh); flow_grid == 0: not in use
+    flow::LayerPtrs* d_layer_ptrs = nullptr;
+    flow::Params fp;
+    int flow_grid = 0, flow_kmax = 0, flow_warps = 0;
+    size_t flow_smem = 0;
+    uint32_t* own_window = nullptr;       // single GPU: the exchange window lives here (no peers)
+    size_t slot_words = 0;
+    float* flow_partial = nullptr;
+    unsigned long long* d_prof = nullptr; // per-job time stamps of one step (rcu_decoder_profile)
     // captured step
     cudaGraphExec_t graph_exec = nullptr;
     const int32_t* cap_token = nullptr;
@@ -750,105 +730,249 @@ struct rcu_decoder {
 
 namespace {
 
-template <int HD>
-rcu_status launch_persistent_hd(rcu_decoder* d) {
+// Embedding row -> tagged words of the x exchange (the flow kernel's first input), this rank only.
+__global__ void publish_words_kernel(const __half* x, int n, gemvq8::LLPush push) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) push.put(i, x[i]);
+}
+
+template <int HD, class ScaleT, int NW>
+bool flow_fits_t(size_t smem) {
+    auto kern = flow::decode_flow_kernel<HD, ScaleT, NW>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, (NW + 1) * 32, smem) != cudaSuccess) return false;
+    return n >= 1;
+}
+
+// Instantiations of the data-flow kernel: head_dim 64 / 96 / 128, f16 or f32 block scales, 8 / 12 / 16 consumer warps.
+#define RCU_FLOW_DISPATCH(HD_, HALF_, NW_, CALL)                                                            \
+    do {                                                                                                    \
+        if ((NW_) == 8) { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 8, CALL); }                                      \
+        else if ((NW_) == 12) { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 12, CALL); }                               \
+        else { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 16, CALL); }                                                \
+    } while (0)
+#define RCU_FLOW_DISPATCH_HD(HD_, HALF_, NWC, CALL)                                                         \
+    do {                                                                                                    \
+        if ((HD_) == 64) { if (HALF_) { CALL(64, __half, NWC); } else { CALL(64, float, NWC); } }           \
+        else if ((HD_) == 96) { if (HALF_) { CALL(96, __half, NWC); } else { CALL(96, float, NWC); } }      \
+        else { if (HALF_) { CALL(128, __half, NWC); } else { CALL(128, float, NWC); } }                     \
+    } while (0)
+
+template <int HD> size_t flow_union_bytes(int kmax, int nw) {
+    return nw == 8 ? flow::union_bytes<HD, 8>(kmax) : nw == 12 ? flow::union_bytes<HD, 12>(kmax) : flow::union_bytes<HD, 16>(kmax);
+}
+
+// Exchange slots of the window (each slot_words 32-bit words): the residual stream alternates between two.
+enum { SLOT_X0 = 0, SLOT_X1 = 1, SLOT_Q = 2, SLOT_A = 3, SLOT_F = 4, SLOT_LOGITS = 5 };
+
+// Describes the decode step to the data-flow kernel if this model and device allow it: rows of whole
+// 256-element runs (the rings' alignment rule), every matrix with at least one item group per CTA, at least
+// eight warps per local head, cooperative launch.  Otherwise the decoder keeps the kernel-per-phase step.
+void setup_flow(rcu_decoder* d) {
     rcu_device* dev = d->dev;
-    RCU_CUDA(dev, cudaMemsetAsync(d->d_bar, 0, sizeof(unsigned int), dev->stream));
+    const rcu_decoder_config& c = d->cfg;
+    const int W = d->comm ? d->comm->world : 1, r = d->comm ? d->comm->rank : 0;
+    const int HD = (int)c.head_dim, L = (int)c.n_layers;
+    const int D = (int)c.d_model, Dl = D / W, ffn = (int)c.ffn, ffnl = ffn / W, Vl = (int)c.vocab / W;
+    const int H = (int)c.n_heads, Hl = H / W, Hkvl = (int)c.n_kv_heads / W;
+    const int qkv_nl = (Hl + 2 * Hkvl) * HD, A = H * HD;
+    const int ss = c.weight_dt == RCU_Q8_0H ? 2 : 4;
+    static const bool off = [] { const char* e = std::getenv("RCU_DECODE_FLOW"); return e && std::atoi(e) == 0; }();
+    if (off) return;
+    int coop = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal) != cudaSuccess || !coop) return;
+    const int grid = dev->sm_count;
+    // consumer warps per CTA and how far beyond the rings L2 is asked for rows (tuning aids; the defaults are the measured best)
+    static const int env_nw = [] { const char* e = std::getenv("RCU_FLOW_WARPS"); return e ? std::atoi(e) : 12; }();
+    static const int env_l2 = [] { const char* e = std::getenv("RCU_FLOW_L2_AHEAD"); return e ? std::atoi(e) : 0; }();
+    const int NW = env_nw == 8 || env_nw == 16 ? env_nw : 12;
+    const long long GW = (long long)grid * NW;
+    if (Hl < 1 || Hl > grid || (int)c.rope_dim > flow::kMaxRope || L > flow::kMaxLayersShared) return;
+    if (Dl % 4 || ffnl % 4 || Vl % 4 || (Hl * HD) % 4) return;          // consumers take four words per load
+    const size_t widest = (size_t)std::max(std::max(D, ffn), std::max((int)c.vocab, std::max(A, qkv_nl)));
+    const size_t slot_words = d->comm ? d->comm->local.slot_bytes / 4 : widest;
+    if (slot_words < widest) return;
+
+    auto off_of = [&](int slot, size_t elem) { return (uint32_t)((size_t)slot * slot_words + elem); };
+    flow::Params& p = d->fp;
+    p = flow::Params{};
+    bool ok = true;
+    int kmax = std::max(std::max(D, ffn), A), slot_bytes = 2 * flow::kTileP * HD * 2;
+    // shared memory left for the rings, and the item size that lets every warp hold two items
+    const size_t ub0 = HD == 64 ? flow_union_bytes<64>(kmax, NW) : HD == 96 ? flow_union_bytes<96>(kmax, NW) : flow_union_bytes<128>(kmax, NW);
+    const size_t fixed = flow::union_off(NW, L) + ub0;
+    if (fixed + (size_t)NW * 2 * slot_bytes > (size_t)dev->smem_optin) return;
+    const int slot_target = (int)(((size_t)dev->smem_optin - fixed) / ((size_t)NW * 2)) & ~127;
+    auto describe = [&](int kind, int n_units, int rows, int K, int unit, bool rms) {
+        flow::KindDesc& k = p.kd[kind];
+        ringq8::Job j{nullptr, nullptr, n_units, n_units, K, 1, K, 1, ss};
+        static const int env_slot = [] { const char* e = std::getenv("RCU_FLOW_SLOT"); return e ? std::atoi(e) : 13056; }();
+        if (!ringq8::plan_job(&j, unit, std::min(slot_target, env_slot))) { ok = false; return; }
+        while (j.ri > 1 && (n_units + j.ri - 1) / j.ri < grid) j.ri >>= 1;                   // every CTA takes part in every matrix
+        const long long n_groups = (n_units + j.ri - 1) / j.ri;
+        if (n_groups < grid || n_groups * GW >= (1ll << 31)) ok = false;
+        if ((kind == flow::K_O || kind == flow::K_DOWN) && ((n_groups + GW - 1) / GW + 1) * j.ri > 32) ok = false;   // a lane per residual
+        k.n_units = n_units; k.K = K; k.ri = j.ri; k.kc = j.kc; k.nc = j.nc; k.unit = unit;
+        k.scales_off = (uint32_t)align256((uint64_t)rows * K);
+        if (align256((uint64_t)rows * K) >= (1ull << 32)) ok = false;
+        k.rms = rms ? 1 : 0;
+        slot_bytes = std::max(slot_bytes, ringq8::item_bytes(j, unit));
+    };
+    const uint32_t per_x0 = (uint32_t)L + 1u, per = (uint32_t)L;
+    describe(flow::K_QKV, qkv_nl, qkv_nl, D, 1, true);
+    describe(flow::K_O, Dl, Dl, A, 1, false);
+    describe(flow::K_GATE_UP, ffnl, 2 * ffnl, D, 2, true);
+    describe(flow::K_DOWN, Dl, Dl, ffn, 1, false);
+    describe(flow::K_HEAD, Vl, Vl, D, 1, true);
+    if (!ok) return;
+    {
+        flow::KindDesc& q = p.kd[flow::K_QKV];       // x (embedding or the previous layer's down) -> this rank's qkv rows
+        q.in_off = off_of(SLOT_X0, 0); q.in_per_step = per_x0; q.in_mul = 1; q.in_add = 0;
+        q.out_off = off_of(SLOT_Q, 0); q.out_per_step = per; q.out_mul = 1; q.out_add = 0;
+        flow::KindDesc& o = p.kd[flow::K_O];         // head outputs -> x + o (second x slot)
+        o.in_off = off_of(SLOT_A, 0); o.in_per_step = per; o.in_mul = 1; o.in_add = 0;
+        o.out_off = off_of(SLOT_X1, (size_t)r * Dl); o.out_per_step = per; o.out_mul = 1; o.out_add = 0;
+        o.res_off = off_of(SLOT_X0, (size_t)r * Dl);
+        o.push = 1;
+        flow::KindDesc& g = p.kd[flow::K_GATE_UP];
+        g.in_off = off_of(SLOT_X1, 0); g.in_per_step = per; g.in_mul = 1; g.in_add = 0;
+        g.out_off = off_of(SLOT_F, (size_t)r * ffnl); g.out_per_step = per; g.out_mul = 1; g.out_add = 0;
+        g.push = 1;
+        flow::KindDesc& dn = p.kd[flow::K_DOWN];     // MLP activations -> x + down (first x slot again: the next layer's input)
+        dn.in_off = off_of(SLOT_F, 0); dn.in_per_step = per; dn.in_mul = 1; dn.in_add = 0;
+        dn.out_off = off_of(SLOT_X0, (size_t)r * Dl); dn.out_per_step = per_x0; dn.out_mul = 1; dn.out_add = 1;
+        dn.res_off = off_of(SLOT_X1, (size_t)r * Dl);
+        dn.push = 1;
+        flow::KindDesc& hd = p.kd[flow::K_HEAD];
+        hd.in_off = off_of(SLOT_X0, 0); hd.in_per_step = per_x0; hd.in_mul = 0; hd.in_add = L;
+        hd.out_off = off_of(SLOT_LOGITS, (size_t)r * Vl); hd.out_per_step = 1; hd.out_mul = 0; hd.out_add = 0;
+        hd.push = 1;
+    }
+    slot_bytes = (slot_bytes + 127) & ~127;
+    if (fixed + (size_t)NW * 2 * slot_bytes > (size_t)dev->smem_optin) return;
+    int depth = (int)(((size_t)dev->smem_optin - fixed) / ((size_t)NW * slot_bytes));
+    depth = std::min(depth, ringq8::kMaxDepth);
+    const size_t smem = fixed + (size_t)NW * depth * slot_bytes;
+    const bool half = c.weight_dt == RCU_Q8_0H;
+    bool fits = false;
+#define RCU_FLOW_FITS(HD_, T_, NW_) fits = flow_fits_t<HD_, T_, NW_>(smem)
+    RCU_FLOW_DISPATCH(HD, half, NW, RCU_FLOW_FITS);
+#undef RCU_FLOW_FITS
+    if (!fits) { cudaGetLastError(); return; }
+
+    const int wph = grid * NW / Hl;
+    if (wph < NW) return;                        // a CTA must hold warps of at most two heads
+    const int part_stride = (wph + NW - 1) / NW + 1;
+    const size_t part_floats = (size_t)Hl * part_stride * (HD + 2);
+    std::vector<flow::LayerPtrs> host(L);
+    for (int li = 0; li < L; ++li) {
+        const rcu_decoder_layer& Lw = d->layers[li];
+        host[li] = flow::LayerPtrs{{(const int8_t*)Lw.qkv, (const int8_t*)Lw.o, (const int8_t*)Lw.gate_up, (const int8_t*)Lw.down},
+                                   (const float*)Lw.attn_norm, (const float*)Lw.ffn_norm, (__half*)Lw.k_cache, (__half*)Lw.v_cache};
+    }
+    if (!d->comm) {
+        if (cudaMalloc(&d->own_window, (size_t)rcu_window::kSlots * slot_words * 4) != cudaSuccess) { cudaGetLastError(); return; }
+        cudaMemsetAsync(d->own_window, 0, (size_t)rcu_window::kSlots * slot_words * 4, dev->stream);
+    }
+    if (cudaMalloc(&d->d_layer_ptrs, host.size() * sizeof(flow::LayerPtrs)) != cudaSuccess || cudaMalloc(&d->flow_partial, part_floats * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    cudaMemcpyAsync(d->d_layer_ptrs, host.data(), host.size() * sizeof(flow::LayerPtrs), cudaMemcpyHostToDevice, dev->stream);
+    cudaStreamSynchronize(dev->stream);     // `host` goes out of scope
+    p.layers = d->d_layer_ptrs;
+    p.n_layers = L;
+    p.head_w = (const int8_t*)d->lm_head;
+    p.out_norm = (const float*)d->out_norm;
+    p.win = d->comm ? reinterpret_cast<uint32_t*>(d->comm->local.base) : d->own_window;
+    p.n_peers = 0;
+    for (int q = 0; q < W; ++q)
+        if (q != r) p.peer_win[p.n_peers++] = reinterpret_cast<uint32_t*>(d->comm->peers[q].base);
+    p.d_step = d->d_step;
+    p.status = dev->d_status;
+    p.scale_size = ss;
+    p.H = Hl; p.Hkv = Hkvl; p.max_cache = (int)c.max_cache; p.rope_dim = (int)c.rope_dim;
+    p.scale = 1.0f / sqrtf((float)HD);
+    p.d_pos = d->scratch.d_pos;
+    p.rope_tab = d->scratch.rope_tab;
+    p.q_off = off_of(SLOT_Q, 0); p.q_per_step = per;
+    p.a_off = off_of(SLOT_A, 0); p.a_per_step = per;
+    p.a_rank_off = r * Hl * HD;
+    p.partial = d->flow_partial;
+    p.counters = d->scratch.counters;
+    p.part_stride = part_stride;
+    p.slot_bytes = slot_bytes;
+    p.depth = depth;
+    p.l2_ahead = env_l2 < 0 ? 0 : env_l2;
+    p.prof_cta = nullptr;
+    p.prof_job = 0;
+    p.eps = c.rms_eps;
+    p.prof = nullptr;
+    d->slot_words = slot_words;
+    d->flow_grid = grid;
+    d->flow_warps = NW;
+    d->flow_kmax = kmax;
+    d->flow_smem = smem;
+}
+
+template <int HD, class ScaleT, int NW>
+rcu_status launch_flow_t(rcu_decoder* d) {
+    rcu_device* dev = d->dev;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(d->persist_grid);
-    cfg.blockDim = dim3(gemvq8::kThreads);
-    cfg.dynamicSmemBytes = d->persist_smem;
+    cfg.gridDim = dim3(d->flow_grid);
+    cfg.blockDim = dim3((NW + 1) * 32);
+    cfg.dynamicSmemBytes = d->flow_smem;
     cfg.stream = dev->stream;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;      // every CTA resident at once: the grid barriers need it
+    attr[0].id = cudaLaunchAttributeCooperative;      // every CTA resident at once: they wait for each other's results
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, persist::decode_layers_kernel<HD>, d->pp));
+    RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, flow::decode_flow_kernel<HD, ScaleT, NW>, d->fp, d->flow_kmax));
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
 
-rcu_status launch_persistent_layers(rcu_decoder* d) {
-    switch (d->cfg.head_dim) {
-        case 64: return launch_persistent_hd<64>(d);
-        case 96: return launch_persistent_hd<96>(d);
-        default: return launch_persistent_hd<128>(d);
-    }
+rcu_status launch_flow(rcu_decoder* d) {
+    const bool half = d->cfg.weight_dt == RCU_Q8_0H;
+    rcu_status st = RCU_OK;
+#define RCU_FLOW_LAUNCH(HD_, T_, NW_) st = launch_flow_t<HD_, T_, NW_>(d)
+    RCU_FLOW_DISPATCH((int)d->cfg.head_dim, half, d->flow_warps, RCU_FLOW_LAUNCH);
+#undef RCU_FLOW_LAUNCH
+    return st;
 }
 
-// K split of a GEMV on the persistent grid: the rule of gemvq8::plan for a fixed number of warps.
-int persistent_ksplit(int n_units, int unit, int K, int grid) {
-    const long long groups = (n_units + 4 / unit - 1) / (4 / unit);
-    const long long warps = (long long)grid * gemvq8::kWarps;
-    int ks = 1;
-    while (ks < 8 && groups * ks * 2 <= warps && (K / (ks * 2)) >= 1024) ks *= 2;
-    return ks;
-}
-
-template <int HD>
-bool persistent_fit(rcu_decoder* d, size_t smem, int* ctas_per_sm) {
-    auto kern = persist::decode_layers_kernel<HD>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, gemvq8::kThreads, smem) != cudaSuccess) return false;
-    *ctas_per_sm = n;
-    return n >= 1;
-}
-
-// Sets up the persistent-kernel path when asked for (RCU_DECODE_PERSISTENT=1) and this model and device
-// allow it (Q8_0H weights, one GPU, cooperative launch, cache short enough for the merge step).  It is
-// not the default: with a grid barrier of about 2 us between phases it measures slower than the
-// kernel-per-phase step, whose kernels hand over through programmatic dependent launch.
-void setup_persistent(rcu_decoder* d) {
+// One decode step through the data-flow kernel: rope table, embedding row -> tagged words, the kernel
+// (all layers and the lm_head), then the gathered logits, arg-max and the position / step counters.
+rcu_status run_sequence_flow(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev) {
     rcu_device* dev = d->dev;
     const rcu_decoder_config& c = d->cfg;
-    const char* env = std::getenv("RCU_DECODE_PERSISTENT");
-    if (!env || std::atoi(env) == 0) return;
-    if (c.weight_dt != RCU_Q8_0H || d->comm) return;
-    if ((c.max_cache + persist::kTile - 1) / persist::kTile > persist::kMaxSplits) return;
-    int coop = 0;
-    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal) != cudaSuccess || !coop) return;
-    const int HD = (int)c.head_dim;
-    const size_t kmax = std::max(std::max((size_t)c.d_model, (size_t)c.ffn), (size_t)c.n_heads * HD);
-    const size_t attn_bytes = HD == 64 ? sizeof(persist::AttnShared<64>) : HD == 96 ? sizeof(persist::AttnShared<96>) : sizeof(persist::AttnShared<128>);
-    const size_t smem = ((kmax * 2 + gemvq8::kWarps * 4 * sizeof(float) + 15) & ~(size_t)15) + 2 * attn_bytes;
-    if (smem > (size_t)dev->smem_optin) return;
-    int per_sm = 0;
-    const bool ok = HD == 64 ? persistent_fit<64>(d, smem, &per_sm) : HD == 96 ? persistent_fit<96>(d, smem, &per_sm) : persistent_fit<128>(d, smem, &per_sm);
-    if (!ok) { cudaGetLastError(); return; }
-    per_sm = std::min(per_sm, 2);
-    const int grid = per_sm * dev->sm_count;
-    std::vector<persist::LayerW> host(c.n_layers);
-    const uint64_t D = c.d_model, F = c.ffn, Q = (uint64_t)(c.n_heads + 2 * c.n_kv_heads) * HD, A = (uint64_t)c.n_heads * HD;
-    auto scales = [](const void* w, uint64_t n) { return (const __half*)((const char*)w + align256(n)); };
-    for (uint32_t i = 0; i < c.n_layers; ++i) {
-        const rcu_decoder_layer& L = d->layers[i];
-        host[i] = persist::LayerW{(const int8_t*)L.qkv, scales(L.qkv, Q * D), (const int8_t*)L.o, scales(L.o, D * A),
-                                  (const int8_t*)L.gate_up, scales(L.gate_up, 2 * F * D), (const int8_t*)L.down, scales(L.down, D * F),
-                                  (const float*)L.attn_norm, (const float*)L.ffn_norm, (__half*)L.k_cache, (__half*)L.v_cache};
+    rope_table_kernel<<<1, 128, 0, dev->stream>>>(d->scratch.d_pos, logf(c.rope_base), (int)c.rope_dim / 2, d->scratch.rope_tab);
+    RCU_LAUNCH_CHECK(dev);
+    rcu_tensor table{c.weight_dt, 2, {c.vocab, c.d_model, 1, 1}, const_cast<void*>(d->tok_embd)};
+    rcu_tensor ids{RCU_I32, 1, {1, 1, 1, 1}, const_cast<int32_t*>(token_dev)};
+    rcu_tensor xrow{RCU_F16, 2, {1, c.d_model, 1, 1}, d->x};
+    rcu_status st;
+    if (c.weight_dt == RCU_Q8_0H) {
+        st = rcu_index_select(dev, &table, &ids, 0, &xrow);
+    } else {
+        rcu_tensor x32{RCU_F32, 2, {1, c.d_model, 1, 1}, d->act};
+        st = rcu_index_select(dev, &table, &ids, 0, &x32);
+        if (st == RCU_OK) st = rcu_cast(dev, &x32, &xrow);
     }
-    if (cudaMalloc(&d->d_layers, host.size() * sizeof(persist::LayerW)) != cudaSuccess || cudaMalloc(&d->d_bar, sizeof(unsigned int)) != cudaSuccess) {
-        cudaGetLastError();
-        return;
-    }
-    cudaMemcpyAsync(d->d_layers, host.data(), host.size() * sizeof(persist::LayerW), cudaMemcpyHostToDevice, dev->stream);
-    cudaStreamSynchronize(dev->stream);     // `host` goes out of scope
-    persist::Params& p = d->pp;
-    p.layers = d->d_layers;
-    p.n_layers = (int)c.n_layers; p.D = (int)D; p.H = (int)c.n_heads; p.Hkv = (int)c.n_kv_heads; p.ffn = (int)F;
-    p.max_cache = (int)c.max_cache; p.rope_dim = (int)c.rope_dim;
-    p.eps = c.rms_eps; p.scale = 1.0f / sqrtf((float)HD);
-    p.x = d->x; p.qkv = d->qkv; p.attn = d->attn; p.act = d->act;
-    p.d_pos = d->scratch.d_pos; p.rope_tab = d->scratch.rope_tab;
-    p.partial = d->scratch.partial; p.counters = d->scratch.counters;
-    p.bar = d->d_bar; p.status = dev->d_status;
-    p.ks_qkv = persistent_ksplit((int)Q, 1, (int)D, grid);
-    p.ks_o = persistent_ksplit((int)D, 1, (int)A, grid);
-    p.ks_gu = persistent_ksplit((int)F, 2, (int)D, grid);
-    p.ks_down = persistent_ksplit((int)D, 1, (int)F, grid);
-    d->persist_grid = grid;
-    d->persist_smem = smem;
+    if (st != RCU_OK) return st;
+    gemvq8::LLPush emb{};
+    emb.local = d->fp.win + (size_t)SLOT_X0 * d->slot_words;
+    emb.n_peers = 0;
+    emb.seq = gemvq8::LLSeq{d->d_step, c.n_layers + 1u, 0u};
+    publish_words_kernel<<<(c.d_model + 255) / 256, 256, 0, dev->stream>>>(d->x, (int)c.d_model, emb);
+    RCU_LAUNCH_CHECK(dev);
+    st = launch_flow(d);
+    if (st != RCU_OK) return st;
+    gemvq8::LLSource lg{d->fp.win + (size_t)SLOT_LOGITS * d->slot_words, gemvq8::LLSeq{d->d_step, 1u, 0u}, dev->d_status};
+    argmax_advance_gathered_kernel<<<1, 1024, 0, dev->stream>>>(lg, (__half*)logits_dev, (int)c.vocab, argmax_dev, d->scratch.d_pos, d->d_step);
+    RCU_LAUNCH_CHECK(dev);
+    return RCU_OK;
 }
 
 rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev) {
@@ -872,10 +996,7 @@ rcu_status run_sequence(rcu_decoder* d, const int32_t* token_dev, void* logits_d
         if (st == RCU_OK) st = rcu_cast(dev, &x32, &xrow);
     }
     if (st != RCU_OK) return st;
-    if (d->persist_grid > 0) {
-        st = launch_persistent_layers(d);
-        if (st != RCU_OK) return st;
-    } else {
+    {
         for (uint32_t li = 0; li < c.n_layers; ++li) {
             const rcu_decoder_layer& L = d->layers[li];
             st = gemv(dev, c.weight_dt, L.qkv, gemvq8::RmsNormPrologueH{d->x, (const float*)L.attn_norm, c.rms_eps},
@@ -998,12 +1119,14 @@ rcu_status run_sequence_sharded(rcu_decoder* d, const int32_t* token_dev, void* 
     return RCU_OK;
 }
 
-}  // namespace
+rcu_status run_step(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, int32_t* argmax_dev) {
+    if (d->flow_grid > 0) return run_sequence_flow(d, token_dev, logits_dev, argmax_dev);
+    return d->comm ? run_sequence_sharded(d, token_dev, logits_dev, argmax_dev) : run_sequence(d, token_dev, logits_dev, argmax_dev);
+}
 
-extern "C" {
-
-rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers, const void* tok_embd,
-                              const void* out_norm, const void* lm_head, rcu_decoder** out) {
+// Validation and buffers shared by the single-GPU and the sharded decoder (`cfg` holds this rank's head counts).
+rcu_status decoder_alloc(rcu_device* dev, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers, const void* tok_embd,
+                         const void* out_norm, const void* lm_head, rcu_decoder** out) {
     if (!dev || !cfg || !layers || !tok_embd || !out_norm || !lm_head || !out) return RCU_ERR_INVALID_ARG;
     RCU_REQUIRE(dev, cfg->weight_dt == RCU_Q8_0H || cfg->weight_dt == RCU_Q8_0F, "decoder: weights must be Q8_0H or Q8_0F");
     RCU_REQUIRE(dev, cfg->head_dim == 64 || cfg->head_dim == 96 || cfg->head_dim == 128, "decoder: head_dim must be 64, 96 or 128");
@@ -1011,6 +1134,7 @@ rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, co
     RCU_REQUIRE(dev, cfg->d_model % 32 == 0 && cfg->ffn % 32 == 0 && (cfg->n_heads * cfg->head_dim) % 32 == 0, "decoder: Q8_0 rows need whole 32-element blocks");
     RCU_REQUIRE(dev, cfg->rope_dim % 2 == 0 && cfg->rope_dim <= cfg->head_dim && cfg->rope_dim <= 256, "decoder: bad rope_dim");
     RCU_REQUIRE(dev, cfg->max_cache >= 1 && cfg->n_layers >= 1, "decoder: empty model");
+    RCU_REQUIRE(dev, cfg->max_cache <= (uint32_t)(kMaxSplits * kTile), "decoder: max_cache %u exceeds %d positions", cfg->max_cache, kMaxSplits * kTile);
     DevGuard g(dev->ordinal);
     rcu_decoder* d = new rcu_decoder();
     d->dev = dev;
@@ -1019,17 +1143,32 @@ rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, co
     d->tok_embd = tok_embd;
     d->out_norm = out_norm;
     d->lm_head = lm_head;
-    rcu_status st = alloc_attn_scratch(dev, (int)cfg->n_heads, (int)cfg->head_dim, (int)cfg->max_cache, &d->scratch);
+    rcu_status st = alloc_attn_scratch(dev, (int)cfg->n_heads, (size_t)cfg->n_heads * attn_splits((int)cfg->max_cache) * (cfg->head_dim + 2), &d->scratch);
     const size_t qkv_n = (size_t)(cfg->n_heads + 2 * cfg->n_kv_heads) * cfg->head_dim;
     const size_t act_n = std::max<size_t>(cfg->ffn, 2 * (size_t)cfg->d_model);   // also stages an f32 embedding row
     if (st == RCU_OK && (cudaMalloc(&d->x, cfg->d_model * sizeof(__half)) != cudaSuccess || cudaMalloc(&d->qkv, qkv_n * sizeof(__half)) != cudaSuccess ||
                          cudaMalloc(&d->attn, (size_t)cfg->n_heads * cfg->head_dim * sizeof(__half)) != cudaSuccess ||
-                         cudaMalloc(&d->act, act_n * sizeof(__half)) != cudaSuccess))
+                         cudaMalloc(&d->act, act_n * sizeof(__half)) != cudaSuccess || cudaMalloc(&d->d_step, sizeof(unsigned int)) != cudaSuccess))
         st = rcu_fail(dev, RCU_ERR_OOM, "decoder: activation buffers");
     if (st != RCU_OK) { rcu_decoder_destroy(d); return st; }
-    setup_persistent(d);
+    cudaMemsetAsync(d->d_step, 0, sizeof(unsigned int), dev->stream);
     st = rcu_decoder_set_position(d, 0);
     if (st != RCU_OK) { rcu_decoder_destroy(d); return st; }
+    *out = d;
+    return RCU_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+rcu_status rcu_decoder_create(rcu_device* dev, const rcu_decoder_config* cfg, const rcu_decoder_layer* layers, const void* tok_embd,
+                              const void* out_norm, const void* lm_head, rcu_decoder** out) {
+    rcu_decoder* d = nullptr;
+    const rcu_status st = decoder_alloc(dev, cfg, layers, tok_embd, out_norm, lm_head, &d);
+    if (st != RCU_OK) return st;
+    DevGuard g(dev->ordinal);
+    setup_flow(d);
     *out = d;
     return RCU_OK;
 }
@@ -1048,24 +1187,20 @@ rcu_status rcu_decoder_create_sharded(rcu_device* dev, rcu_comm* comm, const rcu
     RCU_REQUIRE(dev, (cfg->d_model / W) % 8 == 0 && cfg->d_model % W == 0 && cfg->ffn % W == 0 && (cfg->ffn / W) % 8 == 0 &&
                          cfg->vocab % W == 0 && (cfg->vocab / W) % 8 == 0 && (cfg->n_heads / W * cfg->head_dim) % 8 == 0,
                 "sharded decoder: d_model, ffn and vocab must split over %u ranks into multiples of 8 rows", W);
-    const size_t need = 4 * (size_t)std::max(std::max(cfg->d_model, cfg->ffn), std::max(cfg->vocab, cfg->n_heads * cfg->head_dim));   // one word per element
+    const size_t need = 4 * (size_t)std::max(std::max(std::max(cfg->d_model, cfg->ffn), std::max(cfg->vocab, cfg->n_heads * cfg->head_dim)),
+                                             (cfg->n_heads + 2 * cfg->n_kv_heads) / W * cfg->head_dim);   // one word per element
     RCU_REQUIRE(dev, comm->local.slot_bytes >= need, "sharded decoder: window slots hold %zu bytes, %zu needed", comm->local.slot_bytes, need);
     rcu_decoder_config local = *cfg;   // per-rank sizes for the shared validation and buffers
     local.n_heads = cfg->n_heads / W;
     local.n_kv_heads = cfg->n_kv_heads / W;
     rcu_decoder* d = nullptr;
-    rcu_status st = rcu_decoder_create(dev, &local, layers, tok_embd, out_norm, lm_head, &d);
+    rcu_status st = decoder_alloc(dev, &local, layers, tok_embd, out_norm, lm_head, &d);
     if (st != RCU_OK) return st;
     d->cfg = *cfg;                     // the step works from the whole model's sizes
-    d->persist_grid = 0;               // the sharded step runs kernel by kernel
     DevGuard g(dev->ordinal);
-    if (cudaMalloc(&d->d_step, sizeof(unsigned int)) != cudaSuccess) {
-        rcu_decoder_destroy(d);
-        return rcu_fail(dev, RCU_ERR_OOM, "sharded decoder: step counter");
-    }
-    cudaMemsetAsync(d->d_step, 0, sizeof(unsigned int), dev->stream);
     d->comm = comm;
     comm->bound = true;
+    setup_flow(d);
     *out = d;
     return RCU_OK;
 }
@@ -1084,8 +1219,10 @@ void rcu_decoder_destroy(rcu_decoder* d) {
     cudaFree(d->attn);
     cudaFree(d->act);
     cudaFree(d->d_step);
-    cudaFree(d->d_layers);
-    cudaFree(d->d_bar);
+    cudaFree(d->d_layer_ptrs);
+    cudaFree(d->own_window);
+    cudaFree(d->flow_partial);
+    cudaFree(d->d_prof);
     delete d;
 }
 
@@ -1113,7 +1250,7 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
     if (!use_graph || d->steps == 0) {
         // first step runs eagerly: sets kernel attributes and counts the launches
         const uint64_t l0 = dev->launches;
-        st = d->comm ? run_sequence_sharded(d, token_dev, logits_dev, argmax_dev) : run_sequence(d, token_dev, logits_dev, argmax_dev);
+        st = run_step(d, token_dev, logits_dev, argmax_dev);
         d->kernels_per_step = (uint32_t)(dev->launches - l0);
     } else {
         if (!d->graph_exec || d->cap_token != token_dev || d->cap_logits != logits_dev || d->cap_argmax != argmax_dev ||
@@ -1122,7 +1259,7 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
             cudaGraph_t graph = nullptr;
             const uint64_t l0 = dev->launches;
             RCU_CUDA(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
-            st = d->comm ? run_sequence_sharded(d, token_dev, logits_dev, argmax_dev) : run_sequence(d, token_dev, logits_dev, argmax_dev);
+            st = run_step(d, token_dev, logits_dev, argmax_dev);
             cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
             dev->launches = l0;   // capture launched nothing
             if (st != RCU_OK) { if (graph) cudaGraphDestroy(graph); return st; }
@@ -1142,10 +1279,55 @@ rcu_status rcu_decoder_step(rcu_decoder* d, const int32_t* token_dev, void* logi
     return RCU_OK;
 }
 
+rcu_status rcu_decoder_profile_step(rcu_decoder* d, const int32_t* token_dev, void* logits_dev, uint64_t* stamps_ns, uint32_t capacity,
+                                    uint32_t* n_stamps) {
+    if (!d || !token_dev || !logits_dev || !stamps_ns || !n_stamps) return RCU_ERR_INVALID_ARG;
+    rcu_device* dev = d->dev;
+    RCU_REQUIRE(dev, d->flow_grid > 0, "decoder: this decoder runs kernel by kernel; per-job time stamps exist only for the data-flow kernel");
+    RCU_REQUIRE(dev, d->position < d->cfg.max_cache, "decoder: the KV cache is full (%u entries)", d->cfg.max_cache);
+    const uint32_t n = 2u * (5u * (uint32_t)d->fp.n_layers + 1u) + 1u + 24u;
+    RCU_REQUIRE(dev, capacity >= n, "decoder: %u time stamps needed, room for %u", n, capacity);
+    DevGuard g(dev->ordinal);
+    if (!d->d_prof) RCU_CUDA(dev, cudaMalloc(&d->d_prof, n * sizeof(unsigned long long)));
+    RCU_CUDA(dev, cudaMemsetAsync(d->d_prof, 0, n * sizeof(unsigned long long), dev->stream));
+    d->fp.prof = d->d_prof;
+    const char* pj = std::getenv("RCU_FLOW_PROF_JOB");
+    unsigned long long* d_cta = nullptr;
+    if (pj) {
+        RCU_CUDA(dev, cudaMalloc(&d_cta, 3 * d->flow_grid * sizeof(unsigned long long)));
+        RCU_CUDA(dev, cudaMemsetAsync(d_cta, 0, 3 * d->flow_grid * sizeof(unsigned long long), dev->stream));
+        d->fp.prof_cta = d_cta;
+        d->fp.prof_job = std::atoi(pj);
+    }
+    const rcu_status st = run_sequence_flow(d, token_dev, logits_dev, nullptr);
+    d->fp.prof = nullptr;
+    d->fp.prof_cta = nullptr;
+    if (pj && st == RCU_OK) {
+        std::vector<unsigned long long> h(3 * d->flow_grid);
+        cudaStreamSynchronize(dev->stream);
+        cudaMemcpy(h.data(), d_cta, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+        unsigned long long t0 = ~0ull;
+        for (int i = 0; i < d->flow_grid; ++i) t0 = std::min(t0, h[3 * i]);
+        fprintf(stderr, "per-CTA times of job %d (ns from the first CTA's start): begun staged done\n", d->fp.prof_job);
+        for (int i = 0; i < d->flow_grid; ++i)
+            fprintf(stderr, "cta %3d %6llu %6llu %6llu\n", i, h[3 * i] - t0, h[3 * i + 1] - t0, h[3 * i + 2] - t0);
+    }
+    if (d_cta) cudaFree(d_cta);
+    if (st != RCU_OK) return st;
+    d->steps++;
+    d->position++;
+    static_assert(sizeof(unsigned long long) == sizeof(uint64_t), "time stamps are 64-bit");
+    const rcu_status sd = rcu_d2h(dev, stamps_ns, d->d_prof, n * sizeof(uint64_t));
+    *n_stamps = n;
+    return sd;
+}
+
 rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void* v_cache, uint32_t n_heads, uint32_t n_kv_heads,
                            uint32_t head_dim, uint32_t max_cache, uint32_t rope_dim, float rope_base, uint32_t position, void* out) {
     if (!dev || !qkv || !k_cache || !v_cache || !out) return RCU_ERR_INVALID_ARG;
     RCU_REQUIRE(dev, n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attn_decode: n_heads must be a multiple of n_kv_heads");
+    RCU_REQUIRE(dev, n_heads <= 65535u, "attn_decode: n_heads %u exceeds the grid limit", n_heads);
+    RCU_REQUIRE(dev, max_cache <= (uint32_t)(kMaxSplits * kTile), "attn_decode: max_cache %u exceeds %d positions", max_cache, kMaxSplits * kTile);
     RCU_REQUIRE(dev, position < max_cache, "attn_decode: position %u outside the cache (%u)", position, max_cache);
     RCU_REQUIRE(dev, rope_dim % 2 == 0 && rope_dim <= head_dim && rope_dim <= 256, "attn_decode: bad rope_dim");
     DevGuard g(dev->ordinal);
@@ -1159,9 +1341,10 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
         if (it != table.end()) s = it->second;
     }
     const size_t need = (size_t)n_heads * attn_splits((int)max_cache) * (head_dim + 2);
-    if (!s || s->partial_floats < need) {
+    if (!s || s->partial_floats < need || s->heads < (int)n_heads) {   // the counters hold one word per head
         AttnScratch* ns = new AttnScratch();
-        rcu_status st = alloc_attn_scratch(dev, (int)n_heads, (int)head_dim, (int)max_cache, ns);
+        // never shrink either part: a later call may bring back the larger shape
+        rcu_status st = alloc_attn_scratch(dev, std::max((int)n_heads, s ? s->heads : 0), std::max(need, s ? s->partial_floats : (size_t)0), ns);
         if (st != RCU_OK) { delete ns; return st; }
         {
             std::lock_guard<std::mutex> lock(mu);
@@ -1233,7 +1416,7 @@ extern "C" rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, v
                 "attn_decode_static: n_heads %u exceeds the built-in scratch (at most %d heads); use rcu_attn_decode", n_heads, kStaticMaxHeads);
     RCU_REQUIRE(dev, head_dim <= (uint32_t)kStaticMaxHeadDim,
                 "attn_decode_static: head_dim %u exceeds the built-in scratch (at most %d); use rcu_attn_decode", head_dim, kStaticMaxHeadDim);
-    RCU_REQUIRE(dev, attn_splits((int)max_cache) <= kStaticMaxSplits,
+    RCU_REQUIRE(dev, max_cache <= (uint32_t)(kStaticMaxSplits * kTile),
                 "attn_decode_static: max_cache %u exceeds the built-in scratch (at most %d positions); use rcu_attn_decode", max_cache,
                 kStaticMaxSplits * kTile);
     RCU_REQUIRE(dev, n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attn_decode_static: n_heads must be a multiple of n_kv_heads");

@@ -2,6 +2,8 @@
 //
 // Stands in for ratchet-core's WgpuDevice (gpu/device.rs:18-119), BufferPool
 // (gpu/pools/buffer_pool.rs) and GPUBuffer transfers (storage/gpu_buffer.rs:49-60,200-218).
+#include <cstdlib>
+
 #include "common.cuh"
 
 rcu_status rcu_fail(rcu_device* dev, rcu_status st, const char* fmt, ...) {
@@ -38,11 +40,15 @@ static rcu_status create_common(int ordinal, cudaStream_t stream, bool own, rcu_
     } else {
         dev->stream = stream;
     }
-    if (cudaMalloc(&dev->d_status, sizeof(int)) != cudaSuccess || cudaMallocHost(&dev->h_status, sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&dev->d_status, kStatusBlockBytes) != cudaSuccess || cudaMallocHost(&dev->h_status, sizeof(int)) != cudaSuccess) {
         delete dev;
         return RCU_ERR_OOM;
     }
-    cudaMemsetAsync(dev->d_status, 0, sizeof(int), dev->stream);
+    if (const char* e = std::getenv("RCU_NO_REUSE")) dev->debug_flags |= std::atoi(e) ? RCU_DEBUG_NO_REUSE : 0;
+    if (const char* e = std::getenv("RCU_PROFILE")) dev->debug_flags |= std::atoi(e) ? RCU_DEBUG_PROFILE : 0;
+    cudaMemsetAsync(dev->d_status, 0, kStatusBlockBytes, dev->stream);
+    cudaMemcpyAsync(reinterpret_cast<char*>(dev->d_status) + 8, &dev->wait_limit_ns, 8, cudaMemcpyHostToDevice, dev->stream);
+    cudaStreamSynchronize(dev->stream);
     *dev->h_status = 0;
     *out = dev;
     return RCU_OK;
@@ -189,6 +195,16 @@ rcu_status rcu_sync(rcu_device* dev) {
     RCU_CUDA(dev, cudaMemcpyAsync(dev->h_status, dev->d_status, sizeof(int), cudaMemcpyDeviceToHost, dev->stream));
     RCU_CUDA(dev, cudaStreamSynchronize(dev->stream));
     return check_status_word(dev);
+}
+
+rcu_status rcu_set_wait_limit_ns(rcu_device* dev, uint64_t nanoseconds) {
+    if (!dev || nanoseconds == 0) return RCU_ERR_INVALID_ARG;
+    DevGuard g(dev->ordinal);
+    dev->wait_limit_ns = nanoseconds;
+    // ordered on the stream: kernels launched after this call see the new limit
+    RCU_CUDA(dev, cudaMemcpyAsync(reinterpret_cast<char*>(dev->d_status) + 8, &dev->wait_limit_ns, 8, cudaMemcpyHostToDevice, dev->stream));
+    RCU_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    return RCU_OK;
 }
 
 // ---------------------------------------------------------------------------------- layouts

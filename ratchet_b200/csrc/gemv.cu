@@ -5,9 +5,7 @@
 // (ops/matmul/subgroup_gemv.rs:89-309, ops/matmul/workgroup_gemv.rs:221-371) for the case
 // Matmul::select_kernel (ops/matmul/mod.rs:716-748) routes to them: rhs is a vector and lhs is not
 // transposed.
-#include <cstdlib>
-
-#include "gemv_q8_bulk.cuh"
+#include "ring.cuh"
 
 namespace {
 
@@ -120,44 +118,29 @@ GemvPlan plan_gemv(const rcu_device* dev, int N, int K, int rows_per_warp, int c
     return GemvPlan{p.ksplit, p.grid};
 }
 
-// Inner-product variant for f16 activations: 0 = packed f16 with the mixed-precision fma,
-// 1 = widen to f32 once per chunk, 2 (default) = dp4a on 16-bit fixed-point planes in the plain kernel
-// (measured 6.5-6.7 TB/s sustained on the 1.2 GB shape against 5.8-6.4 for mode 0, whose operand
-// conversions saturate the XU pipe).  RCU_GEMV_MODE selects it at run time (tuning aid).
-int q8_mode() {
-    static int mode = [] {
-        const char* e = std::getenv("RCU_GEMV_MODE");
-        return e ? std::atoi(e) : 2;
-    }();
-    return mode;
-}
-
-int q8_ctas_per_sm() {
-    static int v = [] {
-        const char* e = std::getenv("RCU_GEMV_CTAS");
-        const int n = e ? std::atoi(e) : 3;
-        return n < 1 ? 1 : (n > 3 ? 3 : n);
-    }();
-    return v;
-}
-
 template <class ScaleT, class ActT>
 rcu_status launch_q8(rcu_device* dev, const int8_t* qs, const void* scales, const void* x, const void* bias, void* y, int N, int K) {
     gemvq8::PlainPrologue<ActT> pro{(const ActT*)x};
     gemvq8::PlainEpilogue<ActT> epi{(const ActT*)bias, (ActT*)y};
     if constexpr (sizeof(ActT) == 2) {
-        static const bool bulk = std::getenv("RCU_GEMV_BULK") != nullptr;   // TMA-ring variant: opt-in (the register kernel measures faster on cold weights)
-        if (bulk && gemvq8::bulk_eligible(qs, K, (size_t)dev->smem_optin, sizeof(ScaleT)))
-            return gemvq8::launch_bulk<ScaleT>(dev, qs, scales, pro, epi, N, K, false);
+        // f16 activations, rows of whole 256-element runs: the weight stream goes through the shared-memory rings
+        // (long streams only: a launch that streams a few MB ends before a ring of 200 KB per SM has paid for its start)
+        if (K >= 2048 && (size_t)N * K >= ((size_t)96 << 20)) {
+            ringq8::PlainPlanes<ringq8::VecSource> rpro{{(const __half*)x}};
+            const rcu_status st = ringq8::launch<ScaleT>(dev, qs, scales, rpro, epi, N, K, false);
+            if (st != RCU_ERR_UNSUPPORTED) return st;
+        }
     }
-    const int ctas = q8_ctas_per_sm();
+    const int ctas = 3;
     // short streams (tens of MB) gain from the pre-loaded, double-buffered variant; long ones from occupancy
     const bool pipe = (size_t)N * K < (size_t)128 << 20;
-    if (q8_mode() == 1) return gemvq8::launch<ScaleT, ActT, 1>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
-    if constexpr (sizeof(ActT) == 2) {
-        if (q8_mode() == 2) return gemvq8::launch<ScaleT, ActT, 2>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
-    }
-    return gemvq8::launch<ScaleT, ActT, 0>(dev, qs, scales, pro, epi, N, K, false, ctas, pipe);
+    // No programmatic dependent launch here: the pipelined kernel reads weights before it waits for its
+    // predecessor, and through this entry point the predecessor may be the kernel that produced them.
+    const bool overlap = false;
+    // f16 activations: dp4a on 16-bit fixed-point planes with 16-element scales (the conversions of an f16
+    // fma path saturate the XU pipe: 4.4 TB/s against 6.6); f32 activations: exact int8 -> f32 and FFMA.
+    constexpr int MODE = sizeof(ActT) == 2 ? 2 : 1;
+    return gemvq8::launch<ScaleT, ActT, MODE>(dev, qs, scales, pro, epi, N, K, overlap, ctas, pipe);
 }
 
 template <class T>

@@ -32,29 +32,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return r;
 }
 
-// f32 += f16 * f16 (exact product, f32 accumulate); sm_100 mixed-precision fma.
-__device__ __forceinline__ float fma_mixed(uint16_t a, uint16_t b, float c) {
-    float d;
-    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ void split_h2(uint32_t v, uint16_t& lo, uint16_t& hi) {
-    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(v));
-}
-
-// four packed int8 -> two half2 holding the exact integer values:
-// byte ^ 0x80 placed in the mantissa of 1024.0h gives 1024 + (q + 128); subtract 1152.
-__device__ __forceinline__ void i8x4_to_h2x2(uint32_t w, uint32_t& h01, uint32_t& h23) {
-    const uint32_t t = w ^ 0x80808080u;
-    const uint32_t a = prmt(t, 0x64646464u, 0x4140u);
-    const uint32_t b = prmt(t, 0x64646464u, 0x4342u);
-    const __half2 k = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
-    __half2 ha = __hsub2(*reinterpret_cast<const __half2*>(&a), k);
-    __half2 hb = __hsub2(*reinterpret_cast<const __half2*>(&b), k);
-    h01 = *reinterpret_cast<uint32_t*>(&ha);
-    h23 = *reinterpret_cast<uint32_t*>(&hb);
-}
-
 // four packed int8 -> four exact floats: byte ^ 0x80 in the mantissa of 2^23, minus (2^23 + 128)
 __device__ __forceinline__ void i8x4_to_f32x4(uint32_t w, float q[4]) {
     const uint32_t t = w ^ 0x80808080u;
@@ -65,39 +42,9 @@ __device__ __forceinline__ void i8x4_to_f32x4(uint32_t w, float q[4]) {
 }
 
 // Dot of 16 int8 (one uint4) with 16 activations held in registers.
-// MODE 0: f16 activations stay packed, mixed-precision fma (measured faster on B200).  MODE 1:
-// activations widened to f32 once per chunk (shared by all ROWS rows), int8 -> f32 through the
-// mantissa trick, FFMA; the only mode for f32 activations.
+// MODE 1: activations widened to f32 once per chunk (shared by all ROWS rows), int8 -> f32 through the
+// mantissa trick, FFMA: the path for f32 activations (bar 1e-4).  MODE 2 (f16 activations) is Dot16Local below.
 template <class ActT, int MODE> struct Dot16;
-
-template <> struct Dot16<__half, 0> {
-    uint32_t x[8];
-    __device__ __forceinline__ void load(const __half* xs, int k) {
-        const uint4 a = *reinterpret_cast<const uint4*>(xs + k);
-        const uint4 b = *reinterpret_cast<const uint4*>(xs + k + 8);
-        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-    }
-    __device__ __forceinline__ float dot(const uint4& w) const {
-        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-        float p0 = 0.f, p1 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t h01, h23;
-            i8x4_to_h2x2(ws[i], h01, h23);
-            uint16_t q0, q1, q2, q3, x0, x1, x2, x3;
-            split_h2(h01, q0, q1);
-            split_h2(h23, q2, q3);
-            split_h2(x[2 * i], x0, x1);
-            split_h2(x[2 * i + 1], x2, x3);
-            p0 = fma_mixed(q0, x0, p0);
-            p1 = fma_mixed(q1, x1, p1);
-            p0 = fma_mixed(q2, x2, p0);
-            p1 = fma_mixed(q3, x3, p1);
-        }
-        return p0 + p1;
-    }
-};
 
 template <class ActT> struct Dot16<ActT, 1> {
     float x[16];
@@ -134,13 +81,14 @@ template <class ActT> struct Dot16<ActT, 1> {
         return p0 + p1;
     }
 };
-template <> struct Dot16<float, 0> : Dot16<float, 1> {};
 
-// MODE 2 (f16 activations): the staged vector is re-expressed once per CTA as 16-bit fixed point,
-// x = sx * X with sx = max|x| / 32767, kept as a signed high-byte plane and an unsigned low-byte plane
-// (2^-15 of the vector's scale, below f16's own 2^-11 per element).  Sixteen int8 codes then meet the
-// planes in eight dp4a and one int -> float conversion, against sixteen mixed-precision fma with their
-// operand conversions in MODE 0; the caller multiplies the finished sums by sx.
+// MODE 2 (f16 activations): the staged vector is re-expressed once per CTA as 16-bit fixed point in
+// groups of 16 elements, x = s_g * X with s_g = max|x_g| / 32767, kept as a signed high-byte plane and an
+// unsigned low-byte plane (2^-15 of the group's largest element, below f16's own 2^-11 per element; a
+// group-local scale keeps that true when the vector holds outliers, as transformer residual streams
+// do).  Sixteen int8 codes then meet the planes in eight dp4a and one int -> float conversion.
+// A group that holds a NaN or an infinity gets a NaN scale, so every output that depends on it is NaN
+// (the f16 arithmetic of the reference gives NaN or an infinity there).
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -151,66 +99,9 @@ __device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) {   // sig
     asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-template <> struct Dot16<__half, 2> {
-    uint4 h, l;
-    __device__ __forceinline__ void load(const unsigned char* planes, int K, int k) {
-        h = *reinterpret_cast<const uint4*>(planes + k);
-        l = *reinterpret_cast<const uint4*>(planes + K + k);
-    }
-    __device__ __forceinline__ float dot(const uint4& w) const {
-        int dh = dp4a_ss(w.x, h.x, 0), dl = dp4a_su(w.x, l.x, 0);
-        dh = dp4a_ss(w.y, h.y, dh); dl = dp4a_su(w.y, l.y, dl);
-        dh = dp4a_ss(w.z, h.z, dh); dl = dp4a_su(w.z, l.z, dl);
-        dh = dp4a_ss(w.w, h.w, dh); dl = dp4a_su(w.w, l.w, dl);
-        return (float)(dh * 256 + dl);
-    }
-};
 
-// Build the two byte planes of MODE 2 from the staged f16 vector (all kThreads threads; K % 16 == 0).
-// Returns sx.  `scratch` is kWarps floats of shared memory; ends with a CTA barrier.
-__device__ __forceinline__ float stage_fixed_planes(const __half* xs, unsigned char* planes, int K, float* scratch) {
-    float amax = 0.f;
-    for (int i = threadIdx.x; i < K / 8; i += kThreads) {
-        const uint4 u = reinterpret_cast<const uint4*>(xs)[i];
-        const uint32_t hw[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
-            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    __syncthreads();                                  // scratch may still be read by the prologue's reduction
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = scratch[0];
-#pragma unroll
-    for (int w = 1; w < kWarps; ++w) amax = fmaxf(amax, scratch[w]);
-    const float inv = amax > 0.f ? 32767.f / amax : 0.f;
-    for (int i = threadIdx.x; i < K / 8; i += kThreads) {
-        const uint4 u = reinterpret_cast<const uint4*>(xs)[i];
-        const uint32_t hw[4] = {u.x, u.y, u.z, u.w};
-        uint32_t hi[2] = {0, 0}, lo[2] = {0, 0};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
-            const int X0 = __float2int_rn(f.x * inv), X1 = __float2int_rn(f.y * inv);
-            const int j = 2 * e;
-            hi[j >> 2] |= (uint32_t)((X0 >> 8) & 0xFF) << (8 * (j & 3));
-            lo[j >> 2] |= (uint32_t)(X0 & 0xFF) << (8 * (j & 3));
-            hi[j >> 2] |= (uint32_t)((X1 >> 8) & 0xFF) << (8 * ((j + 1) & 3));
-            lo[j >> 2] |= (uint32_t)(X1 & 0xFF) << (8 * ((j + 1) & 3));
-        }
-        reinterpret_cast<uint2*>(planes)[i] = make_uint2(hi[0], hi[1]);
-        reinterpret_cast<uint2*>(planes + K)[i] = make_uint2(lo[0], lo[1]);
-    }
-    __syncthreads();
-    return amax / 32767.f;
-}
-
-// Variant for the short kernels of a decode step: every 16 activations get a scale of their own (their
-// max / 32767), so building the planes needs no reduction over the CTA, only the barrier after it.
+// Every 16 activations carry a scale of their own, so building the planes needs no reduction over the
+// CTA, only the barrier after it.
 struct Dot16Local {
     uint4 h, l;
     float s;
@@ -220,11 +111,11 @@ struct Dot16Local {
         s = reinterpret_cast<const float*>(planes + 2 * (size_t)K)[k >> 4];
     }
     __device__ __forceinline__ float dot(const uint4& w) const {
-        int dh = dp4a_ss(w.x, h.x, 0), dl = dp4a_su(w.x, l.x, 0);
-        dh = dp4a_ss(w.y, h.y, dh); dl = dp4a_su(w.y, l.y, dl);
-        dh = dp4a_ss(w.z, h.z, dh); dl = dp4a_su(w.z, l.z, dl);
-        dh = dp4a_ss(w.w, h.w, dh); dl = dp4a_su(w.w, l.w, dl);
-        return (float)(dh * 256 + dl) * s;
+        // four chains of two instead of two chains of four: the sums are exact integers, and a warp that has
+        // few others to hide behind gets its result two dp4a latencies sooner
+        const int h0 = dp4a_ss(w.y, h.y, dp4a_ss(w.x, h.x, 0)), h1 = dp4a_ss(w.w, h.w, dp4a_ss(w.z, h.z, 0));
+        const int l0 = dp4a_su(w.y, l.y, dp4a_su(w.x, l.x, 0)), l1 = dp4a_su(w.w, l.w, dp4a_su(w.z, l.z, 0));
+        return (float)((h0 + h1) * 256 + (l0 + l1)) * s;
     }
 };
 
@@ -241,17 +132,20 @@ __device__ __forceinline__ void stage_fixed_planes_local(const __half* xs, unsig
             v[2 * e] = f.x; v[2 * e + 1] = f.y;
             amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
         }
-        const float inv = amax > 0.f ? 32767.f / amax : 0.f;
+        bool finite = true;                    // fmaxf drops a NaN operand: look for NaN / infinity separately
+#pragma unroll
+        for (int e = 0; e < 16; ++e) finite = finite && fabsf(v[e]) <= 65504.f;
+        const float inv = (amax > 0.f && finite) ? 32767.f / amax : 0.f;
         uint32_t hi[4] = {0, 0, 0, 0}, lo[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            const int X = __float2int_rn(v[e] * inv);
+            const int X = __float2int_rn(finite ? v[e] * inv : 0.f);
             hi[e >> 2] |= (uint32_t)((X >> 8) & 0xFF) << (8 * (e & 3));
             lo[e >> 2] |= (uint32_t)(X & 0xFF) << (8 * (e & 3));
         }
         reinterpret_cast<uint4*>(planes)[i] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         reinterpret_cast<uint4*>(planes + K)[i] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        reinterpret_cast<float*>(planes + 2 * (size_t)K)[i] = amax / 32767.f;
+        reinterpret_cast<float*>(planes + 2 * (size_t)K)[i] = finite ? amax / 32767.f : __int_as_float(0x7fc00000);
     }
     __syncthreads();
 }
@@ -315,6 +209,7 @@ template <class ActT> struct PlainEpilogue {
         if (bias) s += to_f32<ActT>(bias[u]);
         y[u] = from_f32<ActT>(s);
     }
+    __device__ __forceinline__ void warp_done(int, int) const {}
     __device__ __forceinline__ void finish() const {}
 };
 
@@ -328,6 +223,7 @@ struct ResidualEpilogueH {
         const float lin = __half2float(__float2half_rn(acc[0]));
         y[u] = __float2half_rn(lin + __half2float(__ldcg(residual + u)));
     }
+    __device__ __forceinline__ void warp_done(int, int) const {}
     __device__ __forceinline__ void finish() const {}
 };
 
@@ -342,26 +238,29 @@ struct SiluGateEpilogueH {
         const float act = __half2float(__float2half_rn(gate / (1.0f + expf(-gate))));
         y[u] = __float2half_rn(up * act);
     }
+    __device__ __forceinline__ void warp_done(int, int) const {}
     __device__ __forceinline__ void finish() const {}
 };
 
-// Output shard of a row-sharded Linear, all-gathered by the kernel itself: units are stored into this
-// GPU's slice of its own full-size output buffer; the last CTA of the grid to finish (ticket counter)
-// then copies the slice into the same place of every peer's buffer with plain 16-byte stores over
-// NVLink (peer-mapped memory, no multicast, no collective library) and raises a flag on each peer
-// with a system-scope release store.  Consumers wait on their own flags (bounded) before reading.
+// Output shard of a row-sharded Linear, all-gathered by the kernel itself.  Units are stored into this
+// GPU's slice of its own full-size output buffer; a warp that has finished its range of rows copies that
+// range into the same place of every peer's buffer with plain stores over NVLink (peer-mapped memory, no
+// multicast, no collective library), so the gather proceeds while other warps are still streaming weights.
+// A CTA whose warps have all pushed adds one to its arrival counter on every peer (system-scope release);
+// the last CTA of the grid then waits (bounded) until every peer's CTAs have arrived here, so the kernel ends
+// with the gathered vector complete and no wait launch follows.  The counters only ever grow: what a step
+// waits for derives from a device-resident use count of the slot, so a captured launch replays correctly.
 constexpr int kMaxPeers = 8;
-struct PushEpilogueH {
+struct GatherEpilogueH {
     static constexpr int UNIT = 1;
-    const __half* bias;            // local slice of the bias or nullptr
-    __half* y_local;               // this rank's slice inside its own full buffer
-    int slice_elems;               // elements in the slice (multiple of 8)
-    unsigned int* ticket;          // zero between launches
-    __half* peer_dst[kMaxPeers];   // where the slice goes in each peer's full buffer
-    unsigned int* peer_flag[kMaxPeers];   // this rank's flag word on each peer
+    const __half* bias;                    // local slice of the bias or nullptr
+    __half* y_local;                       // this rank's slice inside its own full buffer
+    __half* peer_dst[kMaxPeers];           // where the slice goes in each peer's full buffer
+    unsigned int* peer_count[kMaxPeers];   // this rank's arrival counter for the slot, on each peer
     int n_peers;
-    unsigned int seq;              // value the flags take when this step's slice has landed
-    const unsigned int* my_flags;  // this rank's own flag words [world] for the slot: the last CTA also waits for the peers' slices
+    const unsigned int* my_counts;         // the slot's arrival counters on this rank, one per source rank [world]
+    unsigned int* uses;                    // times the slot has been used so far (device memory)
+    unsigned int* ticket;                  // zero between launches
     int world, self;
     int* status;
     __device__ __forceinline__ void store(int u, const float* acc) const {
@@ -369,46 +268,52 @@ struct PushEpilogueH {
         if (bias) s += __half2float(bias[u]);
         y_local[u] = __float2half_rn(s);
     }
+    // all lanes of a warp, once, after its last unit: rows [u_begin, u_end) are this warp's and final
+    __device__ __forceinline__ void warp_done(int u_begin, int u_end) const {
+        __syncwarp();                       // the lanes' stores to y_local are ordered before the loads below
+        const int lane = threadIdx.x & 31;
+#pragma unroll
+        for (int p = 0; p < kMaxPeers; ++p) {
+            if (p < n_peers) {
+                __half* dst = peer_dst[p];
+                for (int i = u_begin + lane; i < u_end; i += 32) dst[i] = y_local[i];
+            }
+        }
+        __threadfence_system();
+    }
     __device__ __forceinline__ void finish() const {
         __shared__ int is_last;
-        __threadfence();
-        __syncthreads();
+        __syncthreads();                    // every warp of the CTA has pushed (and fenced) its rows
+        if ((int)threadIdx.x < n_peers)
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_count[threadIdx.x]) : "memory");
         if (threadIdx.x == 0) {
             const unsigned int t = atomicAdd(ticket, 1u);
             is_last = (t == gridDim.x - 1);
         }
         __syncthreads();
         if (!is_last) return;
-        __threadfence();
-        const uint4* src = reinterpret_cast<const uint4*>(y_local);
-        const int n16 = slice_elems >> 3;
-        for (int p = 0; p < n_peers; ++p) {
-            uint4* dst = reinterpret_cast<uint4*>(peer_dst[p]);
-            for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
-        }
-        __threadfence_system();
-        __syncthreads();
-        if ((int)threadIdx.x < n_peers)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag[threadIdx.x]), "r"(seq) : "memory");
-        if (threadIdx.x == 0) *ticket = 0;
-        // The kernel ends only when every peer's slice has landed here, so whatever follows in the stream
-        // reads a complete vector without a separate wait launch.  Lane p polls peer p's flag (bounded:
-        // two seconds, then RCU_DEVFLAG_TIMEOUT).
+        // Thread p polls source rank p's counter (bounded by the device's wait limit, then RCU_DEVFLAG_TIMEOUT).
+        const unsigned int target = (*reinterpret_cast<volatile unsigned int*>(uses) + 1u) * gridDim.x;
         const int p = threadIdx.x;
-        if (my_flags != nullptr && p < world && p != self) {
+        if (p < world && p != self) {
             unsigned long long t0;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
             for (;;) {
                 unsigned int v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_flags + p) : "memory");
-                if ((int)(v - seq) >= 0) break;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_counts + p) : "memory");
+                if ((int)(v - target) >= 0) break;
                 unsigned long long t;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                if (t - t0 > 2000000000ull) {
+                if (t - t0 > rcu_wait_limit(status)) {
                     atomicOr(status, RCU_DEVFLAG_TIMEOUT);
                     break;
                 }
             }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            *uses += 1u;
+            *ticket = 0;
         }
     }
 };
@@ -454,8 +359,8 @@ __device__ __forceinline__ uint4 ll_load4(const uint32_t* p) {
 __device__ __forceinline__ bool ll_ready4(const uint4& v, uint32_t tag) {
     return (((v.x ^ tag) | (v.y ^ tag) | (v.z ^ tag) | (v.w ^ tag)) & 0xFFFF0000u) == 0u;
 }
-// Re-polls `v` (words 4 i .. 4 i + 3) until all four carry `tag`.  The wait is bounded in time (two
-// seconds); a wait that runs out, or finds that another one already did, records RCU_DEVFLAG_TIMEOUT and
+// Re-polls `v` (words 4 i .. 4 i + 3) until all four carry `tag`.  The wait is bounded in time (the device's
+// wait limit, two seconds by default); a wait that runs out, or finds that another one already did, records RCU_DEVFLAG_TIMEOUT and
 // goes on with what is there.
 __device__ __forceinline__ void ll_wait4(const uint32_t* words, int i, uint32_t tag, int* status, uint4& v) {
     unsigned long long t0 = 0;
@@ -465,7 +370,7 @@ __device__ __forceinline__ void ll_wait4(const uint32_t* words, int i, uint32_t 
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             if (t0 == 0) t0 = t;
-            else if (t - t0 > 2000000000ull) { atomicOr(status, RCU_DEVFLAG_TIMEOUT); break; }
+            else if (t - t0 > rcu_wait_limit(status)) { atomicOr(status, RCU_DEVFLAG_TIMEOUT); break; }
         }
         v = ll_load4(words + 4 * i);
     }
@@ -550,6 +455,7 @@ struct LLPlainEpilogueH {
     static constexpr int UNIT = 1;
     LLPush out;
     __device__ __forceinline__ void store(int u, const float* acc) const { out.put(u, __float2half_rn(acc[0])); }
+    __device__ __forceinline__ void warp_done(int, int) const {}
     __device__ __forceinline__ void finish() const {}
 };
 
@@ -567,6 +473,7 @@ struct LLResidualEpilogueH {
                                   : __half2float(__ushort_as_half((unsigned short)(__ldcg(res_words + u) & 0xFFFFu)));
         out.put(u, __float2half_rn(lin + r));
     }
+    __device__ __forceinline__ void warp_done(int, int) const {}
     __device__ __forceinline__ void finish() const {}
 };
 
@@ -579,6 +486,7 @@ struct LLSiluGateEpilogueH {
         const float act = __half2float(__float2half_rn(gate / (1.0f + expf(-gate))));
         out.put(u, __float2half_rn(up * act));
     }
+    __device__ __forceinline__ void warp_done(int, int) const {}
     __device__ __forceinline__ void finish() const {}
 };
 
@@ -601,10 +509,9 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
     pdl_wait();
     pro.stage(xs, K, red);
     __syncthreads();
-    // MODE 2: fixed-point byte planes of x behind the reduction scratch (the launcher sizes shared memory for them)
+    // MODE 2: fixed-point byte planes of x (with 16-element scales) behind the reduction scratch
     unsigned char* planes = smem_raw + (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float);
-    float sx = 1.f;
-    if constexpr (MODE == 2) sx = stage_fixed_planes(reinterpret_cast<const __half*>(xs), planes, K, red);
+    if constexpr (MODE == 2) stage_fixed_planes_local(reinterpret_cast<const __half*>(xs), planes, K);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -656,7 +563,7 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
             for (int u = 0; u < UNROLL; ++u) {
                 if (!live[u]) continue;
                 const int k = ((c0 + u * KSPLIT) << 9) + kl;
-                Dot16<ActT, MODE> d16;
+                typename std::conditional<MODE == 2, Dot16Local, Dot16<ActT, 1>>::type d16;
                 if constexpr (MODE == 2) d16.load(planes, K, k);
                 else d16.load(xs, k);
 #pragma unroll
@@ -664,7 +571,7 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
             }
         }
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]) * sx;
+        for (int r = 0; r < ROWS; ++r) acc[r] = warp_sum(acc[r]);
 
         if (KSPLIT > 1) {
             if (lane == 0) {
@@ -689,6 +596,7 @@ gemv_q8_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ scales,
                 if (u0 + i < u_end) epi.store(u0 + i, &acc[i * UNIT]);
         }
     }
+    if (ks == 0) epi.warp_done(u_begin, u_end);
     epi.finish();
 }
 
@@ -767,7 +675,7 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
         for (int u = 0; u < UNROLL; ++u) {
             const int k = ((c0 + u * KSPLIT) << 9) + kl;
             if (k < K) {
-                typename std::conditional<MODE == 2, Dot16Local, Dot16<ActT, MODE == 2 ? 0 : MODE>>::type d16;
+                typename std::conditional<MODE == 2, Dot16Local, Dot16<ActT, 1>>::type d16;
                 if constexpr (MODE == 2) d16.load(planes, K, k);
                 else d16.load(xs, k);
 #pragma unroll
@@ -824,6 +732,7 @@ gemv_q8_pipe_kernel(const int8_t* __restrict__ qs, const ScaleT* __restrict__ sc
             if (it + 3 < n_items) load_item(it + 3, s1);
         }
     }
+    if (ks == 0) epi.warp_done(u_begin, u_end);
     epi.finish();
 }
 
@@ -868,7 +777,7 @@ rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const P
     constexpr int UNIT = Epilogue::UNIT;
     const int n_units = N / UNIT;
     const Plan p = plan(dev, n_units, UNIT, K, ctas_per_sm);
-    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float) + (MODE == 2 ? 2 * (size_t)K + (pipelined ? (size_t)K / 4 : 0) : 0);
+    const size_t smem = (size_t)K * sizeof(ActT) + kWarps * 4 * sizeof(float) + (MODE == 2 ? 2 * (size_t)K + (size_t)K / 4 : 0);
     if (smem > (size_t)dev->smem_optin) return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "gemv: K=%d does not fit the activation stage", K);
 #define RCU_GEMV_Q8_CASE(KS)                                                                                  \
     case KS: {                                                                                                \

@@ -149,38 +149,76 @@ bool multi_broadcast(const rcu_lazy* x, const rcu_lazy* y, uint32_t* rank, uint6
 }
 
 // ------------------------------------------------------------------------------------------------
-// execution order (tensor.rs:696-740)
+// execution order (tensor.rs:696-740): post-order walk without recursion.  A node's sources are visited
+// leaves first, then the sources that have sources of their own — what the reference's
+// `partition(|s| s.op().srcs().is_empty())` followed by `chain` does (its variable names say the
+// opposite) — each group in the order the op lists them.  Meeting a node that is still open means the
+// graph has a cycle.
 // ------------------------------------------------------------------------------------------------
 rcu_status execution_order(rcu_lazy* root, std::vector<rcu_lazy*>* order) {
-    std::unordered_set<uint64_t> done, pending;
-    std::vector<std::pair<rcu_lazy*, size_t>> stack{{root, 0}};
+    enum Mark : char { kOpen = 1, kDone = 2 };
+    struct Frame {
+        rcu_lazy* node;
+        std::vector<rcu_lazy*> srcs;   // in visiting order
+        size_t next;
+    };
+    auto open_frame = [](rcu_lazy* n) {
+        Frame f{n, {}, 0};
+        f.srcs.reserve(n->srcs.size());
+        for (rcu_lazy* s : n->srcs)
+            if (s->srcs.empty()) f.srcs.push_back(s);
+        for (rcu_lazy* s : n->srcs)
+            if (!s->srcs.empty()) f.srcs.push_back(s);
+        return f;
+    };
+    std::unordered_map<uint64_t, Mark> mark;
+    std::vector<Frame> stack;
+    stack.push_back(open_frame(root));
+    mark[root->id] = kOpen;
     while (!stack.empty()) {
-        auto [cur, idx] = stack.back();
-        stack.pop_back();
-        if (idx == cur->srcs.size()) {
-            done.insert(cur->id);
-            pending.erase(cur->id);
-            order->push_back(cur);
+        Frame& f = stack.back();
+        if (f.next == f.srcs.size()) {
+            mark[f.node->id] = kDone;
+            order->push_back(f.node);
+            stack.pop_back();
             continue;
         }
-        // sources that themselves have sources first, leaves after
-        std::vector<rcu_lazy*> all;
-        for (rcu_lazy* s : cur->srcs)
-            if (!s->srcs.empty()) all.push_back(s);
-        for (rcu_lazy* s : cur->srcs)
-            if (s->srcs.empty()) all.push_back(s);
-        rcu_lazy* pre = all[idx];
-        if (done.count(pre->id)) {
-            stack.push_back({cur, idx + 1});
-        } else if (pending.count(pre->id)) {
+        rcu_lazy* pre = f.srcs[f.next++];
+        auto it = mark.find(pre->id);
+        if (it == mark.end()) {
+            mark[pre->id] = kOpen;
+            stack.push_back(open_frame(pre));      // invalidates `f`; nothing below uses it
+        } else if (it->second == kOpen) {
             return rcu_fail(root->dev, RCU_ERR_INVALID_ARG, "Cycle detected whilst computing topological order: %llu", (unsigned long long)pre->id);
-        } else {
-            pending.insert(pre->id);
-            stack.push_back({cur, idx});
-            stack.push_back({pre, 0});
         }
     }
     return RCU_OK;
+}
+
+// Kernel key of a node for the per-op timing table (the reference keys its table by kernel name, gpu/profiler.rs:150-158).
+const char* kind_name(int kind) {
+    switch (kind) {
+        case K_BINARY: return "binary";
+        case K_UNARY: return "unary";
+        case K_CAST: return "cast";
+        case K_MATMUL: return "matmul";
+        case K_NORM: return "norm";
+        case K_SOFTMAX: return "softmax";
+        case K_ROPE: return "rope";
+        case K_CONCAT: return "concat";
+        case K_SELECT: return "index_select";
+        case K_PERMUTE: return "permute";
+        case K_SLICE: return "slice";
+        case K_BROADCAST: return "broadcast";
+        case K_CACHE: return "cache";
+        case K_INDEX_WRITE: return "index_write";
+        case K_CONV: return "conv";
+        default: return "other";
+    }
+}
+const char* dt_name(int dt) {
+    static const char* names[] = {"f32", "f16", "bf16", "i32", "u32", "q8_0f", "q8_0h", "q4_kf", "q4_kh"};
+    return dt >= 0 && dt <= RCU_Q4_KH ? names[dt] : "?";
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -255,6 +293,10 @@ rcu_status resolve(rcu_lazy* out) {
     const size_t n = order.size();
     std::unordered_map<uint64_t, size_t> index;
     for (size_t i = 0; i < n; ++i) index[order[i]->id] = i;
+    // Debug aid (the reference's RATCHET_DEBUG, gpu/buffer_allocator/allocator.rs:121): every tensor gets a buffer
+    // of its own and nothing runs in place, so a wrong result that goes away points at the planner.
+    const bool no_reuse = (dev->debug_flags & RCU_DEBUG_NO_REUSE) != 0;
+    const bool profile = (dev->debug_flags & RCU_DEBUG_PROFILE) != 0;
 
     // how many references to each node come from inside this graph
     std::unordered_map<uint64_t, uint32_t> internal_refs;
@@ -272,7 +314,7 @@ rcu_status resolve(rcu_lazy* out) {
         rcu_lazy* s0 = t->srcs[0];
         if (t->kind == K_VIEW) {
             owner[i] = owner[index[s0->id]];
-        } else if (supports_inplace(t->kind) && sole_owner(s0) && s0->dt == t->dt && s0->numel() == t->numel() &&
+        } else if (!no_reuse && supports_inplace(t->kind) && sole_owner(s0) && s0->dt == t->dt && s0->numel() == t->numel() &&
                    !(s0->resolved() && !s0->storage->owned)) {
             // the op is the sole owner of its first source (tensor.rs:823-824); a borrowed buffer
             // (rcu_lazy_wrap) is never written in place
@@ -299,7 +341,7 @@ rcu_status resolve(rcu_lazy* out) {
         Plan& p = plans[it->second];
         p.last = std::max(p.last, i);
         // externally held (or the output itself): keep the buffer out of the sharing pool
-        if (t == out || t->refs.load() > internal_refs[t->id]) p.exclusive = true;
+        if (no_reuse || t == out || t->refs.load() > internal_refs[t->id]) p.exclusive = true;
     }
     for (size_t i = 0; i < n; ++i) {
         rcu_lazy* t = order[i];
@@ -344,6 +386,8 @@ rcu_status resolve(rcu_lazy* out) {
     }
 
     // run
+    struct TimedNode { std::string key; uint64_t bytes; cudaEvent_t e0, e1; };
+    std::vector<TimedNode> timed;
     uint32_t launched = 0, n_inplace = 0;
     const uint64_t launches0 = dev->launches;
     for (size_t i = 0; i < n; ++i) {
@@ -355,9 +399,35 @@ rcu_status resolve(rcu_lazy* out) {
         if (!t->storage) return rcu_fail(dev, RCU_ERR_INVALID_ARG, "resolve: tensor %llu has no storage", (unsigned long long)t->id);   // TensorError::NoStorage
         if (t->kind == K_VIEW || t->kind == K_CONST) continue;
         if (inplace[i]) ++n_inplace;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        if (profile) {
+            // one event pair per node, as the reference's timestamp-query pairs (gpu/profiler.rs:95-133)
+            if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return rcu_fail(dev, RCU_ERR_CUDA, "resolve: cudaEventCreate");
+            cudaEventRecord(e0, dev->stream);
+        }
         st = run_node(t);
         if (st != RCU_OK) return st;
+        if (profile) {
+            cudaEventRecord(e1, dev->stream);
+            uint64_t bytes = t->nbytes();
+            for (rcu_lazy* s : t->srcs) bytes += s->nbytes();
+            std::string key = std::string(kind_name(t->kind)) + " " + dt_name(t->srcs.empty() ? t->dt : t->srcs[0]->dt);
+            timed.push_back(TimedNode{std::move(key), bytes, e0, e1});
+        }
         ++launched;
+    }
+    if (profile) {
+        cudaStreamSynchronize(dev->stream);
+        for (TimedNode& tn : timed) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, tn.e0, tn.e1);
+            rcu_device::OpTime& ot = dev->op_times[tn.key];
+            ot.count += 1;
+            ot.us += (double)ms * 1e3;
+            ot.bytes += tn.bytes;
+            cudaEventDestroy(tn.e0);
+            cudaEventDestroy(tn.e1);
+        }
     }
     dev->last_resolve.nodes = (uint32_t)n;
     dev->last_resolve.launched = (uint32_t)(dev->launches - launches0);
@@ -404,7 +474,7 @@ rcu_status rcu_lazy_zeros(rcu_device* dev, int32_t dt, uint32_t rank, const uint
 }
 
 rcu_status rcu_lazy_wrap(rcu_device* dev, const rcu_tensor* t, rcu_lazy** out) {
-    if (!dev || !out || !t_valid(t)) return RCU_ERR_INVALID_ARG;
+    if (!out || !t_valid(t)) return RCU_ERR_INVALID_ARG;      // dev may be NULL: a graph that is built and inspected, never resolved
     rcu_lazy* n = new_node(dev, K_CONST, t->dt, t->rank, t->shape, {});
     n->storage = std::make_shared<Storage>(dev, t->data, n->nbytes(), false);
     *out = n;
@@ -635,7 +705,48 @@ rcu_status rcu_lazy_index_write(rcu_lazy* dst, rcu_lazy* src, const uint64_t* st
 
 rcu_status rcu_lazy_resolve(rcu_lazy* t) {
     if (!t) return RCU_ERR_INVALID_ARG;
+    if (!t->dev) return RCU_ERR_INVALID_ARG;                  // built without a device
     return resolve(t);
+}
+
+uint64_t rcu_lazy_id(const rcu_lazy* t) { return t ? t->id : 0; }
+
+rcu_status rcu_lazy_execution_order(rcu_lazy* t, uint64_t* ids, uint32_t capacity, uint32_t* n_nodes) {
+    if (!t || !n_nodes || (capacity && !ids)) return RCU_ERR_INVALID_ARG;
+    std::vector<rcu_lazy*> order;
+    const rcu_status st = execution_order(t, &order);
+    if (st != RCU_OK) return st;
+    *n_nodes = (uint32_t)order.size();
+    for (size_t i = 0; i < order.size() && i < capacity; ++i) ids[i] = order[i]->id;
+    return RCU_OK;
+}
+
+rcu_status rcu_set_debug(rcu_device* dev, uint32_t flags) {
+    if (!dev) return RCU_ERR_INVALID_ARG;
+    dev->debug_flags = flags;
+    return RCU_OK;
+}
+
+uint64_t rcu_profile_report(rcu_device* dev, char* buf, uint64_t capacity, int reset) {
+    if (!dev) return 0;
+    double total = 0.0;
+    for (auto& kv : dev->op_times) total += kv.second.us;
+    std::vector<std::pair<std::string, rcu_device::OpTime>> rows(dev->op_times.begin(), dev->op_times.end());
+    std::sort(rows.begin(), rows.end(), [](const auto& a, const auto& b) { return a.second.us > b.second.us; });
+    std::string text = "kernel                    count     total us      %     GB/s\n";
+    char line[160];
+    for (auto& r : rows) {
+        snprintf(line, sizeof(line), "%-24s %6llu %12.1f %6.1f %8.1f\n", r.first.c_str(), (unsigned long long)r.second.count, r.second.us,
+                 total > 0 ? 100.0 * r.second.us / total : 0.0, r.second.us > 0 ? (double)r.second.bytes / r.second.us * 1e-3 : 0.0);
+        text += line;
+    }
+    if (reset) dev->op_times.clear();
+    if (buf && capacity) {
+        const uint64_t n = std::min<uint64_t>(capacity - 1, text.size());
+        memcpy(buf, text.data(), n);
+        buf[n] = 0;
+    }
+    return text.size() + 1;
 }
 
 rcu_status rcu_lazy_to_host(rcu_lazy* t, void* host, uint64_t nbytes) {

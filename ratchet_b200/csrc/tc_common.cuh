@@ -1,10 +1,10 @@
-// Pieces shared by the tcgen05 GEMM kernels: mbarrier / TMA helpers (from the GEMV's TMA ring), the
+// Pieces shared by the tcgen05 GEMM kernels: mbarrier / TMA helpers (bulk_async.cuh), the
 // shared-memory matrix descriptor for 128-byte-swizzled K-major tiles, fences, commit and the
 // tensor-memory load used by the epilogues.
 #pragma once
 #include <cuda.h>
 
-#include "gemv_q8_bulk.cuh"   // mbarrier + tensor-map helpers
+#include "bulk_async.cuh"   // mbarrier + tensor-map helpers
 
 namespace tc {
 

@@ -106,6 +106,19 @@ class Decoder:
         self.dev.check(self.dev._lib.rcu_decoder_step(self._h, C.c_void_p(tp), C.c_void_p(self.logits.ptr),
                                                       C.c_void_p(self.next_token.ptr) if argmax else None))
 
+    def profile_step(self, token_ptr: Optional[int] = None) -> np.ndarray:
+        """One step outside the CUDA graph with time stamps of the data-flow kernel's first CTA (device
+        nanoseconds): for every job — per layer qkv, attention, o, gate/up, down, then lm_head — when it began
+        and when its input was staged; then the kernel's end; then 6 x 4 cycle sums of the grid's first warp (per job
+        kind: slot wait, multiply, store, request)."""
+        tp = self.token.ptr if token_ptr is None else token_ptr
+        cap = 2 * (5 * self.cfg.n_layers + 1) + 1 + 24
+        stamps = np.zeros(cap, np.uint64)
+        n = C.c_uint32()
+        self.dev.check(self.dev._lib.rcu_decoder_profile_step(self._h, C.c_void_p(tp), C.c_void_p(self.logits.ptr),
+                                                              stamps.ctypes.data_as(C.POINTER(C.c_uint64)), cap, C.byref(n)))
+        return stamps[: n.value]
+
     def step(self, token_id: int) -> np.ndarray:
         """What one iteration of the reference's generate loop does (phi3/generate.rs:93-113): upload the
         token id, run the model, bring the logits back to the host (f16 [1,1,vocab])."""

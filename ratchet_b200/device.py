@@ -180,6 +180,28 @@ class Device:
         self.check(self._lib.rcu_dequantize(self.handle, self._ref(src), self._ref(out)))
         return out
 
+    def set_debug(self, no_reuse: bool = False, profile: bool = False) -> None:
+        """Debug switches of the lazy resolver: one buffer per tensor and nothing in place (the reference's
+        RATCHET_DEBUG), and a per-op timing table (its `gpu-profiling` feature)."""
+        self.check(self._lib.rcu_set_debug(self.handle, (capi.DEBUG_NO_REUSE if no_reuse else 0) | (capi.DEBUG_PROFILE if profile else 0)))
+
+    def profile_report(self, reset: bool = True) -> str:
+        """The per-op table collected while the profile switch was on: kernel, count, total us, %, GB/s."""
+        n = self._lib.rcu_profile_report(self.handle, None, 0, 0)
+        buf = C.create_string_buffer(int(n))
+        self._lib.rcu_profile_report(self.handle, buf, n, int(reset))
+        return buf.value.decode()
+
+    def set_wait_limit_ns(self, ns: int) -> None:
+        """How long a device-side wait may last before it gives up (default two seconds)."""
+        self.check(self._lib.rcu_set_wait_limit_ns(self.handle, int(ns)))
+
+    def quantize(self, src: Buffer, out: Optional[Buffer] = None) -> Buffer:
+        """quant.rs:51-99 on the device: f32 -> Q8_0F, f16 -> Q8_0H, same shape."""
+        out = out or self.empty(capi.Q8_0H if src.dt == capi.F16 else capi.Q8_0F, src.shape)
+        self.check(self._lib.rcu_quantize_device(self.handle, self._ref(src), self._ref(out)))
+        return out
+
     def matmul_shape(self, lhs: Buffer, rhs: Buffer, trans_lhs=False, trans_rhs=False, trans_dst=False):
         d = capi.rcu_tensor()
         st = self._lib.rcu_matmul_dst_shape(self._ref(lhs), self._ref(rhs), int(trans_lhs), int(trans_rhs), int(trans_dst),

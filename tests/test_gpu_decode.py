@@ -73,6 +73,30 @@ def test_attn_decode_kernel(dev, H, Hkv, hd, rope_dim, max_cache, P):
     assert np.array_equal(dv.to_numpy().view(np.uint16), vc.view(np.uint16))
 
 
+def test_allocating_entry_point_regrows_its_counters():
+    """rcu_attn_decode keeps one scratch per device: a call with few heads and a long cache followed by one
+    with more heads and a shorter cache (a smaller partial buffer, but more per-head counters) must not reuse
+    the first call's counter array."""
+    from ratchet_b200 import Device, capi
+    dev = Device(0)
+    try:
+        for (H, Hkv, hd, rope_dim, max_cache, P) in [(8, 8, 128, 128, 8192, 2100), (32, 32, 64, 64, 2304, 2200)]:
+            g = np.random.Generator(np.random.PCG64(H * 7 + P))
+            qkv = g.standard_normal((H + 2 * Hkv) * hd).astype(np.float16)
+            kc = np.zeros((Hkv, max_cache, hd), np.float16)
+            vc = np.zeros((Hkv, max_cache, hd), np.float16)
+            kc[:, :P] = g.standard_normal((Hkv, P, hd)).astype(np.float16)
+            vc[:, :P] = g.standard_normal((Hkv, P, hd)).astype(np.float16)
+            dq, dk, dv = dev.from_numpy(qkv), dev.from_numpy(kc), dev.from_numpy(vc)
+            out = dev.empty(capi.F16, (H * hd,))
+            dev.check(dev._lib.rcu_attn_decode(dev.handle, dq.ptr, dk.ptr, dv.ptr, H, Hkv, hd, max_cache, rope_dim, 10000.0, P, out.ptr))
+            got = out.to_numpy().astype(np.float32)
+            cpu = attention_reference(qkv, kc, vc, H, Hkv, hd, rope_dim, 10000.0, P)
+            assert rel_err(got, cpu) < 1e-2, f"H={H} P={P}"
+    finally:
+        dev.close()
+
+
 def test_decoder_matches_reference_graph(dev):
     """Two layers of Phi-3-mini (full widths, vocab 32064, 1024 prior KV positions, Q8_0H weights with
     f16 activations as the reference loads them on an f16-capable device), three greedy steps: the

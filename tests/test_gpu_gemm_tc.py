@@ -63,20 +63,30 @@ def test_gemm_tc_quantised(dev, kind, M, N, K):
     check(y.to_numpy(), ref, 1e-2, f"{kind} {M}x{N}x{K}")
 
 
-def test_config3_q4k_prefill_shape(dev):
-    """Config 3 at its smallest M: x [128, 3072] f16 N(0,1), W [8192, 3072] N(0, 0.02) in ratchet Q4_K
-    (f16 super-block scales), out [128, 8192] f16."""
-    from ratchet_b200 import capi
+@pytest.fixture(scope="module")
+def config3_weight():
+    """W [8192, 3072] N(0, 0.02) in ratchet Q4_K with f16 super-block scales, and its dequantised form."""
     g = np.random.Generator(np.random.PCG64(0))
-    M, N, K = 128, 8192, 3072
+    N, K = 8192, 3072
     w = (g.standard_normal((N, K), dtype=np.float32) * np.float32(0.02))
-    x = g.standard_normal((M, K)).astype(np.float16)
     buf = orc.quantize_q4k(w, True)
     assert buf.size == 14155776          # 144 bytes per 256-weight super-block
-    wd = orc.dequantize_q4k(buf, (N, K), True)
+    return buf, orc.dequantize_q4k(buf, (N, K), True)
+
+
+@pytest.mark.parametrize("M", [128, 512, 2048])
+def test_config3_q4k_prefill_shape(dev, config3_weight, M):
+    """Config 3 at its three sizes: x [M, 3072] f16 N(0,1), W [8192, 3072] in ratchet Q4_K, out [M, 8192]
+    f16.  M <= 512 runs the kernel that converts Q4_K tiles in shared memory; M = 2048 converts the matrix
+    once into scratch and runs the f16 kernel with 128 x 256 tiles: both against dequantise -> matmul."""
+    from ratchet_b200 import capi
+    N, K = 8192, 3072
+    buf, wd = config3_weight
+    x = np.random.Generator(np.random.PCG64(M)).standard_normal((M, K)).astype(np.float16)
     ref = orc.matmul(wd, x, None, False, True, True)
     y = dev.matmul(dev.from_quantized(buf, capi.Q4_KH, (N, K)), dev.from_numpy(x), None, False, True, True)
-    check(y.to_numpy(), ref, 1e-2, "config 3, M=128")
+    assert y.shape == (M, N)
+    check(y.to_numpy(), ref, 1e-2, f"config 3, M={M}")
 
 
 # f32 Linear on the tensor cores (split TF32): the f32 bar, 1e-4 of the result's scale

@@ -128,6 +128,40 @@ def test_buffer_planning_reuses_memory(dev):
     assert np.allclose(h.to_numpy(), ref, atol=1e-4)
 
 
+def test_debug_switches_no_reuse_and_profile(dev):
+    """The resolver's two debug aids: with no-reuse every tensor gets a buffer of its own and nothing runs in
+    place (same results); with profiling every node is bracketed by an event pair and the table names each
+    kernel with its count, time and bandwidth."""
+    from ratchet_b200 import Tensor, last_resolve_stats
+    g = np.random.Generator(np.random.PCG64(31))
+    x = g.standard_normal((64, 256)).astype(np.float32)
+    w = [(g.standard_normal((256, 256)) * 0.05).astype(np.float32) for _ in range(3)]
+
+    def run():
+        h = Tensor.from_data(x, device=dev)
+        for wi in w:
+            h = Tensor.from_data(wi, device=dev).gemm(h, None, False, True, True).tanh()
+        h.resolve()
+        return h.to_numpy(), last_resolve_stats(dev)
+
+    base, st0 = run()
+    assert st0["inplace"] == 3 and st0["buffers"] <= 3
+    dev.set_debug(no_reuse=True, profile=True)
+    try:
+        dev.profile_report(reset=True)
+        again, st1 = run()
+        assert st1["inplace"] == 0 and st1["buffers"] == 6 and st1["planned_bytes"] == st1["naive_bytes"]
+        assert np.array_equal(again, base)
+        table = dev.profile_report(reset=True)
+        rows = {ln.split()[0] + " " + ln.split()[1]: ln.split() for ln in table.splitlines()[1:]}
+        assert set(rows) == {"matmul f32", "unary f32"}, table
+        assert int(rows["matmul f32"][2]) == 3 and int(rows["unary f32"][2]) == 3
+        assert float(rows["matmul f32"][3]) > 0 and abs(float(rows["matmul f32"][4]) + float(rows["unary f32"][4]) - 100.0) < 0.2
+        assert dev.profile_report() .count("\n") == 1          # cleared
+    finally:
+        dev.set_debug()
+
+
 def test_concat_cache_select_through_graph(dev):
     from ratchet_b200 import Tensor, capi
     g = np.random.Generator(np.random.PCG64(4))

@@ -1,6 +1,6 @@
 """Parity of every CUDA op with the CPU oracle, through the C ABI, on identical seeded inputs.
 
-Bars (BASELINE north_star): dequantisation / indexing / copies bit-exact; f32 ops within 1e-4
+Bars: dequantisation / indexing / copies bit-exact; f32 ops within 1e-4
 (relative, with an equal absolute floor as in the reference's all_close, tensor.rs:1039-1043);
 f16 and quantised matmuls within 1e-2.
 """
@@ -107,6 +107,83 @@ def test_gemv_q8(dev, pair, N, K):
         y = dev.matmul(dw, dev.from_numpy(x), None if b is None else dev.from_numpy(b), False, True, True)
         assert y.shape == (1, N) and y.dt == (capi.F16 if half_x else capi.F32)
         assert_matmul_close(y.to_numpy().reshape(-1), ref, 1e-2 if half_x else 1e-4, f"gemv {pair} {N}x{K}")
+
+
+def test_gemv_q8_headline_shape(dev):
+    """The benchmark's shape, K = 16384 x N = 65536 with f32 block scales and f16 activations (1.2 GB of
+    weights: the plain streaming kernel with its K split of 8).  The matrix is 4096 distinct random rows
+    repeated down the 65536, as the benchmark builds it; the oracle computes the distinct rows once and
+    every repetition on the device must reproduce them."""
+    from ratchet_b200 import capi
+    K, N, uniq = 16384, 65536, 4096
+    g = rng(65536)
+    w = (g.standard_normal((uniq, K), dtype=np.float32) * np.float32(0.02))
+    x = g.standard_normal((1, K)).astype(np.float16)
+    small = orc.quantize_q8(w)
+    ref = orc.gemv_q8(small, uniq, K, False, x.reshape(-1))
+    buf = np.zeros(capi.dtype_nbytes(capi.Q8_0F, N * K), np.uint8)
+    off_small = capi.dtype_segments(capi.Q8_0F, uniq * K)[1]
+    off = capi.dtype_segments(capi.Q8_0F, N * K)[1]
+    buf[: N * K].reshape(N // uniq, uniq * K)[:] = small[: uniq * K]
+    buf[off: off + N * K // 8].reshape(N // uniq, uniq * K // 8)[:] = small[off_small: off_small + uniq * K // 8]
+    dw = dev.from_quantized(buf, capi.Q8_0F, (N, K))
+    del buf
+    y = dev.matmul(dw, dev.from_numpy(x), None, False, True, True).to_numpy().reshape(N // uniq, uniq)
+    dw.free()
+    for rep in range(N // uniq):
+        assert_matmul_close(y[rep], ref, 1e-2, f"headline gemv, rows {rep * uniq}..")
+    # every repetition of a row is computed by a different warp team but from the same bytes
+    assert np.array_equal(bits(np.ascontiguousarray(y[0])), bits(np.ascontiguousarray(y[-1])))
+
+
+@pytest.mark.parametrize("pair", ["Q8_0H/F16", "Q8_0F/F16"])
+@pytest.mark.parametrize("N,K", [(512, 8192), (3072, 3072), (40, 16384)])
+@pytest.mark.parametrize("kind", ["one_large", "one_percent_x50", "huge"])
+def test_gemv_q8_activation_outliers(dev, pair, N, K, kind):
+    """Activation vectors with outliers, as transformer residual streams have them: the f16-activation
+    kernels re-express x in 16-bit fixed point per group of 16 elements, so a large element must not cost
+    the others their precision.  Bar as for every f16 matmul: 1e-2 of the result's scale."""
+    from ratchet_b200 import capi
+    g = rng(N + K + len(kind))
+    half_w = pair.startswith("Q8_0H")
+    w = (g.standard_normal((N, K)) * 0.02).astype(np.float16 if half_w else np.float32)
+    x = g.standard_normal(K).astype(np.float32)
+    if kind == "one_large":
+        x[K // 3] = 200.0
+    elif kind == "one_percent_x50":
+        x[g.choice(K, K // 100, replace=False)] *= 50.0
+    else:
+        # 1e3 times the typical magnitude, meeting zero weights: the result is made of the ordinary elements
+        # alone, so any precision they lost to the outlier shows at the result's own scale (with one scale for
+        # the whole vector every other element would be rounded to a multiple of 0.03)
+        x[7] = 1000.0
+        w[:, 7] = 0
+    x = x.astype(np.float16).reshape(1, K)
+    wq = orc.quantize_q8(w)
+    ref = orc.gemv_q8(wq, N, K, half_w, x.reshape(-1))
+    dw = dev.from_quantized(wq, capi.Q8_0H if half_w else capi.Q8_0F, (N, K))
+    y = dev.matmul(dw, dev.from_numpy(x), None, False, True, True).to_numpy().reshape(-1)
+    assert_matmul_close(y, ref, 1e-2, f"gemv outliers {kind} {pair} {N}x{K}")
+
+
+@pytest.mark.parametrize("N,K", [(64, 512), (3072, 3072), (40, 16384)])
+def test_gemv_q8_nan_activation_propagates(dev, N, K):
+    """A NaN in x makes every output NaN, as it does in the reference's float arithmetic (each row's sum
+    includes that element); an infinity makes every output non-finite."""
+    from ratchet_b200 import capi
+    g = rng(N ^ K)
+    w = (g.standard_normal((N, K)) * 0.02).astype(np.float16)
+    wq = orc.quantize_q8(w)
+    dw = dev.from_quantized(wq, capi.Q8_0H, (N, K))
+    for bad in (np.nan, np.inf):
+        x = g.standard_normal((1, K)).astype(np.float16)
+        x[0, K // 2 + 1] = bad
+        y = dev.matmul(dw, dev.from_numpy(x), None, False, True, True).to_numpy().reshape(-1)
+        ref = orc.gemv_q8(wq, N, K, True, x.reshape(-1))
+        assert not np.isfinite(ref).any()
+        assert not np.isfinite(y.astype(np.float32)).any()
+        if np.isnan(bad):
+            assert np.isnan(y.astype(np.float32)).all()
 
 
 # Q4_K weights with a vector: no kernel in the reference (`(gemv, q4)` is todo!, ops/matmul/mod.rs:746); the
