@@ -351,6 +351,9 @@ rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, void* k_cach
 rcu_status rcu_comm_create(rcu_device* dev, int rank, int world, uint64_t slot_bytes, rcu_comm** out);
 rcu_status rcu_comm_export(rcu_comm* comm, void* handle64);
 rcu_status rcu_comm_import(rcu_comm* comm, int peer, const void* handle64);
+/* The same for a peer window that lives in this process on the same device (CUDA IPC handles cannot be opened
+ * by the process that exported them): links `other`'s window as rank `peer`.  `other` must outlive `comm`. */
+rcu_status rcu_comm_import_local(rcu_comm* comm, int peer, rcu_comm* other);
 void rcu_comm_destroy(rcu_comm* comm);
 int rcu_comm_rank(const rcu_comm* comm);
 int rcu_comm_world(const rcu_comm* comm);

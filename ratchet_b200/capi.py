@@ -174,6 +174,7 @@ SIGNATURES = {
     "rcu_comm_create": (C.c_int, [_DEV, C.c_int, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
     "rcu_comm_export": (C.c_int, [C.c_void_p, C.c_void_p]),
     "rcu_comm_import": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "rcu_comm_import_local": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "rcu_comm_destroy": (None, [C.c_void_p]),
     "rcu_comm_rank": (C.c_int, [C.c_void_p]),
     "rcu_comm_world": (C.c_int, [C.c_void_p]),

@@ -69,6 +69,18 @@ rcu_status rcu_comm_import(rcu_comm* c, int peer, const void* handle64) {
     return RCU_OK;
 }
 
+rcu_status rcu_comm_import_local(rcu_comm* c, int peer, rcu_comm* other) {
+    if (!c || !other) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(c->dev, peer >= 0 && peer < c->world && peer != c->rank, "comm: bad peer %d", peer);
+    RCU_REQUIRE(c->dev, other->rank == peer && other->world == c->world && other->local.slot_bytes == c->local.slot_bytes,
+                "comm: the other window is not rank %d of the same exchange", peer);
+    RCU_REQUIRE(c->dev, other->dev->ordinal == c->dev->ordinal, "comm: windows of one process are linked directly only on one device");
+    c->peers[peer] = other->local;
+    c->opened[peer] = false;             // nothing to close: the memory belongs to `other`
+    c->linked[peer] = true;
+    return RCU_OK;
+}
+
 void rcu_comm_destroy(rcu_comm* c) {
     if (!c) return;
     DevGuard g(c->dev->ordinal);
@@ -94,7 +106,7 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
     RCU_REQUIRE(dev, n_local * c->world * 2 <= c->local.slot_bytes, "gemv_allgather: output (%llu B) exceeds the window slot", (unsigned long long)(n_local * c->world * 2));
     RCU_REQUIRE(dev, !bias_shard || (bias_shard->dt == RCU_F16 && t_numel(bias_shard) == n_local), "gemv_allgather: bias shard mismatch");
     for (int p = 0; p < c->world; ++p)
-        RCU_REQUIRE(dev, p == c->rank || c->opened[p], "gemv_allgather: peer %d has not been imported", p);
+        RCU_REQUIRE(dev, p == c->rank || c->opened[p] || c->linked[p], "gemv_allgather: peer %d has not been imported", p);
     DevGuard g(dev->ordinal);
     RCU_REQUIRE(dev, !c->bound, "gemv_allgather: this window belongs to a sharded decoder");
     // Three output slots in rotation: a result stays valid until the call after next, and a peer that is one

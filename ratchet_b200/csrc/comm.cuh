@@ -28,7 +28,8 @@ struct rcu_comm {
     int rank = 0, world = 1;
     rcu_window::Window local;
     rcu_window::Window peers[gemvq8::kMaxPeers];   // peers[rank] == local
-    bool opened[gemvq8::kMaxPeers] = {};
+    bool opened[gemvq8::kMaxPeers] = {};           // imported through CUDA IPC (closed at destruction)
+    bool linked[gemvq8::kMaxPeers] = {};           // another window of this process (rcu_comm_import_local)
     unsigned int seq = 0;          // host-side sequence of rcu_gemv_q8_allgather
     bool bound = false;            // a sharded decoder owns the flags of this window
 };

@@ -718,7 +718,7 @@ struct rcu_decoder {
     size_t flow_smem = 0;
     uint32_t* own_window = nullptr;       // single GPU: the exchange window lives here (no peers)
     size_t slot_words = 0;
-    float* flow_partial = nullptr;
+    unsigned long long* flow_partial = nullptr;
     unsigned long long* d_prof = nullptr; // per-job time stamps of one step (rcu_decoder_profile)
     // captured step
     cudaGraphExec_t graph_exec = nullptr;
@@ -744,12 +744,12 @@ bool flow_fits_t(size_t smem) {
     return n >= 1;
 }
 
-// Instantiations of the data-flow kernel: head_dim 64 / 96 / 128, f16 or f32 block scales, 8 / 12 / 16 consumer warps.
+// Instantiations of the data-flow kernel: head_dim 64 / 96 / 128, f16 or f32 block scales, 7 or 8 consumer warps
+// (with the requester warp: 8 warps, which leaves a thread 255 registers, or 9).
 #define RCU_FLOW_DISPATCH(HD_, HALF_, NW_, CALL)                                                            \
     do {                                                                                                    \
         if ((NW_) == 8) { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 8, CALL); }                                      \
-        else if ((NW_) == 12) { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 12, CALL); }                               \
-        else { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 16, CALL); }                                                \
+        else { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 7, CALL); }                                                 \
     } while (0)
 #define RCU_FLOW_DISPATCH_HD(HD_, HALF_, NWC, CALL)                                                         \
     do {                                                                                                    \
@@ -759,7 +759,7 @@ bool flow_fits_t(size_t smem) {
     } while (0)
 
 template <int HD> size_t flow_union_bytes(int kmax, int nw) {
-    return nw == 8 ? flow::union_bytes<HD, 8>(kmax) : nw == 12 ? flow::union_bytes<HD, 12>(kmax) : flow::union_bytes<HD, 16>(kmax);
+    return nw == 8 ? flow::union_bytes<HD, 8>(kmax) : flow::union_bytes<HD, 7>(kmax);
 }
 
 // Exchange slots of the window (each slot_words 32-bit words): the residual stream alternates between two.
@@ -782,10 +782,9 @@ void setup_flow(rcu_decoder* d) {
     int coop = 0;
     if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal) != cudaSuccess || !coop) return;
     const int grid = dev->sm_count;
-    // consumer warps per CTA and how far beyond the rings L2 is asked for rows (tuning aids; the defaults are the measured best)
-    static const int env_nw = [] { const char* e = std::getenv("RCU_FLOW_WARPS"); return e ? std::atoi(e) : 12; }();
-    static const int env_l2 = [] { const char* e = std::getenv("RCU_FLOW_L2_AHEAD"); return e ? std::atoi(e) : 0; }();
-    const int NW = env_nw == 8 || env_nw == 16 ? env_nw : 12;
+    // consumer warps per CTA (tuning aid; the default is the measured best)
+    static const int env_nw = [] { const char* e = std::getenv("RCU_FLOW_WARPS"); return e ? std::atoi(e) : 7; }();
+    const int NW = env_nw == 8 ? 8 : 7;
     const long long GW = (long long)grid * NW;
     if (Hl < 1 || Hl > grid || (int)c.rope_dim > flow::kMaxRope || L > flow::kMaxLayersShared) return;
     if (Dl % 4 || ffnl % 4 || Vl % 4 || (Hl * HD) % 4) return;          // consumers take four words per load
@@ -797,7 +796,7 @@ void setup_flow(rcu_decoder* d) {
     flow::Params& p = d->fp;
     p = flow::Params{};
     bool ok = true;
-    int kmax = std::max(std::max(D, ffn), A), slot_bytes = 2 * flow::kTileP * HD * 2;
+    int kmax = std::max(std::max(D, ffn), A), slot_bytes = 2 * 16 * HD * 2;      // an attention item: 16 positions of K and V
     // shared memory left for the rings, and the item size that lets every warp hold two items
     const size_t ub0 = HD == 64 ? flow_union_bytes<64>(kmax, NW) : HD == 96 ? flow_union_bytes<96>(kmax, NW) : flow_union_bytes<128>(kmax, NW);
     const size_t fixed = flow::union_off(NW, L) + ub0;
@@ -860,10 +859,8 @@ void setup_flow(rcu_decoder* d) {
 #undef RCU_FLOW_FITS
     if (!fits) { cudaGetLastError(); return; }
 
-    const int wph = grid * NW / Hl;
-    if (wph < NW) return;                        // a CTA must hold warps of at most two heads
-    const int part_stride = (wph + NW - 1) / NW + 1;
-    const size_t part_floats = (size_t)Hl * part_stride * (HD + 2);
+    const int part_stride = std::min(grid / Hl, flow::kMaxCtasPerHead);       // a head spreads over at most this many CTAs
+    const size_t part_words = (size_t)Hl * part_stride * (HD + 2);
     std::vector<flow::LayerPtrs> host(L);
     for (int li = 0; li < L; ++li) {
         const rcu_decoder_layer& Lw = d->layers[li];
@@ -874,10 +871,11 @@ void setup_flow(rcu_decoder* d) {
         if (cudaMalloc(&d->own_window, (size_t)rcu_window::kSlots * slot_words * 4) != cudaSuccess) { cudaGetLastError(); return; }
         cudaMemsetAsync(d->own_window, 0, (size_t)rcu_window::kSlots * slot_words * 4, dev->stream);
     }
-    if (cudaMalloc(&d->d_layer_ptrs, host.size() * sizeof(flow::LayerPtrs)) != cudaSuccess || cudaMalloc(&d->flow_partial, part_floats * sizeof(float)) != cudaSuccess) {
+    if (cudaMalloc(&d->d_layer_ptrs, host.size() * sizeof(flow::LayerPtrs)) != cudaSuccess || cudaMalloc(&d->flow_partial, part_words * sizeof(unsigned long long)) != cudaSuccess) {
         cudaGetLastError();
         return;
     }
+    cudaMemsetAsync(d->flow_partial, 0, part_words * sizeof(unsigned long long), dev->stream);
     cudaMemcpyAsync(d->d_layer_ptrs, host.data(), host.size() * sizeof(flow::LayerPtrs), cudaMemcpyHostToDevice, dev->stream);
     cudaStreamSynchronize(dev->stream);     // `host` goes out of scope
     p.layers = d->d_layer_ptrs;
@@ -899,11 +897,9 @@ void setup_flow(rcu_decoder* d) {
     p.a_off = off_of(SLOT_A, 0); p.a_per_step = per;
     p.a_rank_off = r * Hl * HD;
     p.partial = d->flow_partial;
-    p.counters = d->scratch.counters;
     p.part_stride = part_stride;
     p.slot_bytes = slot_bytes;
     p.depth = depth;
-    p.l2_ahead = env_l2 < 0 ? 0 : env_l2;
     p.prof_cta = nullptr;
     p.prof_job = 0;
     p.eps = c.rms_eps;
@@ -1180,7 +1176,7 @@ rcu_status rcu_decoder_create_sharded(rcu_device* dev, rcu_comm* comm, const rcu
     RCU_REQUIRE(dev, comm->dev == dev, "sharded decoder: the window belongs to another device");
     RCU_REQUIRE(dev, !comm->bound && comm->seq == 0, "sharded decoder: the window must be fresh (its flags count this decoder's steps)");
     for (int p = 0; p < comm->world; ++p)
-        RCU_REQUIRE(dev, p == comm->rank || comm->opened[p], "sharded decoder: peer %d has not been imported", p);
+        RCU_REQUIRE(dev, p == comm->rank || comm->opened[p] || comm->linked[p], "sharded decoder: peer %d has not been imported", p);
     RCU_REQUIRE(dev, cfg->n_heads % W == 0 && cfg->n_kv_heads % W == 0, "sharded decoder: heads (%u, %u kv) must divide over %u ranks",
                 cfg->n_heads, cfg->n_kv_heads, W);
     // slices travel as 16-byte vectors and GEMV rows come in groups of 8
@@ -1294,8 +1290,8 @@ rcu_status rcu_decoder_profile_step(rcu_decoder* d, const int32_t* token_dev, vo
     const char* pj = std::getenv("RCU_FLOW_PROF_JOB");
     unsigned long long* d_cta = nullptr;
     if (pj) {
-        RCU_CUDA(dev, cudaMalloc(&d_cta, 3 * d->flow_grid * sizeof(unsigned long long)));
-        RCU_CUDA(dev, cudaMemsetAsync(d_cta, 0, 3 * d->flow_grid * sizeof(unsigned long long), dev->stream));
+        RCU_CUDA(dev, cudaMalloc(&d_cta, 10 * d->flow_grid * sizeof(unsigned long long)));
+        RCU_CUDA(dev, cudaMemsetAsync(d_cta, 0, 10 * d->flow_grid * sizeof(unsigned long long), dev->stream));
         d->fp.prof_cta = d_cta;
         d->fp.prof_job = std::atoi(pj);
     }
@@ -1303,14 +1299,17 @@ rcu_status rcu_decoder_profile_step(rcu_decoder* d, const int32_t* token_dev, vo
     d->fp.prof = nullptr;
     d->fp.prof_cta = nullptr;
     if (pj && st == RCU_OK) {
-        std::vector<unsigned long long> h(3 * d->flow_grid);
+        std::vector<unsigned long long> h(10 * d->flow_grid);
         cudaStreamSynchronize(dev->stream);
         cudaMemcpy(h.data(), d_cta, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
         unsigned long long t0 = ~0ull;
-        for (int i = 0; i < d->flow_grid; ++i) t0 = std::min(t0, h[3 * i]);
-        fprintf(stderr, "per-CTA times of job %d (ns from the first CTA's start): begun staged done\n", d->fp.prof_job);
-        for (int i = 0; i < d->flow_grid; ++i)
-            fprintf(stderr, "cta %3d %6llu %6llu %6llu\n", i, h[3 * i] - t0, h[3 * i + 1] - t0, h[3 * i + 2] - t0);
+        for (int i = 0; i < d->flow_grid; ++i) t0 = std::min(t0, h[2 * i]);
+        fprintf(stderr, "per-CTA times (ns) of five jobs from job %d: for each job, begun and staged\n", d->fp.prof_job);
+        for (int i = 0; i < d->flow_grid; ++i) {
+            fprintf(stderr, "cta %3d", i);
+            for (int j = 0; j < 5; ++j) fprintf(stderr, " %6llu %6llu", h[(j * d->flow_grid + i) * 2] - t0, h[(j * d->flow_grid + i) * 2 + 1] - t0);
+            fprintf(stderr, "\n");
+        }
     }
     if (d_cta) cudaFree(d_cta);
     if (st != RCU_OK) return st;

@@ -15,17 +15,20 @@
 //   * the weights, and the cached K/V rows, do not depend on activations.  Every consumer warp owns a
 //     ring of shared-memory slots; one more warp per CTA, the requester, walks each consumer's sequence
 //     of items through the whole job list and keeps its ring full with 1-D bulk copies (ring.cuh; no
-//     tensor maps, no multicast), asking L2 for the items a few places further on.  While a warp waits
+//     tensor maps, no multicast).  While a warp waits
 //     for the activation vector of one matrix, its slots fill with rows of that matrix and of the next,
 //     so HBM keeps streaming across the hand-overs.
 // Arithmetic and rounding points are those of the per-kernel step: gemvq8's dp4a inner product on
 // 16-bit fixed-point planes, its prologues and epilogues, and split-KV attention with f16-rounded
 // scores (phi3/attn.rs:142-157).
 //
-// Attention: the warps of the grid are dealt to the local heads (wph warps per head), a warp owns a
-// contiguous run of 16-position tiles of one head and folds them with an online softmax; the warps of a
-// head inside one CTA merge through shared memory, the (at most few) CTAs of a head through a small
-// global scratch and a per-head ticket; the last one publishes the head's output as tagged words.
+// Attention: head h belongs to the CTAs [h * stride, h * stride + c) with stride = grid / heads and c = the
+// CTAs a head needs so that a warp folds about two 16-position tiles (at most eight, at most stride).
+// A warp owns a contiguous run of tiles and folds them with an online softmax, its q in registers; the
+// warps of a CTA merge through shared memory; with c = 1 that CTA publishes the head's output as tagged
+// words at once, otherwise the head's CTAs merge through a small global scratch and a per-head ticket
+// and the last one publishes (every partial result requested before any is used: one trip to L2).
+// The CTAs without a head keep requesting the weights of the jobs ahead.
 //
 // Every wait (mbarrier, tagged word) is bounded by the device's wait limit; a wait that runs out raises
 // RCU_DEVFLAG_TIMEOUT, after which every other wait returns at once and the kernel runs to its end
@@ -35,7 +38,10 @@
 
 namespace flow {
 
-constexpr int kTileP = 16;               // cached positions per attention item
+// cached positions per attention item (K rows, then V rows, in one ring slot).  Sixteen measured faster than
+// thirty-two (fewer, larger items leave a head's warps with less to overlap).
+template <int HD> __host__ __device__ constexpr int tile_positions() { return 16; }
+constexpr int kSubP = 16;                // positions folded per pass: two lanes per position
 constexpr int kMaxRope = 256;
 constexpr int kMaxLayersShared = 48;     // layer pointer tables up to this many layers are kept in shared memory
 constexpr int kMaxDepth = ringq8::kMaxDepth;
@@ -87,14 +93,12 @@ struct Params {
     uint32_t q_off, q_per_step;          // exchange holding this rank's qkv rows
     uint32_t a_off, a_per_step;          // exchange the head outputs go to (start of the whole vector)
     int a_rank_off;                      // first element of this rank's heads in it
-    float* partial;                      // [H][max CTAs per head][HD + 2]
-    unsigned int* counters;              // [H], zero between steps
+    unsigned long long* partial;         // [H][part_stride][HD + 2] tagged 64-bit words: partial results between the CTAs of a head
     int part_stride;                     // CTAs per head the scratch is laid out for
     // ring
     int slot_bytes, depth;
-    int l2_ahead;                        // items beyond the ring the requester asks L2 for (0: none)
-    int prof_job;                        // with prof_cta: the job whose per-CTA times are recorded
-    unsigned long long* prof_cta;        // optional: [3 x grid] per CTA: job begun, input staged, items done (job prof_job)
+    int prof_job;                        // with prof_cta: the first of five consecutive jobs whose per-CTA times are recorded
+    unsigned long long* prof_cta;        // optional: [5][grid][2] per CTA: job begun, input staged
     float eps;
     unsigned long long* prof;            // optional (nullptr: off): [2 n_jobs + 1] time stamps of CTA 0 (job begun, input staged; end), then
                                          // per job kind four sums of SM clock cycles of the grid's first warp: slot wait, multiply, store, release
@@ -128,18 +132,29 @@ __device__ __forceinline__ Range gemv_range(const KindDesc& k, int warp) {      
     return Range{g0, (g1 - g0) * k.nc};
 }
 
-// warps per head; warp gw serves head gw / wph (none if that is >= H), segment gw % wph of its tiles
-template <int NW> __device__ __forceinline__ int warps_per_head(int H) { return (int)((gridDim.x * NW) / H); }
+// CTAs per head for this step's cached length, and the head (or -1) this CTA works for.
+constexpr int kTilesPerWarp = 2;
+constexpr int kMaxCtasPerHead = 8;
+template <int NW> __device__ __forceinline__ int ctas_per_head(int H, int n_tiles) {
+    const int stride = min((int)gridDim.x / H, kMaxCtasPerHead);
+    const int want = (n_tiles + NW * kTilesPerWarp - 1) / (NW * kTilesPerWarp);
+    return min(stride, max(1, want));
+}
+__device__ __forceinline__ int head_of_cta(int H, int cph) {
+    const int stride = (int)gridDim.x / H;
+    const int h = (int)blockIdx.x / stride;
+    return (h < H && (int)blockIdx.x - h * stride < cph) ? h : -1;
+}
 
 template <int NW>
 __device__ __forceinline__ Range attn_range(int H, int n_tiles, int warp, int* head) {
-    const int gw = blockIdx.x * NW + warp;
-    const int wph = warps_per_head<NW>(H);
-    const int h = gw / wph;
+    const int cph = ctas_per_head<NW>(H, n_tiles);
+    const int h = head_of_cta(H, cph);
     *head = h;
-    if (h >= H) return Range{0, 0};
-    const int s = gw - h * wph;
-    const int t0 = s * n_tiles / wph, t1 = (s + 1) * n_tiles / wph;
+    if (h < 0) return Range{0, 0};
+    const int stride = (int)gridDim.x / H;
+    const int s = ((int)blockIdx.x - h * stride) * NW + warp, n = cph * NW;      // this warp among the head's warps
+    const int t0 = s * n_tiles / n, t1 = (s + 1) * n_tiles / n;
     return Range{t0, t1 - t0};
 }
 
@@ -167,28 +182,20 @@ __device__ __forceinline__ void advance(const Params& p, const Ranges& rg, Curso
     seek(p, rg, c);
 }
 
-__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-
-// One thread: request the item at `c` into `slot` (completion on `bar`), or, with slot == nullptr, only ask L2 for it.
+// One thread: request the item at `c` into `slot` (completion on `bar`).
 template <int HD>
 __device__ __forceinline__ void issue(const Params& p, const LayerPtrs* lp, const Ranges& rg, const Cursor& c, int P, unsigned char* slot, uint64_t* bar) {
     if (c.kind == K_ATTN) {
         const int h = rg.head, kvh = h / (p.H / p.Hkv);
-        const int begin = (rg.r[K_ATTN].first + c.idx) * kTileP;
-        const int n_cached = min(kTileP, P - begin);                     // rows already in the cache (the tile may also hold position P)
+        const int begin = (rg.r[K_ATTN].first + c.idx) * tile_positions<HD>();
+        const int n_cached = min(tile_positions<HD>(), P - begin);                     // rows already in the cache (the tile may also hold position P)
         const unsigned bytes = n_cached > 0 ? (unsigned)n_cached * HD * 2u : 0u;
         const __half* kc = lp[c.li].kc + ((size_t)kvh * p.max_cache + begin) * HD;
         const __half* vc = lp[c.li].vc + ((size_t)kvh * p.max_cache + begin) * HD;
-        if (!slot) {
-            if (bytes) { l2_prefetch(kc, bytes); l2_prefetch(vc, bytes); }
-            return;
-        }
         gemvq8::mbar_expect_tx(bar, 2u * bytes);
         if (bytes) {
             gemvq8::bulk_load_1d(slot, kc, bytes, bar);
-            gemvq8::bulk_load_1d(slot + kTileP * HD * 2, vc, bytes, bar);
+            gemvq8::bulk_load_1d(slot + tile_positions<HD>() * HD * 2, vc, bytes, bar);
         }
         return;
     }
@@ -202,29 +209,19 @@ __device__ __forceinline__ void issue(const Params& p, const LayerPtrs* lp, cons
     const int sc_row = (k.kc >> 5) * p.scale_size;                  // scale bytes of one row chunk
     const size_t sc_pitch = (size_t)(k.K >> 5) * p.scale_size;      // scale bytes of a whole row
     const unsigned char* scales = reinterpret_cast<const unsigned char*>(w) + k.scales_off;
-    if (slot) gemvq8::mbar_expect_tx(bar, (unsigned)(k.unit * nr * (k.kc + sc_row)));
+    gemvq8::mbar_expect_tx(bar, (unsigned)(k.unit * nr * (k.kc + sc_row)));
     unsigned char* sdst = slot + k.unit * k.ri * k.kc;
     for (int b = 0; b < k.unit; ++b) {
         const size_t row0 = (size_t)u0 + (size_t)b * k.n_units;    // the up rows follow the gate rows
         if (k.nc == 1) {
-            if (slot) {
-                gemvq8::bulk_load_1d(slot + b * k.ri * k.kc, w + row0 * k.K, (uint32_t)(nr * k.kc), bar);
-                gemvq8::bulk_load_1d(sdst + b * k.ri * sc_row, scales + row0 * sc_pitch, (uint32_t)(nr * sc_row), bar);
-            } else {
-                l2_prefetch(w + row0 * k.K, (uint32_t)(nr * k.kc));
-                l2_prefetch(scales + row0 * sc_pitch, (uint32_t)(nr * sc_row));
-            }
+            gemvq8::bulk_load_1d(slot + b * k.ri * k.kc, w + row0 * k.K, (uint32_t)(nr * k.kc), bar);
+            gemvq8::bulk_load_1d(sdst + b * k.ri * sc_row, scales + row0 * sc_pitch, (uint32_t)(nr * sc_row), bar);
         } else {
             for (int r = 0; r < nr; ++r) {
                 const int8_t* qsrc = w + (row0 + r) * k.K + (size_t)ch * k.kc;
                 const unsigned char* ssrc = scales + (row0 + r) * sc_pitch + (size_t)ch * sc_row;
-                if (slot) {
-                    gemvq8::bulk_load_1d(slot + (b * k.ri + r) * k.kc, qsrc, (uint32_t)k.kc, bar);
-                    gemvq8::bulk_load_1d(sdst + (b * k.ri + r) * sc_row, ssrc, (uint32_t)sc_row, bar);
-                } else {
-                    l2_prefetch(qsrc, (uint32_t)k.kc);
-                    l2_prefetch(ssrc, (uint32_t)sc_row);
-                }
+                gemvq8::bulk_load_1d(slot + (b * k.ri + r) * k.kc, qsrc, (uint32_t)k.kc, bar);
+                gemvq8::bulk_load_1d(sdst + (b * k.ri + r) * sc_row, ssrc, (uint32_t)sc_row, bar);
             }
         }
     }
@@ -246,11 +243,6 @@ __device__ __forceinline__ void requester(const Params& p, const LayerPtrs* lp, 
     const int n_jobs = n_jobs_of(p);
     Cursor pc{0, 0, 0, 0};
     seek(p, rg, pc);
-    Cursor lc = pc;                                    // runs l2_ahead items ahead of pc
-    for (int i = 0; i < p.depth + p.l2_ahead && lc.job < n_jobs; ++i) {
-        if (i >= p.depth) issue<HD>(p, lp, rg, lc, P, nullptr, nullptr);
-        advance(p, rg, lc);
-    }
     int slot = 0, round = 0;
     unsigned long long t0 = 0;
     unsigned spins = 0;
@@ -260,10 +252,6 @@ __device__ __forceinline__ void requester(const Params& p, const LayerPtrs* lp, 
         if (is_free) {
             issue<HD>(p, lp, rg, pc, P, ring + (size_t)slot * p.slot_bytes, &full[slot]);
             advance(p, rg, pc);
-            if (p.l2_ahead > 0 && lc.job < n_jobs) {
-                issue<HD>(p, lp, rg, lc, P, nullptr, nullptr);
-                advance(p, rg, lc);
-            }
             if (++slot == p.depth) { slot = 0; ++round; }
             spins = 0;
             t0 = 0;
@@ -393,10 +381,12 @@ __device__ __forceinline__ void run_gemv_items(const Params& p, const Ranges& rg
 }
 
 // ------------------------------------------------------------------------------------------------
-// Attention.  Per-warp scratch in shared memory: a raw row and the rotated q, HD floats each.
+// Attention.  Per-warp scratch in shared memory: raw q / k / v rows and the rotated q, HD floats each.
 template <int HD> struct WarpAttn {
     float raw[HD];
     float q[HD];
+    float raw_k[HD];     // the new position's k and v rows (only the warp whose tiles hold that position fetches them)
+    float raw_v[HD];
 };
 // Partial result of one warp / one CTA for a head: m, l, unnormalised o.
 template <int HD> struct Part {
@@ -405,21 +395,45 @@ template <int HD> struct Part {
 };
 template <int HD, int NW> struct AttnShared {
     WarpAttn<HD> w[NW];
-    Part<HD> part[2][NW];                // [head slot of this CTA][warp]
+    Part<HD> part[NW];                   // one per warp of the CTA
 };
 
-// HD tagged words starting at word `off` -> floats in `dst` (all lanes; HD / 4 lanes carry four values each)
+// The q row and, if asked, the new k and v rows of a head at once: all words are requested before any is waited for.
 template <int HD>
-__device__ __forceinline__ void fetch_row(const Params& p, uint32_t off, uint32_t tag, float* dst) {
+__device__ __forceinline__ void fetch_qkv(const Params& p, uint32_t q_off, uint32_t k_off, uint32_t v_off, bool with_kv, uint32_t tag,
+                                          WarpAttn<HD>& wa) {
     const int lane = threadIdx.x & 31;
     if (lane < HD / 4) {
-        const uint32_t* words = p.win + off;
-        uint4 w = gemvq8::ll_load4(words + 4 * lane);
-        gemvq8::ll_wait4(words, lane, tag, p.status, w);
-        const uint2 h = gemvq8::ll_pack4(w);
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
-        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
-        dst[4 * lane] = f0.x; dst[4 * lane + 1] = f0.y; dst[4 * lane + 2] = f1.x; dst[4 * lane + 3] = f1.y;
+        const uint32_t* qw = p.win + q_off;
+        const uint32_t* kw = p.win + k_off;
+        const uint32_t* vw = p.win + v_off;
+        uint4 a = gemvq8::ll_load4(qw + 4 * lane), b = a, c = a;
+        if (with_kv) {
+            b = gemvq8::ll_load4(kw + 4 * lane);
+            c = gemvq8::ll_load4(vw + 4 * lane);
+        }
+        unsigned long long t0 = 0;
+        for (unsigned int n = 0;; ++n) {
+            const bool ra = gemvq8::ll_ready4(a, tag), rb = !with_kv || gemvq8::ll_ready4(b, tag), rc = !with_kv || gemvq8::ll_ready4(c, tag);
+            if (ra && rb && rc) break;
+            if ((n & 63u) == 63u) {
+                if (*reinterpret_cast<volatile int*>(p.status) & RCU_DEVFLAG_TIMEOUT) break;
+                const unsigned long long t = ringq8::globaltimer();
+                if (t0 == 0) t0 = t;
+                else if (t - t0 > rcu_wait_limit(p.status)) { atomicOr(p.status, RCU_DEVFLAG_TIMEOUT); break; }
+            }
+            if (!ra) a = gemvq8::ll_load4(qw + 4 * lane);
+            if (!rb) b = gemvq8::ll_load4(kw + 4 * lane);
+            if (!rc) c = gemvq8::ll_load4(vw + 4 * lane);
+        }
+        auto unpack = [&](const uint4& w, float* dst) {
+            const uint2 h = gemvq8::ll_pack4(w);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+            dst[4 * lane] = f0.x; dst[4 * lane + 1] = f0.y; dst[4 * lane + 2] = f1.x; dst[4 * lane + 3] = f1.y;
+        };
+        unpack(a, wa.raw);
+        if (with_kv) { unpack(b, wa.raw_k); unpack(c, wa.raw_v); }
     }
     __syncwarp();
 }
@@ -471,25 +485,21 @@ struct Running {
     float o0, o1, o2, o3;
 };
 
-// One landed tile (K rows then V rows in `slot`) folded into the running state.
+// Sixteen positions from `begin` of a landed tile (their K rows at Ks, V rows at Vs) folded into the running state.
 template <int HD>
-__device__ __forceinline__ void attn_tile(const Params& p, const LayerPtrs& lw, int h, int tile, int P, unsigned char* slot, WarpAttn<HD>& ws,
-                                          const float* tab, uint32_t qtag, Running& st) {
+__device__ __forceinline__ void attn_tile(const Params& p, const LayerPtrs& lw, int h, int begin, int P, __half* Ks, __half* Vs, WarpAttn<HD>& ws,
+                                          const float (&q)[HD / 2], const float* tab, Running& st) {
     const int lane = threadIdx.x & 31;
     const int group = p.H / p.Hkv, kvh = h / group;
-    const int begin = tile * kTileP;
     const int T = P + 1;
-    __half* Ks = reinterpret_cast<__half*>(slot);
-    __half* Vs = Ks + kTileP * HD;
-    if (P >= begin && P < begin + kTileP) {
+    if (P >= begin && P < begin + kSubP) {
         // this tile holds the new position: rotate k, append both rows to the cache (ops/cache.rs:73-103) and to the tile
+        // (its k and v rows were fetched with q when the job began)
         const int row = P - begin;
         const bool to_cache = h % group == 0;
-        fetch_row<HD>(p, p.q_off + (uint32_t)(p.H + kvh) * HD, qtag, ws.raw);
-        rope_row_half<HD>(ws.raw, tab, p.rope_dim, Ks + row * HD, to_cache ? lw.kc + ((size_t)kvh * p.max_cache + P) * HD : nullptr);
-        fetch_row<HD>(p, p.q_off + (uint32_t)(p.H + p.Hkv + kvh) * HD, qtag, ws.raw);
+        rope_row_half<HD>(ws.raw_k, tab, p.rope_dim, Ks + row * HD, to_cache ? lw.kc + ((size_t)kvh * p.max_cache + P) * HD : nullptr);
         for (int i = lane; i < HD; i += 32) {
-            const __half vh = __float2half_rn(ws.raw[i]);                 // exact: the value was an f16
+            const __half vh = __float2half_rn(ws.raw_v[i]);               // exact: the value was an f16
             Vs[row * HD + i] = vh;
             if (to_cache) lw.vc[((size_t)kvh * p.max_cache + P) * HD + i] = vh;
         }
@@ -500,18 +510,21 @@ __device__ __forceinline__ void attn_tile(const Params& p, const LayerPtrs& lw, 
     float dot = 0.f;
     if (begin + pos < T) {
         const uint4* kp = reinterpret_cast<const uint4*>(Ks + pos * HD + hf * (HD / 2));
-        const float* q = ws.q + hf * (HD / 2);
+        uint4 kw[HD / 16];
+#pragma unroll
+        for (int v = 0; v < HD / 16; ++v) kw[v] = kp[v];
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};            // four chains: the sum's order is fixed, whatever the head it belongs to
 #pragma unroll
         for (int v = 0; v < HD / 16; ++v) {
-            const uint4 w = kp[v];
-            const __half2* hp = reinterpret_cast<const __half2*>(&w);
+            const __half2* hp = reinterpret_cast<const __half2*>(&kw[v]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(hp[j]);
-                dot = fmaf(q[v * 8 + 2 * j], f.x, dot);
-                dot = fmaf(q[v * 8 + 2 * j + 1], f.y, dot);
+                d4[j] = fmaf(q[v * 8 + 2 * j], f.x, d4[j]);
+                d4[j] = fmaf(q[v * 8 + 2 * j + 1], f.y, d4[j]);
             }
         }
+        dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
     }
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     const float sc = begin + pos < T ? f16r(dot * p.scale) : -INFINITY;      // `.mul(scale).cast(f16)` (attn.rs:142-146)
@@ -521,9 +534,9 @@ __device__ __forceinline__ void attn_tile(const Params& p, const LayerPtrs& lw, 
     const float pe = begin + pos < T ? expf(sc - m_new) : 0.f;
     st.l = st.l * corr + 0.5f * warp_sum(pe);                                 // every position sits in two lanes
     st.o0 *= corr; st.o1 *= corr; st.o2 *= corr; st.o3 *= corr;
-    const int n = min(kTileP, T - begin);
+    const int n = min(kSubP, T - begin);
 #pragma unroll
-    for (int j = 0; j < kTileP; ++j) {
+    for (int j = 0; j < kSubP; ++j) {
         const float pj = __shfl_sync(0xffffffffu, pe, 2 * j);
         if (j < n) {
             const __half2* vr = reinterpret_cast<const __half2*>(Vs + j * HD);
@@ -552,24 +565,129 @@ __device__ __forceinline__ void write_part(Part<HD>& dst, const Running& st) {
     }
 }
 
-// One warp: merge n partial results (m, l, o[HD]; `stride` floats apart) into (M, L, o); every lane ends with its features.
-template <int HD, bool GLOBAL>
+// One warp: merge n <= MAXN partial results (m, l, o[HD]; `stride` floats apart) into (M, L, o); every lane ends
+// with its features.  All loads are requested before any is used: from global scratch each costs a trip to L2.
+template <int HD, bool GLOBAL, int MAXN>
 __device__ __forceinline__ void merge_parts(const float* parts, int n, int stride, Running& out) {
     const int lane = threadIdx.x & 31;
     auto ld = [&](const float* q) { return GLOBAL ? __ldcg(q) : *q; };
-    float M = -INFINITY;
-    for (int j = 0; j < n; ++j) M = fmaxf(M, ld(parts + (size_t)j * stride));
+    constexpr bool kWide = HD > 64;
+    const bool wide = kWide && lane < HD / 2 - 32;
+    float m[MAXN], l[MAXN], a0[MAXN], a1[MAXN], a2[MAXN], a3[MAXN];
+#pragma unroll
+    for (int j = 0; j < MAXN; ++j) {
+        m[j] = -INFINITY; l[j] = 0.f; a0[j] = a1[j] = a2[j] = a3[j] = 0.f;
+        if (j < n) {
+            const float* q = parts + (size_t)j * stride;
+            m[j] = ld(q);
+            l[j] = ld(q + 1);
+            a0[j] = ld(q + 2 + 2 * lane);
+            a1[j] = ld(q + 2 + 2 * lane + 1);
+            if (wide) {
+                a2[j] = ld(q + 2 + 64 + 2 * lane);
+                a3[j] = ld(q + 2 + 64 + 2 * lane + 1);
+            }
+        }
+    }
+    float M = m[0];
+#pragma unroll
+    for (int j = 1; j < MAXN; ++j) M = fmaxf(M, m[j]);
     Running r{M, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < n; ++j) {
-        const float* q = parts + (size_t)j * stride;
-        const float mj = ld(q);
-        const float w = mj > -INFINITY ? expf(mj - M) : 0.f;
-        r.l = fmaf(ld(q + 1), w, r.l);
-        r.o0 = fmaf(ld(q + 2 + 2 * lane), w, r.o0);
-        r.o1 = fmaf(ld(q + 2 + 2 * lane + 1), w, r.o1);
-        if (HD > 64 && lane < HD / 2 - 32) {
-            r.o2 = fmaf(ld(q + 2 + 64 + 2 * lane), w, r.o2);
-            r.o3 = fmaf(ld(q + 2 + 64 + 2 * lane + 1), w, r.o3);
+#pragma unroll
+    for (int j = 0; j < MAXN; ++j) {
+        const float w = m[j] > -INFINITY ? expf(m[j] - M) : 0.f;
+        r.l = fmaf(l[j], w, r.l);
+        r.o0 = fmaf(a0[j], w, r.o0);
+        r.o1 = fmaf(a1[j], w, r.o1);
+        r.o2 = fmaf(a2[j], w, r.o2);
+        r.o3 = fmaf(a3[j], w, r.o3);
+    }
+    out = r;
+}
+
+// A partial result as tagged 64-bit words (tag in the high half, the float's bits in the low half): an aligned
+// 8-byte store is indivisible, so a reader that finds the tag has the value.
+__device__ __forceinline__ void put64(unsigned long long* p, uint32_t tag, float v) {
+    *p = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+}
+__device__ __forceinline__ unsigned long long ld64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+template <int HD>
+__device__ __forceinline__ void put_part(unsigned long long* dst, uint32_t tag, const Running& r) {
+    const int lane = threadIdx.x & 31;
+    if (lane == 0) { put64(dst, tag, r.m); put64(dst + 1, tag, r.l); }
+    put64(dst + 2 + 2 * lane, tag, r.o0);
+    put64(dst + 2 + 2 * lane + 1, tag, r.o1);
+    if (HD > 64 && lane < HD / 2 - 32) {
+        put64(dst + 2 + 64 + 2 * lane, tag, r.o2);
+        put64(dst + 2 + 64 + 2 * lane + 1, tag, r.o3);
+    }
+}
+
+// The head's first CTA: its own partial `mine` (slot 0) merged with the partials of the head's other CTAs
+// (slots 1 .. n - 1 of `parts`), in slot order.  All words are requested together and re-requested together
+// until they carry `tag` (bounded by the device's wait limit).
+template <int HD, int MAXN>
+__device__ __forceinline__ void gather_parts(const unsigned long long* parts, int n, int stride, uint32_t tag, int* status, const Running& mine,
+                                             Running& out) {
+    const int lane = threadIdx.x & 31;
+    constexpr bool kWide = HD > 64;
+    const bool wide = kWide && lane < HD / 2 - 32;
+    unsigned long long w[MAXN][6];
+    const unsigned long long done = (unsigned long long)tag << 32;
+#pragma unroll
+    for (int j = 1; j < MAXN; ++j) {
+#pragma unroll
+        for (int e = 0; e < 6; ++e) w[j][e] = done;           // slots beyond n, and the wide features of narrow lanes, count as arrived
+    }
+    unsigned long long t0 = 0;
+    for (unsigned int it = 0;; ++it) {
+        // every word that has not arrived is requested again, all of them before any is looked at
+#pragma unroll
+        for (int j = 1; j < MAXN; ++j) {
+            if (j < n) {
+                const unsigned long long* q = parts + (size_t)j * stride;
+                if (it == 0 || (uint32_t)(w[j][0] >> 32) != tag) w[j][0] = ld64(q);
+                if (it == 0 || (uint32_t)(w[j][1] >> 32) != tag) w[j][1] = ld64(q + 1);
+                if (it == 0 || (uint32_t)(w[j][2] >> 32) != tag) w[j][2] = ld64(q + 2 + 2 * lane);
+                if (it == 0 || (uint32_t)(w[j][3] >> 32) != tag) w[j][3] = ld64(q + 2 + 2 * lane + 1);
+                if (wide && (it == 0 || (uint32_t)(w[j][4] >> 32) != tag)) w[j][4] = ld64(q + 2 + 64 + 2 * lane);
+                if (wide && (it == 0 || (uint32_t)(w[j][5] >> 32) != tag)) w[j][5] = ld64(q + 2 + 64 + 2 * lane + 1);
+            }
+        }
+        bool all = true;
+#pragma unroll
+        for (int j = 1; j < MAXN; ++j) {
+#pragma unroll
+            for (int e = 0; e < 6; ++e) all = all && (uint32_t)(w[j][e] >> 32) == tag;
+        }
+        if (__all_sync(0xffffffffu, all)) break;
+        if ((it & 63u) == 63u) {
+            if (*reinterpret_cast<volatile int*>(status) & RCU_DEVFLAG_TIMEOUT) break;
+            const unsigned long long t = ringq8::globaltimer();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > rcu_wait_limit(status)) { atomicOr(status, RCU_DEVFLAG_TIMEOUT); break; }
+        }
+    }
+    float M = mine.m;
+#pragma unroll
+    for (int j = 1; j < MAXN; ++j)
+        if (j < n) M = fmaxf(M, __uint_as_float((uint32_t)w[j][0]));
+    const float w0 = mine.m > -INFINITY ? expf(mine.m - M) : 0.f;
+    Running r{M, mine.l * w0, mine.o0 * w0, mine.o1 * w0, mine.o2 * w0, mine.o3 * w0};
+#pragma unroll
+    for (int j = 1; j < MAXN; ++j) {
+        if (j < n) {
+            const float mj = __uint_as_float((uint32_t)w[j][0]);
+            const float wj = mj > -INFINITY ? expf(mj - M) : 0.f;
+            r.l = fmaf(__uint_as_float((uint32_t)w[j][1]), wj, r.l);
+            r.o0 = fmaf(__uint_as_float((uint32_t)w[j][2]), wj, r.o0);
+            r.o1 = fmaf(__uint_as_float((uint32_t)w[j][3]), wj, r.o1);
+            r.o2 = fmaf(__uint_as_float((uint32_t)w[j][4]), wj, r.o2);
+            r.o3 = fmaf(__uint_as_float((uint32_t)w[j][5]), wj, r.o3);
         }
     }
     out = r;
@@ -643,6 +761,81 @@ struct TaggedSource {
     }
 };
 
+// Activation vector of a GEMV job -> planes (waits for the words still in flight).
+template <int NT>
+__device__ __forceinline__ void stage_job(const Params& p, const KindDesc& k, const float* gamma, uint32_t tag, unsigned char* planes, float* scratch) {
+    const TaggedSource src{p.win + k.in_off, tag, p.status};
+    if (k.rms) {
+        ringq8::RmsPlanes<TaggedSource, NT> pro{src, gamma, p.eps};
+        pro.stage(planes, k.K, scratch);
+    } else {
+        ringq8::PlainPlanes<TaggedSource, NT> pro{src};
+        pro.stage(planes, k.K, scratch);
+    }
+}
+
+// The attention job of one consumer warp whose CTA works for head `h`: its run of tiles folded with an online
+// softmax, then the merges that end with the head's output published.  Kept out of line: it runs once per
+// layer and would otherwise claim registers in the GEMV item loops.
+template <int HD, int NW>
+__device__ __noinline__ WarpState attention_job(const Params& p, const LayerPtrs& lw, const Ranges& rg, WarpState ws, int li, int j, int P, int n_tiles,
+                                                unsigned step, unsigned char* ring, uint64_t* full, uint64_t* empty, AttnShared<HD, NW>* ash,
+                                                const float* tab) {
+    constexpr int NT = NW * 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = rg.head;
+    Running st{-INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (rg.r[K_ATTN].count > 0) {
+        const uint32_t qtag = make_tag(step, p.q_per_step, (uint32_t)li);
+        WarpAttn<HD>& wa = ash->w[warp];
+        const int tile_p = P / tile_positions<HD>(), kvh = h / (p.H / p.Hkv);
+        const bool owns_new = rg.r[K_ATTN].first <= tile_p && tile_p < rg.r[K_ATTN].first + rg.r[K_ATTN].count;
+        fetch_qkv<HD>(p, p.q_off + (uint32_t)h * HD, p.q_off + (uint32_t)(p.H + kvh) * HD, p.q_off + (uint32_t)(p.H + p.Hkv + kvh) * HD, owns_new, qtag, wa);
+        rope_row<HD>(wa.raw, tab, p.rope_dim, wa.q);
+        float q[HD / 2];                                // this lane's half of the rotated q
+#pragma unroll
+        for (int i = 0; i < HD / 2; ++i) q[i] = wa.q[(lane & 1) * (HD / 2) + i];
+        while (ws.cc.job == j) {
+            if (ws.alive && !ringq8::ring_wait(&full[ws.slot], ws.parity, p.status)) ws.alive = false;
+            if (ws.alive) {
+                const int begin = (rg.r[K_ATTN].first + ws.cc.idx) * tile_positions<HD>();
+                __half* Ks = reinterpret_cast<__half*>(ring + (size_t)ws.slot * p.slot_bytes);
+                __half* Vs = Ks + tile_positions<HD>() * HD;
+#pragma unroll
+                for (int sub = 0; sub < tile_positions<HD>() / kSubP; ++sub)
+                    if (begin + sub * kSubP <= P) attn_tile<HD>(p, lw, h, begin + sub * kSubP, P, Ks + sub * kSubP * HD, Vs + sub * kSubP * HD, wa, q, tab, st);
+            }
+            release_slot(p, rg, ws, empty);
+        }
+    }
+    if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j + 1] = ringq8::globaltimer();     // warp 0's tiles are folded
+    if (p.prof_cta && tid == 0 && j >= p.prof_job && j < p.prof_job + 5)
+        p.prof_cta[((j - p.prof_job) * gridDim.x + blockIdx.x) * 2 + 1] = ringq8::globaltimer();
+    // ---- the warps of the CTA merge through shared memory
+    write_part<HD>(ash->part[warp], st);
+    ringq8::stage_barrier<NT>();
+    if (warp != 0) return ws;
+    constexpr int kStride = (int)(sizeof(Part<HD>) / sizeof(float));
+    const uint32_t atag = make_tag(step, p.a_per_step, (uint32_t)li);
+    Running r;
+    merge_parts<HD, false, NW>(&ash->part[0].m, NW, kStride, r);
+    const int cph = ctas_per_head<NW>(p.H, n_tiles);
+    const int cta_first = h * ((int)gridDim.x / p.H);
+    unsigned long long* head_parts = p.partial + (size_t)h * p.part_stride * kStride;
+    if (cph == 1) {
+        publish_head<HD>(p, h, r, atag);
+    } else if ((int)blockIdx.x != cta_first) {
+        // ---- the other CTAs of the head hand their partial result to the head's first CTA: every float
+        // travels with the exchange's tag in one 64-bit word, so there is no fence and no counter
+        put_part<HD>(head_parts + (size_t)(blockIdx.x - cta_first) * kStride, atag, r);
+    } else {
+        Running all;
+        gather_parts<HD, kMaxCtasPerHead>(head_parts, cph, kStride, atag, p.status, r, all);
+        publish_head<HD>(p, h, all, atag);
+    }
+    return ws;
+}
+
 template <int HD, class ScaleT, int NW>
 __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __grid_constant__ Params p, int kmax) {
     constexpr int NT = NW * 32;                      // consumer threads
@@ -659,7 +852,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __g
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int P = (int)*p.d_pos;
-    const int n_tiles = (P + 1 + kTileP - 1) / kTileP;
+    const int n_tiles = (P + 1 + tile_positions<HD>() - 1) / tile_positions<HD>();
     const unsigned step = *p.d_step;
     const int n_jobs = n_jobs_of(p);
     if (warp < NW && lane == 0) {
@@ -694,16 +887,13 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __g
     ws.slot = 0;
     ws.parity = 0;
     ws.alive = true;
-    const int wph = warps_per_head<NW>(p.H);
     for (int j = 0; j < n_jobs; ++j) {
         int li, kind;
         split_job(p, j, li, kind);
         ringq8::stage_barrier<NT>();                       // the planes and the attention scratch of job j - 1 are free again
         if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j] = ringq8::globaltimer();
-        if (p.prof_cta && tid == 0) {
-            if (j == p.prof_job) p.prof_cta[3 * blockIdx.x] = ringq8::globaltimer();
-            if (j == p.prof_job + 1) p.prof_cta[3 * blockIdx.x + 2] = ringq8::globaltimer();
-        }
+        if (p.prof_cta && tid == 0 && j >= p.prof_job && j < p.prof_job + 5)
+            p.prof_cta[((j - p.prof_job) * gridDim.x + blockIdx.x) * 2] = ringq8::globaltimer();
         if (kind != K_ATTN) {
             const KindDesc& k = p.kd[kind];
             // the residuals of this warp's units (final since the job before last): lane i, unit i of the warp
@@ -713,18 +903,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __g
                 if (u < k.n_units) resv = __half2float(__ushort_as_half((unsigned short)(__ldcg(p.win + k.res_off + u) & 0xFFFFu)));
             }
             // ---- activation vector -> planes (waits for the words still in flight)
-            const TaggedSource src{p.win + k.in_off, make_tag(step, k.in_per_step, (uint32_t)(li * k.in_mul + k.in_add)), p.status};
-            if (k.rms) {
-                const float* gamma = kind == K_HEAD ? p.out_norm : (kind == K_QKV ? lp[li].attn_norm : lp[li].ffn_norm);
-                ringq8::RmsPlanes<TaggedSource, NT> pro{src, gamma, p.eps};
-                pro.stage(planes, k.K, scratch);
-            } else {
-                ringq8::PlainPlanes<TaggedSource, NT> pro{src};
-                pro.stage(planes, k.K, scratch);
-            }
+            const float* gamma = !k.rms ? nullptr : (kind == K_HEAD ? p.out_norm : (kind == K_QKV ? lp[li].attn_norm : lp[li].ffn_norm));
+            stage_job<NT>(p, k, gamma, make_tag(step, k.in_per_step, (uint32_t)(li * k.in_mul + k.in_add)), planes, scratch);
             ringq8::stage_barrier<NT>();
             if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j + 1] = ringq8::globaltimer();
-            if (p.prof_cta && tid == 0 && j == p.prof_job) p.prof_cta[3 * blockIdx.x + 1] = ringq8::globaltimer();
+            if (p.prof_cta && tid == 0 && j >= p.prof_job && j < p.prof_job + 5)
+                p.prof_cta[((j - p.prof_job) * gridDim.x + blockIdx.x) * 2 + 1] = ringq8::globaltimer();
             if (ws.cc.job != j) continue;
             const Out out = make_out(p, k.out_off, k.push != 0, make_tag(step, k.out_per_step, (uint32_t)(li * k.out_mul + k.out_add)), kind);
             switch (k.unit * 8 + k.ri) {
@@ -736,64 +920,12 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __g
             }
             continue;
         }
-        // ---- attention: this warp's run of tiles of one head, folded with an online softmax
-        const int h = rg.head;
-        Running st{-INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (rg.r[K_ATTN].count > 0) {
-            const uint32_t qtag = make_tag(step, p.q_per_step, (uint32_t)li);
-            WarpAttn<HD>& wa = ash->w[warp];
-            fetch_row<HD>(p, p.q_off + (uint32_t)h * HD, qtag, wa.raw);
-            rope_row<HD>(wa.raw, tab, p.rope_dim, wa.q);
-            while (ws.cc.job == j) {
-                if (ws.alive && !ringq8::ring_wait(&full[ws.slot], ws.parity, p.status)) ws.alive = false;
-                if (ws.alive)
-                    attn_tile<HD>(p, lp[li], h, rg.r[K_ATTN].first + ws.cc.idx, P, ring + (size_t)ws.slot * p.slot_bytes, wa, tab, qtag, st);
-                release_slot(p, rg, ws, empty);
-            }
+        // ---- attention: CTAs that work for a head fold its tiles and merge; the others go on (their requester keeps asking for weights)
+        if (rg.head < 0) {
+            if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j + 1] = ringq8::globaltimer();
+            continue;
         }
-        if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j + 1] = ringq8::globaltimer();     // warp 0's tiles are folded
-        // ---- the warps of a head inside this CTA merge through shared memory (a CTA holds warps of at most two heads)
-        const int h_first = (blockIdx.x * NW) / wph;
-        if (h < p.H) write_part<HD>(ash->part[h - h_first][warp], st);
-        ringq8::stage_barrier<NT>();
-        if (warp < 2) {
-            const int hh = h_first + warp;
-            const int gw0 = blockIdx.x * NW;
-            const int w0 = max(hh * wph, gw0) - gw0, w1 = min((hh + 1) * wph, gw0 + NW) - gw0;
-            if (hh < p.H && w1 > w0) {
-                constexpr int kStride = (int)(sizeof(Part<HD>) / sizeof(float));
-                const uint32_t atag = make_tag(step, p.a_per_step, (uint32_t)li);
-                Running r;
-                merge_parts<HD, false>(&ash->part[warp][w0].m, w1 - w0, kStride, r);
-                const int cta_first = (hh * wph) / NW, cta_last = ((hh + 1) * wph - 1) / NW;
-                const int n_ctas = cta_last - cta_first + 1;
-                if (n_ctas == 1) {
-                    publish_head<HD>(p, hh, r, atag);
-                } else {
-                    // ---- the CTAs of a head merge through global scratch; the last one to arrive publishes
-                    float* mine = p.partial + ((size_t)hh * p.part_stride + (blockIdx.x - cta_first)) * kStride;
-                    if (lane == 0) { mine[0] = r.m; mine[1] = r.l; }
-                    mine[2 + 2 * lane] = r.o0;
-                    mine[2 + 2 * lane + 1] = r.o1;
-                    if (HD > 64 && lane < HD / 2 - 32) {
-                        mine[2 + 64 + 2 * lane] = r.o2;
-                        mine[2 + 64 + 2 * lane + 1] = r.o3;
-                    }
-                    __threadfence();
-                    __syncwarp();
-                    unsigned int ticket = 0;
-                    if (lane == 0) ticket = atomicAdd(&p.counters[hh], 1u);
-                    ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                    if (ticket == (unsigned int)n_ctas - 1) {
-                        __threadfence();
-                        Running all;
-                        merge_parts<HD, true>(p.partial + (size_t)hh * p.part_stride * kStride, n_ctas, kStride, all);
-                        publish_head<HD>(p, hh, all, atag);
-                        if (lane == 0) p.counters[hh] = 0;       // ready for the next layer
-                    }
-                }
-            }
-        }
+        ws = attention_job<HD, NW>(p, lp[li], rg, ws, li, j, P, n_tiles, step, ring, full, empty, ash, tab);
     }
     if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * n_jobs] = ringq8::globaltimer();
 }

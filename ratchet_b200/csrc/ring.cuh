@@ -414,8 +414,9 @@ struct Geometry { int slot_bytes, depth; size_t smem; };
 inline bool geometry(const rcu_device* dev, const Job& job, int unit, Geometry* g) {
     const int slot = (item_bytes(job, unit) + 127) & ~127;
     const size_t fixed = kBarBytes + planes_bytes(job.K) + 8 * sizeof(float) + 128;
-    if (fixed + (size_t)kWarps * 2 * slot > (size_t)dev->smem_optin) return false;
-    int depth = (int)(((size_t)dev->smem_optin - fixed) / ((size_t)kWarps * slot));
+    const size_t budget = (size_t)dev->smem_optin - 256;          // an epilogue may keep a few words of static shared memory
+    if (fixed + (size_t)kWarps * 2 * slot > budget) return false;
+    int depth = (int)((budget - fixed) / ((size_t)kWarps * slot));
     if (depth > kMaxDepth) depth = kMaxDepth;
     g->slot_bytes = slot;
     g->depth = depth;
@@ -449,7 +450,7 @@ rcu_status launch(rcu_device* dev, const int8_t* qs, const void* scales, const P
     case RI_: {                                                                                                         \
         if constexpr (RI_ * UNIT <= 4) {                                                                                \
             auto kern = gemv_q8_ring_kernel<ScaleT, RI_, Prologue, Epilogue>;                                           \
-            RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dev->smem_optin));     \
+            RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)geo.smem));       \
             RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, kern, job, pro, epi, geo.slot_bytes, geo.depth, dev->d_status));     \
         }                                                                                                               \
         break;                                                                                                          \

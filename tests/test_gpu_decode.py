@@ -170,3 +170,35 @@ def test_decoder_greedy_loop_on_device(dev):
         dev_tokens.append(int(b.next_token.to_numpy()[0]))
     assert dev_tokens == host_tokens
     assert a.position == b.position == 11
+
+
+def test_decoder_kernel_per_phase_fallback(dev):
+    """A model whose rows are not whole 256-element runs (d_model 480 = 5 heads of 96) cannot use the rings of
+    the data-flow kernel: the decoder keeps the kernel-per-phase step (five kernels per layer), with the same
+    results against the oracle's graph."""
+    W = mb.phi3_weights(21, n_layers=2, d=480, n_heads=5, ffn=1024, vocab=2048, quant="q8h")
+    ref_model = mb.phi3_model(OTensor, None, W, 70, np.float16, max_cache=128)
+    dec = mb.phi3_decoder(dev, W, 70, max_cache=128)
+    tok = 3
+    for step in range(3):
+        ref = ref_model.schedule(OTensor.from_data(np.array([[tok]], np.int32))).full().to_numpy().reshape(-1)
+        ref_model.kv_cache.update(1)
+        got = dec.step(tok).astype(np.float32).reshape(-1)
+        assert rel_err(got, ref) < 1e-2, f"step {step}"
+        tok = int(ref.argmax())
+    assert dec.kernels_per_step == 2 + 5 * 2 + 2
+    with pytest.raises(Exception):
+        dec.profile_step()              # per-job time stamps exist only for the data-flow kernel
+
+
+def test_decoder_profile_step_reports_every_job(dev):
+    W = mb.phi3_weights(4, n_layers=2, d=512, n_heads=8, ffn=1024, vocab=4096, quant="q8h")
+    dec = mb.phi3_decoder(dev, W, 5, max_cache=64)
+    assert dec.kernels_per_step in (0, 5)
+    dev.h2d(dec.token.ptr, np.array([11], np.int32))
+    stamps = dec.profile_step()
+    n_jobs = 5 * 2 + 1
+    assert stamps.size == 2 * n_jobs + 1 + 24
+    t = stamps[: 2 * n_jobs + 1].astype(np.int64)
+    assert (np.diff(t) >= 0).all() and t[-1] > t[0]          # one clock, in job order
+    assert dec.position == 6
