@@ -539,6 +539,72 @@ def phi3_decode_bench(dev, torch, stream, steps, warmup, rank=0, world=1, dist=N
     return res
 
 
+def sharded_decode_check(dev, torch, rank, world, dist):
+    """Two Phi-3-mini layers at full width, three greedy steps: the sharded decoder's logits must equal the
+    single-GPU decoder's bit for bit on every rank (each output element is computed by one rank with the
+    single-GPU arithmetic).  Run outside every timed region."""
+    from ratchet_b200 import capi
+    from ratchet_b200.comm import Comm, decoder_shard_ranges, take_rows_q8
+    from ratchet_b200.decoder import Decoder, DecoderConfig, DecoderLayer
+    c = PHI3
+    d, H, hd, ffn, V, L, prior, cache = c["d"], c["n_heads"], c["head_dim"], c["ffn"], c["vocab"], 2, c["kv_prior"], 2048
+    R = decoder_shard_ranges(H, H, hd, d, ffn, V, rank, world)
+    rows = lambda key: sum(b - a for a, b in R[key])
+    rng = np.random.Generator(np.random.PCG64(77))
+    ones = np.ones(d, np.float32)
+    full = {"qkv": (3 * d, d), "o": (d, d), "gate_up": (2 * ffn, d), "down": (d, ffn)}
+    host = [{k: _q8h_weights(n, kk, 900 + 10 * li + i) for i, (k, (n, kk)) in enumerate(full.items())} for li in range(L)]
+    kv = rng.standard_normal((L, 2, H, prior, hd)).astype(np.float16)
+    emb_h, head_h = _q8h_weights(V, d, 990), _q8h_weights(V, d, 991)
+    h0, h1 = R["kv_heads"]
+
+    def build(sharded, comm):
+        layers = []
+        for li in range(L):
+            w = {}
+            for k, (n, kk) in full.items():
+                if sharded:
+                    w[k] = dev.from_quantized(take_rows_q8(host[li][k], capi.Q8_0H, n, kk, R[k]), capi.Q8_0H, (rows(k), kk))
+                else:
+                    w[k] = dev.from_quantized(host[li][k], capi.Q8_0H, (n, kk))
+            heads = slice(h0, h1) if sharded else slice(0, H)
+            kc = np.zeros((heads.stop - heads.start, cache, hd), np.float16)
+            vc = np.zeros_like(kc)
+            kc[:, :prior] = kv[li, 0, heads]
+            vc[:, :prior] = kv[li, 1, heads]
+            layers.append(DecoderLayer(dev.from_numpy(ones), w["qkv"], w["o"], dev.from_numpy(ones), w["gate_up"], w["down"],
+                                       dev.from_numpy(kc), dev.from_numpy(vc)))
+        head = dev.from_quantized(take_rows_q8(head_h, capi.Q8_0H, V, d, R["lm_head"]), capi.Q8_0H, (rows("lm_head"), d)) if sharded \
+            else dev.from_quantized(head_h, capi.Q8_0H, (V, d))
+        cfg = DecoderConfig(L, d, H, H, hd, ffn, V, cache, hd, 10000.0, 1e-5, capi.Q8_0H)
+        dec = Decoder(dev, cfg, layers, dev.from_quantized(emb_h, capi.Q8_0H, (V, d)), dev.from_numpy(ones), head, comm=comm)
+        dec.position = prior
+        return dec
+
+    def run(dec):
+        out = []
+        dev.h2d(dec.token.ptr, np.array([1234], np.int32))
+        for i in range(3):
+            dec.step_device(dec.token.ptr if i == 0 else dec.next_token.ptr)
+            dev.sync()
+            out.append(dec.logits.to_numpy().copy())
+        return out
+
+    single = build(False, None)
+    ref = run(single)
+    single.close()
+    comm = Comm(dev, rank, world, max(d, ffn, V, H * hd), bytes_per_elem=4)
+    shard = build(True, comm)
+    got = run(shard)
+    same = all(np.array_equal(a.view(np.uint16), b.view(np.uint16)) for a, b in zip(got, ref))
+    flag = torch.tensor([1 if same else 0], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.barrier()
+    shard.close()
+    comm.close()
+    return {"sharded_logits_equal_single_gpu_bits": bool(int(flag.item())), "layers": L, "steps": 3, "ranks": world}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -569,9 +635,15 @@ def run_ours(args):
     x_dev.copy_(x_host)
     y_full = torch.empty((1, N), dtype=torch.float16, device="cuda")      # gathered output
     y_local = y_full[:, rank * n_local:(rank + 1) * n_local] if world == 1 else torch.empty((1, n_local), dtype=torch.float16, device="cuda")
-    y_host = torch.empty((1, N), dtype=torch.float16).pin_memory()
+    y_host = torch.empty((2, N), dtype=torch.float16).pin_memory()          # results of two steps in flight
     bx = dev.wrap(capi.F16, (1, K), x_dev.data_ptr())
     by = dev.wrap(capi.F16, (1, n_local), y_local.data_ptr())
+    y_alt = torch.empty((1, n_local), dtype=torch.float16, device="cuda")    # N = 1: second output buffer for the end-to-end loop
+    by_alt = dev.wrap(capi.F16, (1, n_local), y_alt.data_ptr())
+    # a second handle of the library on a stream of its own carries the device-to-host copies, so that the copy of
+    # one step's result overlaps the next step's kernel
+    copy_stream = torch.cuda.Stream()
+    dev_copy = Device(local_rank, stream=copy_stream.cuda_stream)
 
     comm = None
     if world > 1:
@@ -589,12 +661,27 @@ def run_ours(args):
 
     x_host_np = x_host.numpy()
 
-    def step_e2e():
-        # host buffers in and out through the C ABI: rcu_h2d (asynchronous on the device's stream, pinned
-        # source), the GEMV, rcu_d2h (blocks until the result is in host memory)
+    def step_e2e(i):
+        # Host buffers in and out through the C ABI, every step: rcu_h2d of the activation (pinned source), the
+        # GEMV, and rcu_d2h_async of the whole result on the copy handle behind rcu_stream_wait.  The kernel of
+        # step i + 2 is ordered after the copy of step i: the gathered output rotates through three slots (two
+        # buffers at N = 1), so a slot is never rewritten while its copy is in flight.
+        if i >= 2:
+            dev.wait_for(dev_copy)             # copies up to step i - 1 are queued there; the copy of step i - 2 is what matters
         dev.h2d(bx.ptr, x_host_np, K * 2)
-        out = step()
-        dev.d2h(y_host_np, by.ptr if out is None else out.ptr, N * 2)
+        if comm is None:
+            out = by if i % 2 == 0 else by_alt
+            dev.matmul(dw, bx, None, False, True, True, out=out)
+        else:
+            out = comm.linear(dw, bx, N)
+        dev_copy.wait_for(dev)
+        dev_copy.d2h_async(y_host_np[i % 2], out.ptr, N * 2)
+
+    def run_e2e(n):
+        for i in range(n):
+            step_e2e(i)
+        dev_copy.sync()
+        dev.sync()
 
     def barrier():
         if world > 1:
@@ -609,28 +696,59 @@ def run_ours(args):
         sampler.start()
     launches0 = dev.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph = None
+    if world > 1:
+        # the K steps as one captured CUDA graph: eight Python processes launching step by step would put
+        # their host skew inside every step's peer wait
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(args.steps):
+                step()
+        barrier()
+        graph.replay()                      # one untimed replay: first-use costs of the instantiated graph
     barrier()
     mark0 = sampler.mark()
     ev0.record(stream)
-    for _ in range(args.steps):
-        step()
+    if graph is not None:
+        graph.replay()
+    else:
+        for _ in range(args.steps):
+            step()
     ev1.record(stream)
     barrier()
     mark1 = sampler.mark()
     ms = ev0.elapsed_time(ev1)
-    launches = dev.launches - launches0
+    launches = (dev.launches - launches0) if graph is None else args.steps
     # Every step is exactly one launch of the GEMV kernel (at N > 1 the same kernel also pushes its slice to
     # the peers and waits for theirs), so the kernel's average launch duration is the timed region / steps.
     kernel_ms = ms / args.steps
     # end to end: host activation in, host result out, every step
-    for _ in range(3):
-        step_e2e()
+    run_e2e(4)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_e2e()
+    run_e2e(args.steps)
     barrier()
     e2e_s = (time.perf_counter() - t0) / args.steps
+
+    # The collective this fused gather replaces, on the same box: the plain GEMV into a local buffer, then
+    # torch.distributed's NCCL all-gather of the f16 slices (a reported comparison, not the product path).
+    nccl = None
+    if world > 1:
+        y_gather = torch.empty((1, N), dtype=torch.float16, device="cuda")
+
+        def step_nccl():
+            dev.matmul(dw, bx, None, False, True, True, out=by)
+            dist.all_gather_into_tensor(y_gather, y_local)
+        for _ in range(5):
+            step_nccl()
+        barrier()
+        n0, n1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0.record(stream)
+        for _ in range(args.steps):
+            step_nccl()
+        n1.record(stream)
+        barrier()
+        nccl_ms = n0.elapsed_time(n1) / args.steps
     clocks = sampler.stop(mark0, max(mark1, mark0 + 1)) if rank == 0 else None
 
     # What was timed is checked, outside the timed region: one more step, the gathered output of all ranks
@@ -649,10 +767,10 @@ def run_ours(args):
             parity = parity_report(y_all.astype(np.float32), ref_all, rtol=1e-2, atol=1e-2 * float(np.sqrt(np.mean(ref * ref))))
             parity["against"] = "CPU oracle (dequantise + f32 matmul), every output row of every rank"
 
-    t = torch.tensor([ms, kernel_ms, e2e_s], dtype=torch.float64, device="cuda")
+    t = torch.tensor([ms, kernel_ms, e2e_s, nccl_ms if world > 1 else 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, kernel_ms, e2e_s = (float(v) for v in t.tolist())
+    ms, kernel_ms, e2e_s, nccl_ms = (float(v) for v in t.tolist())
     ms_per_step = ms / args.steps
     total_bytes = gemv_bytes(N, K)
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
@@ -669,15 +787,19 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "K": K, "N": N, "rows_per_gpu": n_local, "parallelism": f"row-shard x{world}, all-gather fused into the GEMV (peer stores over NVLink)" if world > 1 else "single GPU",
                        "l2": "weights per GPU exceed L2 (126 MB) at every N <= 8; no flush"},
             "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": N * 2,
-                    "note": "weights stay resident (loaded once, as ratchet loads a model); activation H2D and result D2H each step"},
+                    "note": "weights stay resident (loaded once, as ratchet loads a model); activation rcu_h2d and result rcu_d2h_async every step, "
+                            "the copy of step i overlapping the kernel of step i + 1 (second library handle on a copy stream)"},
             "gpu_launches": int(launches),
             "parity": parity,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "gemv_q8_kernel",
+                         "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "gemv_q8_ring_kernel",
                          "kernel_ms": kernel_ms, "bytes_per_launch": local_bytes, "traffic": None},
         }
         line["roofline"]["traffic"] = GEMV_TRAFFIC_PER_ROW_BYTES * n_local
+        if world > 1:
+            line["nccl_allgather_baseline"] = {"ms_per_step": nccl_ms, "gbs": total_bytes / (nccl_ms * 1e-3) / 1e9,
+                                               "what": "plain GEMV on the shard + torch.distributed all_gather_into_tensor (NCCL) of the f16 slices, same stream, un-graphed"}
         if world == 1 and not args.rows:
             line["cpu_baseline"] = cpu_baseline_sample(K, N)
     # release the GEMV weights before the other legs allocate theirs
@@ -702,14 +824,17 @@ def run_ours(args):
             dist.barrier()
             comm.close()
             comm = None
+        check = sharded_decode_check(dev, torch, rank, world, dist)
         extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3), rank=rank,
                                                   world=world, dist=dist)
+        extras["phi3_decode"]["parity"] = check
     if rank == 0:
         line.update(extras)
         print(json.dumps(line))
     if comm is not None:
         dist.barrier()
         comm.close()
+    dev_copy.close()
     dev.close()
     if world > 1:
         dist.destroy_process_group()

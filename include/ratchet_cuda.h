@@ -113,6 +113,13 @@ void rcu_pool_stats(rcu_device* dev, uint64_t* in_use, uint64_t* reserved);
  * asynchronous: the source must stay untouched until the next rcu_sync / rcu_d2h on this device. */
 rcu_status rcu_h2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
 rcu_status rcu_d2h(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
+/* d2h without the wait: `dst` should be pinned memory and is valid after the next rcu_sync / rcu_d2h on this
+ * handle.  With a second handle on a stream of its own (rcu_device_create_on_stream) and rcu_stream_wait, the
+ * copy of one step's result overlaps the next step's kernels. */
+rcu_status rcu_d2h_async(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
+/* Work queued on `dev` after this call starts only when everything queued on `other` (same GPU) so far has
+ * finished.  Does not block the host. */
+rcu_status rcu_stream_wait(rcu_device* dev, rcu_device* other);
 rcu_status rcu_d2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes);
 rcu_status rcu_memset(rcu_device* dev, void* dst, int value, uint64_t nbytes);
 /* device.poll(Wait) (tensor.rs:856).  Also reports what kernels flagged since the last check:
@@ -342,12 +349,14 @@ rcu_status rcu_attn_decode_static(rcu_device* dev, const void* qkv, void* k_cach
 /* ------------------------------------------------------------------ row-sharded Linear over the GPUs of a node
  * No counterpart in the reference, which is single-device (gpu/device.rs:15-16).  A Linear's weight
  * W[N,K] (ratchet-nn/src/linear.rs:17-24) is split by rows: rank r of g holds rows [r N/g, (r+1) N/g)
- * as its own ratchet Q8_0 buffer.  One process per GPU; each creates a window (two full-size f16
- * output slots + flags), exports it as a 64-byte CUDA IPC handle, the host framework exchanges the
- * handles, and every rank imports its peers'.  rcu_gemv_q8_allgather runs the local GEMV; its last
- * CTA stores the output slice into every peer's window over NVLink and raises their flags, then this
- * rank waits (bounded: RCU_ERR_TIMEOUT at the next sync) for its peers' slices.  *y_full is the
- * device pointer of the gathered f16 [N] output, valid until the call after next. */
+ * as its own ratchet Q8_0 buffer.  One process per GPU; each creates a window (full-size f16 output slots,
+ * arrival counters), exports it as a 64-byte CUDA IPC handle, the host framework exchanges the handles, and every
+ * rank imports its peers'.  rcu_gemv_q8_allgather runs the local GEMV; each warp stores its finished rows into
+ * every peer's window over NVLink as it goes, each CTA then counts itself in on every peer, and the kernel ends
+ * once every peer's CTAs have arrived here (bounded: RCU_ERR_TIMEOUT at the next sync).  Every rank must call with
+ * shards of the same shape.  *y_full is the device pointer of the gathered f16 [N] output, valid until the call
+ * after next.  The kernel is launched so that it may begin requesting weights while the previous kernel on the
+ * stream is still finishing: a weight shard produced on the device must be complete (rcu_sync) before the call. */
 rcu_status rcu_comm_create(rcu_device* dev, int rank, int world, uint64_t slot_bytes, rcu_comm** out);
 rcu_status rcu_comm_export(rcu_comm* comm, void* handle64);
 rcu_status rcu_comm_import(rcu_comm* comm, int peer, const void* handle64);

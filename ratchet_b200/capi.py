@@ -89,6 +89,8 @@ SIGNATURES = {
     "rcu_pool_stats": (None, [_DEV, _u64p, _u64p]),
     "rcu_h2d": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
     "rcu_d2h": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "rcu_d2h_async": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "rcu_stream_wait": (C.c_int, [_DEV, _DEV]),
     "rcu_d2d": (C.c_int, [_DEV, C.c_void_p, C.c_void_p, C.c_uint64]),
     "rcu_memset": (C.c_int, [_DEV, C.c_void_p, C.c_int, C.c_uint64]),
     "rcu_sync": (C.c_int, [_DEV]),

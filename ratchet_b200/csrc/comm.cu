@@ -115,8 +115,8 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
     gemvq8::GatherEpilogueH epi;
     epi.bias = bias_shard ? (const __half*)bias_shard->data : nullptr;
     epi.y_local = reinterpret_cast<__half*>(c->local.slot(slot)) + (size_t)c->rank * n_local;
-    epi.ticket = c->local.ticket(c->world, 0);
-    epi.uses = c->local.ticket(c->world, 1 + slot);
+    epi.ticket = c->local.ticket(c->world, slot);           // per slot: the next call's CTAs may start (and count) while this call's last CTA still waits
+    epi.uses = c->local.ticket(c->world, 3 + slot);
     epi.n_peers = 0;
     for (int p = 0; p < c->world; ++p) {
         if (p == c->rank) continue;
@@ -135,8 +135,10 @@ rcu_status rcu_gemv_q8_allgather(rcu_comm* c, const rcu_tensor* w_shard, const r
     rcu_status st = RCU_ERR_UNSUPPORTED;
     if (K >= 2048) {
         ringq8::PlainPlanes<ringq8::VecSource> rpro{{(const __half*)x->data}};
-        st = w_shard->dt == RCU_Q8_0H ? ringq8::launch<__half>(dev, qs, sc, rpro, epi, (int)n_local, (int)K, false)
-                                      : ringq8::launch<float>(dev, qs, sc, rpro, epi, (int)n_local, (int)K, false);
+        // Programmatic dependent launch: until griddepcontrol.wait the kernel only requests weights into its rings, so
+        // its start overlaps the previous call's wait for the peers.
+        st = w_shard->dt == RCU_Q8_0H ? ringq8::launch<__half>(dev, qs, sc, rpro, epi, (int)n_local, (int)K, true)
+                                      : ringq8::launch<float>(dev, qs, sc, rpro, epi, (int)n_local, (int)K, true);
     }
     if (st == RCU_ERR_UNSUPPORTED) {
         gemvq8::PlainPrologue<__half> pro{(const __half*)x->data};

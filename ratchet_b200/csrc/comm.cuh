@@ -1,7 +1,7 @@
 // Peer-mapped exchange windows shared by the sharded GEMV entry point and the sharded decoder.
 //
 // One process per GPU.  Each rank allocates one window: kSlots full-size slots followed by an array of
-// `world` arrival counters per slot and four more words (a ticket and the use counts of the GEMV's three
+// `world` arrival counters per slot and eight more words (the tickets and the use counts of the GEMV's three
 // slots).  Windows are exported as CUDA IPC handles, exchanged by the host framework, and opened by every
 // peer.  Data moves with plain peer stores issued by the producing GPU into the consumer's own HBM (all
 // later reads are local).  The row-sharded GEMV signals completion with system-scope release increments
@@ -19,7 +19,7 @@ struct Window {
     char* slot(int s) const { return base + (size_t)s * slot_bytes; }
     unsigned int* flags(int s, int world) const { return reinterpret_cast<unsigned int*>(base + kSlots * slot_bytes) + (size_t)s * world; }
     unsigned int* ticket(int world, int which = 0) const { return flags(kSlots, world) + which; }
-    static size_t bytes(size_t slot_bytes, int world) { return kSlots * slot_bytes + (size_t)(kSlots * world + 4) * sizeof(unsigned int); }
+    static size_t bytes(size_t slot_bytes, int world) { return kSlots * slot_bytes + (size_t)(kSlots * world + 8) * sizeof(unsigned int); }
 };
 }  // namespace rcu_window
 

@@ -175,6 +175,26 @@ rcu_status rcu_d2h(rcu_device* dev, void* dst, const void* src, uint64_t nbytes)
     return check_status_word(dev);
 }
 
+rcu_status rcu_d2h_async(rcu_device* dev, void* dst, const void* src, uint64_t nbytes) {
+    if (!dev || (nbytes && (!dst || !src))) return RCU_ERR_INVALID_ARG;
+    DevGuard g(dev->ordinal);
+    RCU_CUDA(dev, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, dev->stream));
+    return RCU_OK;
+}
+
+rcu_status rcu_stream_wait(rcu_device* dev, rcu_device* other) {
+    if (!dev || !other) return RCU_ERR_INVALID_ARG;
+    RCU_REQUIRE(dev, dev->ordinal == other->ordinal, "stream_wait: the handles are on different GPUs");
+    DevGuard g(dev->ordinal);
+    cudaEvent_t ev;
+    RCU_CUDA(dev, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaError_t e = cudaEventRecord(ev, other->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(dev->stream, ev, 0);
+    cudaEventDestroy(ev);                 // released once the wait has been satisfied
+    if (e != cudaSuccess) return rcu_fail(dev, RCU_ERR_CUDA, "stream_wait: %s", cudaGetErrorString(e));
+    return RCU_OK;
+}
+
 rcu_status rcu_d2d(rcu_device* dev, void* dst, const void* src, uint64_t nbytes) {
     if (!dev || (nbytes && (!dst || !src))) return RCU_ERR_INVALID_ARG;
     DevGuard g(dev->ordinal);

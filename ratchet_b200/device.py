@@ -131,6 +131,14 @@ class Device:
     def d2h(self, host: np.ndarray, ptr: int, nbytes: int) -> None:
         self.check(self._lib.rcu_d2h(self.handle, host.ctypes.data_as(C.c_void_p), C.c_void_p(ptr), nbytes))
 
+    def d2h_async(self, host: np.ndarray, ptr: int, nbytes: int) -> None:
+        """Device-to-host copy that does not wait (pinned `host`; valid after the next sync on this handle)."""
+        self.check(self._lib.rcu_d2h_async(self.handle, host.ctypes.data_as(C.c_void_p), C.c_void_p(ptr), nbytes))
+
+    def wait_for(self, other: "Device") -> None:
+        """Work queued on this handle from now on starts after what is queued on `other` (same GPU) so far."""
+        self.check(self._lib.rcu_stream_wait(self.handle, other.handle))
+
     # ------------------------------------------------------------------ storage
     def empty(self, dt: int, shape) -> Buffer:
         shape = tuple(int(s) for s in shape)
