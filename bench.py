@@ -202,8 +202,8 @@ def cpu_baseline_sample(K, N):
             "sample": f"{rows} of {N} rows, {reps} repetitions (~10 s)"}
 
 
-# DRAM bytes per weight row of the headline GEMV (K=16384), from the ncu capture summarised in
-# profiles/gemv_q8_kernel_K16384_N8192.md: (dram__bytes_read.sum + dram__bytes_write.sum) / rows.
+# DRAM bytes per weight row of the headline GEMV (K=16384): (dram__bytes_read.sum + dram__bytes_write.sum) / rows
+# of an ncu capture of the same kernel on an 8192-row matrix (134 MB, larger than L2; traffic grows with rows).
 GEMV_TRAFFIC_PER_ROW_BYTES = (151.047936e6 + 3.8e6) / 8192
 
 SWEEP_SHAPES = [(3072, 3072), (3072, 16384), (8192, 3072)]   # (K, N) of the decode sweep below the headline shape
@@ -283,8 +283,9 @@ def _q4kh_weights(N, K, seed):
 
 def prefill_gemm_bench(dev, torch, stream):
     """Config 3: x [M, 3072] f16 . W[8192, 3072]^T with W in ratchet Q4_KH, out [M, 8192] f16, M in
-    {128, 512, 2048}: dequantise-to-f16 kernel + tcgen05 GEMM, timed together from a CUDA graph, and
-    the GEMM alone on f16 weights (tensor-pipe figure)."""
+    {128, 512, 2048}, timed from a CUDA graph: up to M = 512 one tcgen05 kernel that converts the Q4_K tiles
+    in shared memory; beyond, a dequantise-to-f16 kernel into pooled scratch followed by the f16 tcgen05 GEMM
+    (timed together).  Also the GEMM alone on f16 weights (tensor-pipe figure)."""
     from ratchet_b200 import capi
     N, K = 8192, 3072
     wq = dev.from_quantized(_q4kh_weights(N, K, 21), capi.Q4_KH, (N, K))

@@ -1,6 +1,6 @@
 """One launch group per kernel family at a size that does not fit in L2.
 
-``python -m ratchet_b200.profile_cases [case ...]`` runs each named case (all of them by default)
+``python profile_cases.py [case ...]`` runs each named case (all of them by default)
 ``--reps`` times on one GPU, times it with CUDA events on the library's stream and prints one line
 per case: microseconds per launch, the algorithmic bytes the launch must move (inputs read once,
 outputs written once) and the resulting GB/s, or TFLOP/s for the tensor-core GEMM.  The same command
@@ -18,7 +18,13 @@ import sys
 
 import numpy as np
 
-from . import capi
+import os
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from ratchet_b200 import capi  # noqa: E402
 
 
 def _rand_f16(rng, n):
@@ -284,7 +290,7 @@ def main(argv=None):
     chosen = [by_name[n] for n in args.cases] if args.cases else CASES
 
     import torch
-    from .device import Device
+    from ratchet_b200.device import Device
     if not torch.cuda.is_available():
         print("profile_cases needs a CUDA device (there is no CPU path)", file=sys.stderr)
         return 2

@@ -14,8 +14,10 @@
 // Every kernel is HBM-bound at batch 1: the GEMVs stream the Q8_0 weights once (gemv_q8.cuh); the
 // attention kernel streams the K and V rows of the populated cache once, 16 CTAs per head so that
 // 32 heads fill the 148 SMs.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
+#include <mutex>
 
 #include <cooperative_groups.h>
 
@@ -498,10 +500,8 @@ __global__ void argmax_advance_kernel(const __half* logits, int n, int32_t* out,
 // Which attention kernel serves a step at `position` cached entries: 2 = one 16-CTA cluster per head with
 // tiles in registers (fastest while a CTA has at most two tiles, i.e. up to 2048 positions), 0 = one CTA
 // per tile staged in shared memory (more CTAs in flight for long caches), 1 = tiles in registers with the
-// global merge.  RCU_ATTN_KERNEL forces one.
+// global merge.
 int attn_variant(uint32_t position) {
-    static const int forced = [] { const char* e = std::getenv("RCU_ATTN_KERNEL"); return e ? std::atoi(e) : -1; }();
-    if (forced >= 0) return forced;
     return position + 1 <= 2u * kClusterCtas * kTile ? 2 : 0;
 }
 
@@ -521,27 +521,25 @@ rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool 
     cfg.numAttrs = overlap ? 1 : 0;
     // Same shared-memory carve-out as the GEMVs around it: an SM that has to change its L1/shared split
     // between consecutive kernels drains first, which costs microseconds per kernel in a decode step.
-    static bool carveout_set = false;
-    if (!carveout_set) {
+    static std::once_flag carveout_once;        // handles of different devices may be driven from different host threads
+    std::call_once(carveout_once, [] {
         cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(attn_decode_kernel<96>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(rope_table_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(set_u32_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        carveout_set = true;
-    }
+    });
     if (head_dim != 64 && head_dim != 96 && head_dim != 128)
         return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "attn_decode: head_dim %d (supported: 64, 96, 128)", head_dim);
-    static bool cluster_ok = true;
-    if (which == 1 || (which == 2 && cluster_ok)) {
-        static bool attr_set = false;
-        if (!attr_set) {
+    static std::atomic<bool> cluster_ok{true};
+    if (which == 1 || (which == 2 && cluster_ok.load())) {
+        static std::once_flag cluster_once;
+        std::call_once(cluster_once, [] {
             cudaFuncSetAttribute(attn_cluster_kernel<64, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             cudaFuncSetAttribute(attn_cluster_kernel<96, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             cudaFuncSetAttribute(attn_cluster_kernel<128, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-            attr_set = true;
-        }
+        });
         cudaLaunchConfig_t cc = cfg;
         cudaLaunchAttribute ca[2];
         int na = 0;
@@ -570,7 +568,7 @@ rcu_status launch_attn(rcu_device* dev, const AttnParams& p, int head_dim, bool 
             return RCU_OK;
         }
         cudaGetLastError();          // clusters of 16 not available here: use the staged kernel from now on
-        cluster_ok = false;
+        cluster_ok.store(false);
     }
     switch (head_dim) {
         case 64: RCU_CUDA(dev, cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, p)); break;
@@ -744,13 +742,11 @@ bool flow_fits_t(size_t smem) {
     return n >= 1;
 }
 
-// Instantiations of the data-flow kernel: head_dim 64 / 96 / 128, f16 or f32 block scales, 7 or 8 consumer warps
-// (with the requester warp: 8 warps, which leaves a thread 255 registers, or 9).
-#define RCU_FLOW_DISPATCH(HD_, HALF_, NW_, CALL)                                                            \
-    do {                                                                                                    \
-        if ((NW_) == 8) { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 8, CALL); }                                      \
-        else { RCU_FLOW_DISPATCH_HD(HD_, HALF_, 7, CALL); }                                                 \
-    } while (0)
+// Instantiations of the data-flow kernel: head_dim 64 / 96 / 128, f16 or f32 block scales.  Seven consumer warps:
+// with the requester warp that is eight warps, which leaves a thread 255 registers (nine warps are allotted
+// registers as twelve, 168 per thread, and the item loops spill: measured 630 tokens/s against 730).
+constexpr int kFlowWarps = 7;
+#define RCU_FLOW_DISPATCH(HD_, HALF_, NW_, CALL) RCU_FLOW_DISPATCH_HD(HD_, HALF_, kFlowWarps, CALL)
 #define RCU_FLOW_DISPATCH_HD(HD_, HALF_, NWC, CALL)                                                         \
     do {                                                                                                    \
         if ((HD_) == 64) { if (HALF_) { CALL(64, __half, NWC); } else { CALL(64, float, NWC); } }           \
@@ -759,7 +755,8 @@ bool flow_fits_t(size_t smem) {
     } while (0)
 
 template <int HD> size_t flow_union_bytes(int kmax, int nw) {
-    return nw == 8 ? flow::union_bytes<HD, 8>(kmax) : flow::union_bytes<HD, 7>(kmax);
+    (void)nw;
+    return flow::union_bytes<HD, kFlowWarps>(kmax);
 }
 
 // Exchange slots of the window (each slot_words 32-bit words): the residual stream alternates between two.
@@ -782,9 +779,7 @@ void setup_flow(rcu_decoder* d) {
     int coop = 0;
     if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal) != cudaSuccess || !coop) return;
     const int grid = dev->sm_count;
-    // consumer warps per CTA (tuning aid; the default is the measured best)
-    static const int env_nw = [] { const char* e = std::getenv("RCU_FLOW_WARPS"); return e ? std::atoi(e) : 7; }();
-    const int NW = env_nw == 8 ? 8 : 7;
+    const int NW = kFlowWarps;
     const long long GW = (long long)grid * NW;
     if (Hl < 1 || Hl > grid || (int)c.rope_dim > flow::kMaxRope || L > flow::kMaxLayersShared) return;
     if (Dl % 4 || ffnl % 4 || Vl % 4 || (Hl * HD) % 4) return;          // consumers take four words per load
@@ -805,8 +800,7 @@ void setup_flow(rcu_decoder* d) {
     auto describe = [&](int kind, int n_units, int rows, int K, int unit, bool rms) {
         flow::KindDesc& k = p.kd[kind];
         ringq8::Job j{nullptr, nullptr, n_units, n_units, K, 1, K, 1, ss};
-        static const int env_slot = [] { const char* e = std::getenv("RCU_FLOW_SLOT"); return e ? std::atoi(e) : 13056; }();
-        if (!ringq8::plan_job(&j, unit, std::min(slot_target, env_slot))) { ok = false; return; }
+        if (!ringq8::plan_job(&j, unit, slot_target)) { ok = false; return; }
         while (j.ri > 1 && (n_units + j.ri - 1) / j.ri < grid) j.ri >>= 1;                   // every CTA takes part in every matrix
         const long long n_groups = (n_units + j.ri - 1) / j.ri;
         if (n_groups < grid || n_groups * GW >= (1ll << 31)) ok = false;
@@ -900,8 +894,6 @@ void setup_flow(rcu_decoder* d) {
     p.part_stride = part_stride;
     p.slot_bytes = slot_bytes;
     p.depth = depth;
-    p.prof_cta = nullptr;
-    p.prof_job = 0;
     p.eps = c.rms_eps;
     p.prof = nullptr;
     d->slot_words = slot_words;
@@ -1287,31 +1279,8 @@ rcu_status rcu_decoder_profile_step(rcu_decoder* d, const int32_t* token_dev, vo
     if (!d->d_prof) RCU_CUDA(dev, cudaMalloc(&d->d_prof, n * sizeof(unsigned long long)));
     RCU_CUDA(dev, cudaMemsetAsync(d->d_prof, 0, n * sizeof(unsigned long long), dev->stream));
     d->fp.prof = d->d_prof;
-    const char* pj = std::getenv("RCU_FLOW_PROF_JOB");
-    unsigned long long* d_cta = nullptr;
-    if (pj) {
-        RCU_CUDA(dev, cudaMalloc(&d_cta, 10 * d->flow_grid * sizeof(unsigned long long)));
-        RCU_CUDA(dev, cudaMemsetAsync(d_cta, 0, 10 * d->flow_grid * sizeof(unsigned long long), dev->stream));
-        d->fp.prof_cta = d_cta;
-        d->fp.prof_job = std::atoi(pj);
-    }
     const rcu_status st = run_sequence_flow(d, token_dev, logits_dev, nullptr);
     d->fp.prof = nullptr;
-    d->fp.prof_cta = nullptr;
-    if (pj && st == RCU_OK) {
-        std::vector<unsigned long long> h(10 * d->flow_grid);
-        cudaStreamSynchronize(dev->stream);
-        cudaMemcpy(h.data(), d_cta, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-        unsigned long long t0 = ~0ull;
-        for (int i = 0; i < d->flow_grid; ++i) t0 = std::min(t0, h[2 * i]);
-        fprintf(stderr, "per-CTA times (ns) of five jobs from job %d: for each job, begun and staged\n", d->fp.prof_job);
-        for (int i = 0; i < d->flow_grid; ++i) {
-            fprintf(stderr, "cta %3d", i);
-            for (int j = 0; j < 5; ++j) fprintf(stderr, " %6llu %6llu", h[(j * d->flow_grid + i) * 2] - t0, h[(j * d->flow_grid + i) * 2 + 1] - t0);
-            fprintf(stderr, "\n");
-        }
-    }
-    if (d_cta) cudaFree(d_cta);
     if (st != RCU_OK) return st;
     d->steps++;
     d->position++;

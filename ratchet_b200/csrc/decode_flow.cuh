@@ -97,8 +97,6 @@ struct Params {
     int part_stride;                     // CTAs per head the scratch is laid out for
     // ring
     int slot_bytes, depth;
-    int prof_job;                        // with prof_cta: the first of five consecutive jobs whose per-CTA times are recorded
-    unsigned long long* prof_cta;        // optional: [5][grid][2] per CTA: job begun, input staged
     float eps;
     unsigned long long* prof;            // optional (nullptr: off): [2 n_jobs + 1] time stamps of CTA 0 (job begun, input staged; end), then
                                          // per job kind four sums of SM clock cycles of the grid's first warp: slot wait, multiply, store, release
@@ -809,8 +807,6 @@ __device__ __noinline__ WarpState attention_job(const Params& p, const LayerPtrs
         }
     }
     if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j + 1] = ringq8::globaltimer();     // warp 0's tiles are folded
-    if (p.prof_cta && tid == 0 && j >= p.prof_job && j < p.prof_job + 5)
-        p.prof_cta[((j - p.prof_job) * gridDim.x + blockIdx.x) * 2 + 1] = ringq8::globaltimer();
     // ---- the warps of the CTA merge through shared memory
     write_part<HD>(ash->part[warp], st);
     ringq8::stage_barrier<NT>();
@@ -892,8 +888,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __g
         split_job(p, j, li, kind);
         ringq8::stage_barrier<NT>();                       // the planes and the attention scratch of job j - 1 are free again
         if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j] = ringq8::globaltimer();
-        if (p.prof_cta && tid == 0 && j >= p.prof_job && j < p.prof_job + 5)
-            p.prof_cta[((j - p.prof_job) * gridDim.x + blockIdx.x) * 2] = ringq8::globaltimer();
         if (kind != K_ATTN) {
             const KindDesc& k = p.kd[kind];
             // the residuals of this warp's units (final since the job before last): lane i, unit i of the warp
@@ -907,8 +901,6 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_flow_kernel(const __g
             stage_job<NT>(p, k, gamma, make_tag(step, k.in_per_step, (uint32_t)(li * k.in_mul + k.in_add)), planes, scratch);
             ringq8::stage_barrier<NT>();
             if (p.prof && blockIdx.x == 0 && tid == 0) p.prof[2 * j + 1] = ringq8::globaltimer();
-            if (p.prof_cta && tid == 0 && j >= p.prof_job && j < p.prof_job + 5)
-                p.prof_cta[((j - p.prof_job) * gridDim.x + blockIdx.x) * 2 + 1] = ringq8::globaltimer();
             if (ws.cc.job != j) continue;
             const Out out = make_out(p, k.out_off, k.push != 0, make_tag(step, k.out_per_step, (uint32_t)(li * k.out_mul + k.out_add)), kind);
             switch (k.unit * 8 + k.ri) {

@@ -64,7 +64,7 @@ struct Cursor {
     bool ok = true;
     template <class T> T get() {
         T v{};
-        if (pos + sizeof(T) > size) { ok = false; return v; }
+        if (pos > size || sizeof(T) > size - pos) { ok = false; return v; }     // lengths come from the file: no sum that can wrap
         memcpy(&v, base + pos, sizeof(T));
         pos += sizeof(T);
         return v;
@@ -72,7 +72,7 @@ struct Cursor {
     uint64_t len(int version) { return version == 1 ? get<uint32_t>() : get<uint64_t>(); }
     std::string str(int version) {
         const uint64_t n = len(version);
-        if (!ok || pos + n > size) { ok = false; return {}; }
+        if (!ok || pos > size || n > size - pos) { ok = false; return {}; }
         std::string s((const char*)base + pos, (size_t)n);
         pos += n;
         while (version == 1 && !s.empty() && s.back() == '\0') s.pop_back();   // v1 strings carry their terminator
@@ -115,8 +115,9 @@ bool read_value(Cursor& c, int version, uint32_t type, MetaValue* out, int depth
                     if (!read_value(c, version, 9, &tmp, depth + 1)) return false;
             } else {
                 const size_t es = value_size(et);
-                if (es == 0 || c.pos + n * es > c.size) return false;
-                c.pos += n * es;
+                uint64_t bytes = 0;
+                if (es == 0 || __builtin_mul_overflow(n, (uint64_t)es, &bytes) || c.pos > c.size || bytes > c.size - c.pos) return false;
+                c.pos += bytes;
             }
             break;
         }
@@ -225,9 +226,14 @@ rcu_status rcu_gguf_open(const char* path, rcu_gguf** out) {
         }
         uint64_t dims[4];
         for (uint32_t d = 0; d < t.rank; ++d) dims[d] = c.len(g->version);
+        bool overflow = false;
         for (uint32_t d = 0; d < t.rank; ++d) {             // stored innermost first
             t.shape[d] = dims[t.rank - 1 - d];
-            t.numel *= t.shape[d];
+            overflow = overflow || __builtin_mul_overflow(t.numel, t.shape[d], &t.numel);
+        }
+        if (overflow || t.numel > (1ull << 48)) {           // no tensor of a real file comes near; larger counts would wrap the byte arithmetic below
+            rcu_gguf_close(g);
+            return gguf_fail(RCU_ERR_INVALID_ARG, "gguf: tensor %llu ('%s') has an impossible shape", (unsigned long long)i, t.name.c_str());
         }
         t.ggml_type = c.get<uint32_t>();
         t.offset = c.get<uint64_t>();
@@ -314,8 +320,9 @@ rcu_status rcu_gguf_transcode(const rcu_gguf* g, uint64_t index, int32_t dt, voi
     if (t.numel % bn != 0)
         return gguf_fail(RCU_ERR_INVALID_ARG, "the number of elements %llu is not divisible by the block size %llu", (unsigned long long)t.numel,
                          (unsigned long long)bn);                         // gguf.rs:119-123
+    if (g->data_offset > g->size || t.offset > g->size - g->data_offset || t.file_bytes > g->size - g->data_offset - t.offset)
+        return gguf_fail(RCU_ERR_INVALID_ARG, "gguf: tensor '%s' runs past the end of the file", t.name.c_str());
     const uint64_t begin = g->data_offset + t.offset;
-    if (begin + t.file_bytes > g->size) return gguf_fail(RCU_ERR_INVALID_ARG, "gguf: tensor '%s' runs past the end of the file", t.name.c_str());
     const uint64_t need = rcu_dtype_nbytes(dt, t.numel);
     if (need == 0 || out_bytes < need)
         return gguf_fail(RCU_ERR_INVALID_ARG, "gguf: '%s' as dtype %d needs %llu bytes, buffer has %llu", t.name.c_str(), dt, (unsigned long long)need,

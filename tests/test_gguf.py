@@ -140,3 +140,37 @@ def test_rejects_what_the_reference_rejects(tmp_path):
     with GGUFFile(str(trunc)) as f:
         with pytest.raises(RatchetCudaError):
             f.transcode("w")
+
+
+def test_hostile_lengths_are_refused_not_followed(tmp_path):
+    """Lengths, counts and offsets come from the file: values chosen so that `position + length` wraps around
+    64 bits must be refused like any other value that points outside the file."""
+    huge = 0xFFFFFFFFFFFFFFF0
+    # a metadata string whose length wraps position + length
+    p1 = tmp_path / "str.gguf"
+    p1.write_bytes(struct.pack("<II", 0x46554747, 3) + struct.pack("<QQ", 0, 1) + struct.pack("<Q", huge) + b"k" * 64)
+    with pytest.raises(RatchetCudaError):
+        GGUFFile(str(p1))
+    # an array of u64 whose count times the element size wraps
+    p2 = tmp_path / "arr.gguf"
+    p2.write_bytes(struct.pack("<II", 0x46554747, 3) + struct.pack("<QQ", 0, 1) + _s("a", 3) + struct.pack("<I", 9) +
+                   struct.pack("<I", 10) + struct.pack("<Q", 0x2000000000000001) + b"\0" * 64)
+    with pytest.raises(RatchetCudaError):
+        GGUFFile(str(p2))
+    # a tensor whose shape overflows the element count, and one whose offset wraps data_offset + offset
+    p3 = tmp_path / "shape.gguf"
+    p3.write_bytes(struct.pack("<II", 0x46554747, 3) + struct.pack("<QQ", 1, 0) + _s("w", 3) + struct.pack("<I", 2) +
+                   struct.pack("<QQ", 1 << 40, 1 << 40) + struct.pack("<IQ", GGML_F32, 0) + b"\0" * 64)
+    with pytest.raises(RatchetCudaError) as e:
+        GGUFFile(str(p3))
+    assert "impossible shape" in str(e.value)
+    p4 = str(tmp_path / "off.gguf")
+    write_gguf(p4, [("w", (64,), GGML_F32, b"\0" * 256)], [])
+    raw = bytearray(open(p4, "rb").read())
+    at = raw.index(b"w") + 1 + 4 + 8 + 4          # name, rank, one dimension, type -> the offset field
+    raw[at: at + 8] = struct.pack("<Q", huge)
+    open(p4, "wb").write(bytes(raw))
+    with GGUFFile(p4) as f:
+        with pytest.raises(RatchetCudaError) as e:
+            f.transcode("w")
+        assert "past the end of the file" in str(e.value)
