@@ -337,8 +337,9 @@ rcu_status rcu_attn_decode(rcu_device* dev, const void* qkv, void* k_cache, void
  * host framework that owns the device heap, latency-bound serving loops that cannot take the device
  * synchronisation of an allocation, processes that have given all free memory to their KV caches.
  * The split-KV scratch is a fixed 2.04 MiB array inside the library's device image (held by every GPU
- * that loads the library until the process exits), which limits this variant to n_heads <= 64 and
- * head_dim <= 128; larger requests return RCU_ERR_INVALID_ARG with a message naming the limit.
+ * that loads the library until the process exits), which limits this variant to n_heads <= 64,
+ * head_dim <= 128 and max_cache <= 4096 positions; larger requests return RCU_ERR_INVALID_ARG with a
+ * message naming the limit.
  * Same arguments and results as rcu_attn_decode.  The first call on a device looks up the array's
  * device address and should be made before any stream capture.  All calls on a device share the
  * array: calls that overlap on the GPU race, so keep them on one stream or otherwise ordered. */

@@ -340,11 +340,16 @@ bool rcu_gemm_tc_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64
     return true;
 }
 
+// gemm_tc2.cu: the CTA-pair kernel for f16 weights
+bool rcu_gemm_tc2_eligible(rcu_device* dev, uint64_t M, uint64_t N, uint64_t K);
+rcu_status rcu_gemm_tc2_launch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N, uint64_t K);
+
 rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int act_dt, const void* x, const void* bias, void* y,
                                 uint64_t M, uint64_t N, uint64_t K) {
     if (!rcu_gemm_tc_eligible(lhs_dt, act_dt, M, N, K)) return RCU_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w)) & 15) return RCU_ERR_UNSUPPORTED;
     DevGuard g(dev->ordinal);
+    if (lhs_dt == RCU_F16 && rcu_gemm_tc2_eligible(dev, M, N, K)) return rcu_gemm_tc2_launch(dev, w, x, bias, y, M, N, K);
     // Quantised weights.  The fused kernel converts a weight tile once per 128-row token tile, i.e.
     // M/128 times over the whole problem; beyond kFusedMaxM token rows that repeated conversion costs
     // more than converting the matrix once into pooled f16 scratch (which stays in L2) and running the

@@ -26,7 +26,10 @@ def check(got, ref, tol, what):
 
 
 # (M, N, K): full tiles, ragged M / N / K edges, several k-steps beyond the pipeline depth, both tile widths
-SHAPES = [(128, 256, 256), (512, 512, 1024), (100, 200, 136), (37, 64, 64), (2048, 256, 512), (130, 1032, 3072), (1500, 384, 384)]
+SHAPES = [(128, 256, 256), (512, 512, 1024), (100, 200, 136), (37, 64, 64), (2048, 256, 512), (130, 1032, 3072), (1500, 384, 384),
+          # the CTA-pair kernel (at least 37 tiles of 256 x 256): full tiles; ragged M, N and K; more tiles than CTA pairs
+          # (persistent loop, both accumulator buffers, the stage ring wrapping across tiles); one k-step only
+          (1024, 2560, 320), (1000, 2504, 328), (2048, 4096, 512), (1300, 5000, 136), (2048, 8192, 64)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
