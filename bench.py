@@ -378,14 +378,29 @@ def _q8f_random(N, K, seed):
     return buf
 
 
-def whisper_encoder_bench(dev, torch, stream, quantised=False):
+def _q8h_random(N, K, seed):
+    """Q8_0H buffer (f16 scales) of random int8 codes with scales that give weights of N(0, 0.02)-like size."""
+    from ratchet_b200 import capi
+    rng = np.random.Generator(np.random.PCG64(seed))
+    buf = np.zeros(capi.dtype_nbytes(capi.Q8_0H, N * K), np.uint8)
+    buf[: N * K].view(np.int8)[:] = rng.integers(-127, 128, N * K, dtype=np.int8)
+    off = capi.dtype_segments(capi.Q8_0H, N * K)[1]
+    buf[off: off + (N * K // 32) * 2].view(np.float16)[:] = (np.abs(rng.standard_normal(N * K // 32)) * 0.0002 + 0.0003).astype(np.float16)
+    return buf
+
+
+def whisper_encoder_bench(dev, torch, stream, mode="f32"):
     """Config 4: Whisper-tiny encoder forward through the lazy Tensor graph: mel [1,80,3000] U(-1,1),
-    conv stem, sinusoidal positions, 4 pre-LN blocks (d 384, 6 heads, MLP 1536), final LayerNorm;
-    f32 activations; weights N(0, 0.02) in f32, or (quantised) the Linear weights as Q8_0F buffers."""
+    conv stem, sinusoidal positions, 4 pre-LN blocks (d 384, 6 heads, MLP 1536), final LayerNorm.
+    mode "f32": f32 activations and weights N(0, 0.02); "q8f": f32 activations, Linear weights as Q8_0F
+    buffers; "q8h": f16 activations and parameters, Linear weights as Q8_0H buffers (what ratchet loads on
+    a device with f16 support)."""
     from ratchet_b200 import Tensor, callers, capi, nn
     g = np.random.Generator(np.random.PCG64(0))
     d, H, mlp, n_ctx = 384, 6, 1536, 1500
     seeds = iter(range(1000, 2000))
+    quantised = mode != "f32"
+    act_np, act_dt = (np.float16, capi.F16) if mode == "q8h" else (np.float32, capi.F32)
 
     def w(*shape):
         if quantised and len(shape) == 2:
@@ -394,12 +409,14 @@ def whisper_encoder_bench(dev, torch, stream, quantised=False):
 
     def t(a):   # Linear weights come as (None, shape) when they are to be quantised
         if isinstance(a, tuple):
+            if mode == "q8h":
+                return Tensor.from_quantized(_q8h_random(a[1][0], a[1][1], next(seeds)), capi.Q8_0H, a[1], dev)
             return Tensor.from_quantized(_q8f_random(a[1][0], a[1][1], next(seeds)), capi.Q8_0F, a[1], dev)
-        return Tensor.from_data(np.ascontiguousarray(a, np.float32), device=dev)
+        return Tensor.from_data(np.ascontiguousarray(a, np.float32), device=dev)    # parameters stay f32, as the checkpoint has them
     inc = np.log(10000.0) / (d // 2 - 1)
     ang = np.arange(n_ctx)[:, None] * np.exp(-inc * np.arange(d // 2))[None, :]
     pos = np.concatenate([np.sin(ang), np.cos(ang)], 1)
-    dk = t(np.array([np.float32(d // H) ** np.float32(-0.25)], np.float32))
+    dk = Tensor.from_data(np.array([np.float32(d // H) ** np.float32(-0.25)], np.float32).astype(act_np), device=dev)
     blocks = []
     for _ in range(4):
         mha = callers.WhisperMHA(nn.Linear(t(w(d, d)), t(w(d))), nn.Linear(t(w(d, d)), None), nn.Linear(t(w(d, d)), t(w(d))),
@@ -408,7 +425,7 @@ def whisper_encoder_bench(dev, torch, stream, quantised=False):
                                            nn.LayerNorm(t(np.ones(d)), t(np.zeros(d)), 1e-5),
                                            callers.WhisperMLP(nn.Linear(t(w(mlp, d)), t(w(mlp))), nn.Linear(t(w(d, mlp)), t(w(d))))))
     enc = callers.WhisperEncoder(t(w(d, 80, 3)), t(w(d)), t(w(d, d, 3)), t(w(d)), t(pos), blocks,
-                                 nn.LayerNorm(t(np.ones(d)), t(np.zeros(d)), 1e-5), capi.F32)
+                                 nn.LayerNorm(t(np.ones(d)), t(np.zeros(d)), 1e-5), act_dt)
     mel = t(g.uniform(-1.0, 1.0, (1, 80, 3000)))
     l0 = dev.launches
     enc.schedule(mel).resolve()
@@ -416,9 +433,12 @@ def whisper_encoder_bench(dev, torch, stream, quantised=False):
     us = _lazy_forward_us(torch, stream, lambda: enc.schedule(mel).resolve(), 20)
     # flops: conv stem + per block (4 projections, QK^T, PV, two MLP matmuls)
     flops = 2.0 * 3000 * d * 80 * 3 + 2.0 * n_ctx * d * d * 3 + 4 * (2.0 * n_ctx * d * d * 4 + 2 * 2.0 * n_ctx * n_ctx * d + 2 * 2.0 * n_ctx * d * mlp)
+    what = {"f32": "f32 activations and weights",
+            "q8f": "f32 activations, Q8_0F Linear weights (dequantised into pooled scratch, then the f32 tensor-core GEMM)",
+            "q8h": "f16 activations, Q8_0H Linear weights (tcgen05 f16 GEMM)"}[mode]
+    score_mb = 6 * n_ctx * n_ctx * (2 if mode == "q8h" else 4) * 3 / 1e6
     return {"us_per_forward": us, "kernels_per_forward": int(launches), "tflops": flops / us * 1e-6,
-            "note": ("f32 activations, Q8_0F Linear weights (dequantised into pooled scratch, then the f32 tensor-core GEMM)" if quantised else
-                     "f32 activations and weights") + "; mixed launch- and compute-bound (241 MB of 1500x1500 score matrices per layer pass through L2)"}
+            "note": what + f"; mixed launch- and compute-bound ({score_mb:.0f} MB of 1500x1500 score matrices per layer pass through L2)"}
 
 
 def phi3_decode_bytes(c):
@@ -817,7 +837,8 @@ def run_ours(args):
             extras["phi2_mlp_f32"] = phi2_mlp_bench(dev, torch, stream)
         if want("whisper"):
             extras["whisper_tiny_encoder_f32"] = whisper_encoder_bench(dev, torch, stream)
-            extras["whisper_tiny_encoder_q8_0f"] = whisper_encoder_bench(dev, torch, stream, quantised=True)
+            extras["whisper_tiny_encoder_q8_0f"] = whisper_encoder_bench(dev, torch, stream, mode="q8f")
+            extras["whisper_tiny_encoder_q8_0h"] = whisper_encoder_bench(dev, torch, stream, mode="q8h")
         if want("decode"):
             extras["phi3_decode"] = phi3_decode_bench(dev, torch, stream, steps=min(args.steps, 200), warmup=max(args.warmup, 3))
     if world > 1 and not args.rows and not args.no_extras:

@@ -14,7 +14,7 @@
 //                      the accumulator barrier;
 //   warps 2-5          epilogue: tcgen05.ld the f32 accumulators (lane = token row, column =
 //                      output feature), add bias, round to f16, store rows.
-// Quantised weights (Q8_0H, Q4_KH) are dequantised inside the kernel (up to 512 token rows): TMA
+// Quantised weights (Q8_0H, Q4_KH) are dequantised inside the kernel (up to 256 token rows): TMA
 // brings the packed bytes of the weight tile into shared memory, further warps convert them to f16
 // with the CPU dequantiser's arithmetic and write the swizzled tile the MMA reads.  Larger M
 // dequantises once into pooled scratch and runs the f16 kernel.
@@ -77,6 +77,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * BN;
     const int nk = (K + TK - 1) / TK;
+    const int bz = blockIdx.z;                       // independent problem (batched f16 products); 0 otherwise
+    out += (size_t)bz * M * N;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -106,11 +108,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 unsigned char* st = smem + s * STAGE;
                 if (WK == WK_F16) {
                     mbar_expect_tx(&full[s], STAGE);
-                    tma_load_2d(st, &xmap, it * TK, m0, &full[s]);             // activations: rows m0.., k it*64..
-                    tma_load_2d(st + A_BYTES, &wmap, it * TK, n0, &full[s]);   // weights: rows n0..
+                    tma_load_3d(st, &xmap, it * TK, m0, bz, &full[s]);             // activations: rows m0.., k it*64..
+                    tma_load_3d(st + A_BYTES, &wmap, it * TK, n0, bz, &full[s]);   // weights: rows n0..
                 } else {
                     mbar_expect_tx(&raw_full[s], A_BYTES + RAW_BYTES);
-                    tma_load_2d(st, &xmap, it * TK, m0, &raw_full[s]);
+                    tma_load_3d(st, &xmap, it * TK, m0, 0, &raw_full[s]);
                     tma_load_2d(st + STAGE - RAW_BYTES, &wmap, it * RAW_ROW, n0, &raw_full[s]);   // packed bytes of 64 weights per row
                 }
             }
@@ -149,17 +151,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
                 if (row < M) {
                     __half* orow = out + (size_t)row * N + n0 + c;
+                    if ((N & 7) == 0) {              // rows start on 16-byte boundaries
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        const int col = n0 + c + j;
-                        if (col + 8 <= N) {
-                            __align__(16) __half h[8];
+                        for (int j = 0; j < 32; j += 8) {
+                            const int col = n0 + c + j;
+                            if (col + 8 <= N) {
+                                __align__(16) __half h[8];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) h[e] = __float2half_rn(v[j + e] + (bias ? __half2float(bias[col + e]) : 0.f));
-                            *reinterpret_cast<uint4*>(orow + j) = *reinterpret_cast<const uint4*>(h);
-                        } else {
-                            for (int e = 0; e < 8 && col + e < N; ++e)
-                                orow[j + e] = __float2half_rn(v[j + e] + (bias ? __half2float(bias[col + e]) : 0.f));
+                                for (int e = 0; e < 8; ++e) h[e] = __float2half_rn(v[j + e] + (bias ? __half2float(bias[col + e]) : 0.f));
+                                *reinterpret_cast<uint4*>(orow + j) = *reinterpret_cast<const uint4*>(h);
+                            } else {
+                                for (int e = 0; e < 8 && col + e < N; ++e)
+                                    orow[j + e] = __float2half_rn(v[j + e] + (bias ? __half2float(bias[col + e]) : 0.f));
+                            }
+                        }
+                    } else {                         // N a multiple of 4 (checked by the host): 8-byte stores
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const int col = n0 + c + j;
+                            if (col + 4 <= N) {
+                                __align__(8) __half h[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) h[e] = __float2half_rn(v[j + e] + (bias ? __half2float(bias[col + e]) : 0.f));
+                                *reinterpret_cast<uint2*>(orow + j) = *reinterpret_cast<const uint2*>(h);
+                            }
                         }
                     }
                 }
@@ -304,28 +319,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 
 template <int BN, int WK>
 rcu_status launch_tc(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const QuantArgs& qa, const void* bias, void* out,
-                     int M, int N, int K) {
+                     int M, int N, int K, int batch = 1) {
     constexpr int STAGE = TM * TK * 2 + BN * TK * 2;
     constexpr int STAGES = (100 * 1024) / STAGE;     // two CTAs per SM
     const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
     auto kern = gemm_tc_kernel<BN, WK, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM);
+    dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batch);
     kern<<<grid, WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, smem, dev->stream>>>(xmap, wmap, qa, (const __half*)bias, (__half*)out, M, N, K,
                                                                                       dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
 
-// [rows, K] f16 row-major, box = box_rows x 64 elements, 128-byte swizzle
-bool make_map_f16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+// [batch, rows, K] f16, rows `pitch` elements apart (a multiple of 8: tensor-map strides are 16-byte multiples), box =
+// box_rows x 64 elements of one problem, 128-byte swizzle; reads beyond K or rows are filled with zeros
+bool make_map_f16_sw128(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows, uint64_t batch = 1, uint64_t pitch = 0) {
     gemvq8::EncodeTiledFn fn = gemvq8::encode_tiled_fn();
     if (!fn) return false;
-    cuuint64_t dims[2] = {K, rows};
-    cuuint64_t strides[1] = {K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TK, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    if (pitch == 0) pitch = K;
+    cuuint64_t dims[3] = {K, rows, batch};
+    cuuint64_t strides[2] = {pitch * 2, rows * pitch * 2};
+    cuuint32_t box[3] = {(cuuint32_t)TK, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -351,10 +368,11 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
     DevGuard g(dev->ordinal);
     if (lhs_dt == RCU_F16 && rcu_gemm_tc2_eligible(dev, M, N, K)) return rcu_gemm_tc2_launch(dev, w, x, bias, y, M, N, K);
     // Quantised weights.  The fused kernel converts a weight tile once per 128-row token tile, i.e.
-    // M/128 times over the whole problem; beyond kFusedMaxM token rows that repeated conversion costs
-    // more than converting the matrix once into pooled f16 scratch (which stays in L2) and running the
-    // f16 kernel on it.  RCU_GEMM_FUSED=0/1 forces either path.
-    constexpr uint64_t kFusedMaxM = 512;
+    // M/128 times over the whole problem, and it is the one-CTA kernel.  Beyond kFusedMaxM token rows it
+    // is cheaper to convert the matrix once into pooled f16 scratch (which stays in L2) and run the f16
+    // kernels on it (M = 512, N = 8192, K = 3072, Q4_K: 34 us against 46 us fused).  RCU_GEMM_FUSED=0/1
+    // forces either path.
+    constexpr uint64_t kFusedMaxM = 256;
     if (lhs_dt != RCU_F16) {
         const char* force = getenv("RCU_GEMM_FUSED");
         const bool fused = force ? atoi(force) != 0 : M <= kFusedMaxM;
@@ -411,4 +429,25 @@ rcu_status rcu_gemm_tc_dispatch(rcu_device* dev, int lhs_dt, const void* w, int 
     }
 #undef RCU_TC
     return st;
+}
+
+// `batch` independent products out[b] = X[b] . W[b]^T with X [batch, M, pitch_x] and W [batch, N, pitch_w] f16, both K-major
+// (K <= pitch, pitches multiples of 8), out [batch, M, N] f16 contiguous with N a multiple of 4.  The attention products
+// of an f16 model (whisper/mha.rs:95-110: q.k^T over 6 heads, then weights.v) take this; blockIdx.z is the problem.
+rcu_status rcu_gemm_tc_batched_f16(rcu_device* dev, const void* w, const void* x, void* y, uint64_t M, uint64_t N, uint64_t K, uint64_t batch,
+                                   uint64_t pitch_w, uint64_t pitch_x) {
+    if (M < 32 || N < 64 || K < 64 || N % 4 != 0 || pitch_w % 8 != 0 || pitch_x % 8 != 0 || batch == 0 || batch > 65535) return RCU_ERR_UNSUPPORTED;
+    if (M > 0x7fffffffull || N > 0x7fffffffull || K > 0x7fffffffull) return RCU_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return RCU_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(y) & ((N % 8 == 0) ? 15 : 7)) return RCU_ERR_UNSUPPORTED;
+    DevGuard g(dev->ordinal);
+    const uint64_t tiles128 = ((M + TM - 1) / TM) * ((N + 127) / 128) * batch;
+    const int bn = (tiles128 >= (uint64_t)dev->sm_count && N >= 128) ? 128 : 64;
+    CUtensorMap xmap, wmap;
+    if (!make_map_f16_sw128(&xmap, x, M, K, TM, batch, pitch_x) || !make_map_f16_sw128(&wmap, w, N, K, (uint32_t)bn, batch, pitch_w))
+        return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed (batched M=%llu N=%llu K=%llu)", (unsigned long long)M,
+                        (unsigned long long)N, (unsigned long long)K);
+    QuantArgs qa{nullptr, nullptr, nullptr};
+    return bn == 128 ? launch_tc<128, WK_F16>(dev, xmap, wmap, qa, nullptr, y, (int)M, (int)N, (int)K, (int)batch)
+                     : launch_tc<64, WK_F16>(dev, xmap, wmap, qa, nullptr, y, (int)M, (int)N, (int)K, (int)batch);
 }

@@ -17,6 +17,9 @@ bool rcu_gemm_tc_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64
 rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* x, const void* bias, void* y, uint64_t M, uint64_t N,
                                     uint64_t K, uint64_t batches, const void* bias_rows = nullptr);
 bool rcu_gemm_tc_f32_eligible(int lhs_dt, int act_dt, uint64_t M, uint64_t N, uint64_t K);
+rcu_status rcu_gemm_tc_batched_f16(rcu_device* dev, const void* w, const void* x, void* y, uint64_t M, uint64_t N, uint64_t K, uint64_t batch,
+                                   uint64_t pitch_w, uint64_t pitch_x);
+rcu_status rcu_copy2d_pitched(rcu_device* dev, const void* src, void* dst, size_t rows, size_t row_bytes, size_t spitch, size_t dpitch);
 rcu_status rcu_gemv_q4k_dispatch(rcu_device* dev, int lhs_dt, const void* w, int act_dt, const void* x, const void* bias, void* y,
                                  uint64_t N, uint64_t K);
 
@@ -279,6 +282,41 @@ rcu_status rcu_matmul(rcu_device* dev, const rcu_tensor* lhs, const rcu_tensor* 
         }
         if (st == RCU_OK) st = rcu_gemm_tc_f32_dispatch(dev, wptr, lhs->data, nullptr, dst->data, d.m, d.n, d.k, d.lstack);
         if (scratch) rcu_free(dev, scratch);     // the pool reuses blocks in stream order
+        if (st != RCU_ERR_UNSUPPORTED) return st;
+    }
+    // The same products in f16 (the attention of an f16 model): A[b, M, K] . B[b, K, N] on the f16 tensor-core
+    // kernel, one problem per blockIdx.z.  Tensor maps need row pitches of whole 16 bytes: an operand whose K
+    // is not a multiple of 8 (Whisper's 1500 positions) is copied into pooled scratch with padded rows (the
+    // kernel never reads the padding: the maps give the true K and fill beyond it with zeros), and an
+    // untransposed B is transposed first.
+    if (!tl && !td && !bias && lhs->dt == RCU_F16 && rhs->dt == RCU_F16 && d.lstack == d.rstack && d.dstack == d.lstack &&
+        d.m >= 128 && d.n >= 64 && d.k >= 64 && d.n % 4 == 0 && d.m * d.n * d.k * d.lstack >= (1ull << 24)) {
+        const uint64_t b = d.lstack, kp = (d.k + 7) & ~7ull;
+        void* scratch[3] = {nullptr, nullptr, nullptr};
+        const void* aptr = lhs->data;
+        const void* wptr = rhs->data;
+        st = RCU_OK;
+        if (!tr) {          // B [b, K, N] -> [b, N, K]
+            st = rcu_alloc(dev, b * d.k * d.n * 2, &scratch[0]);
+            if (st == RCU_OK) {
+                rcu_tensor src{RCU_F16, 3, {b, d.k, d.n, 1}, rhs->data};
+                rcu_tensor tdst{RCU_F16, 3, {b, d.n, d.k, 1}, scratch[0]};
+                const uint32_t perm[3] = {0, 2, 1};
+                st = rcu_permute(dev, &src, perm, &tdst);
+                wptr = scratch[0];
+            }
+        }
+        if (st == RCU_OK && kp != d.k) {
+            st = rcu_alloc(dev, b * d.n * kp * 2, &scratch[1]);
+            if (st == RCU_OK) st = rcu_copy2d_pitched(dev, wptr, scratch[1], b * d.n, d.k * 2, d.k * 2, kp * 2);
+            wptr = scratch[1];
+            if (st == RCU_OK) st = rcu_alloc(dev, b * d.m * kp * 2, &scratch[2]);
+            if (st == RCU_OK) st = rcu_copy2d_pitched(dev, aptr, scratch[2], b * d.m, d.k * 2, d.k * 2, kp * 2);
+            aptr = scratch[2];
+        }
+        if (st == RCU_OK) st = rcu_gemm_tc_batched_f16(dev, wptr, aptr, dst->data, d.m, d.n, d.k, b, kp, kp);
+        for (void* s : scratch)
+            if (s) rcu_free(dev, s);     // the pool reuses blocks in stream order
         if (st != RCU_ERR_UNSUPPORTED) return st;
     }
     const uint64_t numel = t_numel(lhs);

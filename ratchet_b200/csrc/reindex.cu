@@ -343,6 +343,13 @@ gather_q8_rows16_kernel(const uint4* __restrict__ q, const ScaleT* __restrict__ 
 
 }  // namespace
 
+// rows of row_bytes each, source and destination pitches in bytes (used by the batched f16 matmul to give
+// rows a pitch the tensor maps accept)
+rcu_status rcu_copy2d_pitched(rcu_device* dev, const void* src, void* dst, size_t rows, size_t row_bytes, size_t spitch, size_t dpitch) {
+    return copy2d(dev, src, dst, rows, row_bytes, spitch, dpitch);
+}
+
+
 extern "C" {
 
 rcu_status rcu_permute(rcu_device* dev, const rcu_tensor* src, const uint32_t* perm, rcu_tensor* dst) {

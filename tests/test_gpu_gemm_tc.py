@@ -45,6 +45,21 @@ def test_gemm_tc_f16(dev, M, N, K, with_bias):
     check(y.to_numpy(), ref, 1e-2, f"f16 {M}x{N}x{K}")
 
 
+# batched f16 products A[b, M, K] . B[b, K, N] (or B as [b, N, K] with trans_rhs): Whisper-tiny's q.k^T and weights.v over six
+# heads of 1500 positions (K = 1500 is not a multiple of 8: padded scratch rows; N = 1500 is not one either: 8-byte stores),
+# a shape with whole tiles, and one with ragged M
+@pytest.mark.parametrize("b,M,K,N,trans_rhs", [(6, 1500, 64, 1500, False), (6, 1500, 1500, 64, False), (2, 256, 128, 256, True),
+                                                (3, 200, 72, 132, False), (2, 384, 1000, 64, True)])
+def test_gemm_tc_batched_f16(dev, b, M, K, N, trans_rhs):
+    g = np.random.Generator(np.random.PCG64(b * M + K + N))
+    a = (g.standard_normal((1, b, M, K)) * 0.5).astype(np.float16)
+    bm = (g.standard_normal((1, b, N, K) if trans_rhs else (1, b, K, N)) * 0.5).astype(np.float16)
+    ref = orc.matmul(a, bm, None, False, trans_rhs, False)
+    y = dev.matmul(dev.from_numpy(a), dev.from_numpy(bm), None, False, trans_rhs, False)
+    assert y.shape == (1, b, M, N)
+    check(y.to_numpy(), ref, 1e-2, f"batched f16 {b}x{M}x{K}x{N}")
+
+
 @pytest.mark.parametrize("kind", ["Q8_0H", "Q4_KH"])
 @pytest.mark.parametrize("M,N,K", [(128, 512, 768), (512, 256, 3072), (77, 96, 512)])
 def test_gemm_tc_quantised(dev, kind, M, N, K):
@@ -77,11 +92,12 @@ def config3_weight():
     return buf, orc.dequantize_q4k(buf, (N, K), True)
 
 
-@pytest.mark.parametrize("M", [128, 512, 2048])
+@pytest.mark.parametrize("M", [128, 256, 512, 2048])
 def test_config3_q4k_prefill_shape(dev, config3_weight, M):
-    """Config 3 at its three sizes: x [M, 3072] f16 N(0,1), W [8192, 3072] in ratchet Q4_K, out [M, 8192]
-    f16.  M <= 512 runs the kernel that converts Q4_K tiles in shared memory; M = 2048 converts the matrix
-    once into scratch and runs the f16 kernel with 128 x 256 tiles: both against dequantise -> matmul."""
+    """Config 3 at its three sizes (and 256, the last size of the fused kernel): x [M, 3072] f16 N(0,1),
+    W [8192, 3072] in ratchet Q4_K, out [M, 8192] f16.  M <= 256 runs the kernel that converts Q4_K tiles in
+    shared memory; M = 512 and 2048 convert the matrix once into scratch and run the CTA-pair f16 kernel:
+    all against dequantise -> matmul."""
     from ratchet_b200 import capi
     N, K = 8192, 3072
     buf, wd = config3_weight
