@@ -204,7 +204,7 @@ def cpu_baseline_sample(K, N):
 
 # DRAM bytes per weight row of the headline GEMV (K=16384): (dram__bytes_read.sum + dram__bytes_write.sum) / rows
 # of an ncu capture of the same kernel on an 8192-row matrix (134 MB, larger than L2; traffic grows with rows).
-GEMV_TRAFFIC_PER_ROW_BYTES = (151.047936e6 + 3.8e6) / 8192
+GEMV_TRAFFIC_PER_ROW_BYTES = (151.075e6 + 4.9e6) / 8192
 
 SWEEP_SHAPES = [(3072, 3072), (3072, 16384), (8192, 3072)]   # (K, N) of the decode sweep below the headline shape
 
