@@ -348,6 +348,28 @@ def _lazy_forward_us(torch, stream, build_and_resolve, iters):
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+def _lazy_forward_device_us(torch, stream, build_and_resolve, iters):
+    """Device time of the same forward with the host out of the picture: the launches of one build + resolve
+    are captured into a CUDA graph (the resolver neither synchronises nor allocates from the driver once its
+    pool is warm) and the graph is replayed.  None if the capture is refused."""
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            keep = build_and_resolve()       # alive until the capture ends
+        del keep
+        graph.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / iters
+    except Exception:
+        return None
+
+
 def phi2_mlp_bench(dev, torch, stream):
     """Config 1: Phi-2 MLP block in f32 through the lazy Tensor graph: x [1,64,2560] N(0,1), LayerNorm,
     W1 [10240,2560] + b1, tanh-GELU, W2 [2560,10240] + b2, residual.  HBM-bound at M=64 (210 MB of weights)."""
@@ -360,10 +382,11 @@ def phi2_mlp_bench(dev, torch, stream):
                                nn.Linear(t(g.standard_normal((ffn, d), dtype=np.float32) * np.float32(0.02)), t(np.zeros(ffn, np.float32))),
                                nn.Linear(t(g.standard_normal((d, ffn), dtype=np.float32) * np.float32(0.02)), t(np.zeros(d, np.float32))))
     us = _lazy_forward_us(torch, stream, lambda: blk.schedule(x).resolve(), 50)
+    dev_us = _lazy_forward_device_us(torch, stream, lambda: blk.schedule(x).resolve(), 50)
     nbytes = 2 * ffn * d * 4 + 4 * 64 * d * 4
     flops = 2.0 * 64 * d * ffn * 2
     peak, kind = measured_peak()
-    return {"us_per_forward": us, "algorithmic_bytes": nbytes, "gbs": nbytes / us * 1e-3, "frac_of_hbm_peak": nbytes / us * 1e-3 / peak,
+    return {"us_per_forward": us, "device_us_per_forward": dev_us, "algorithmic_bytes": nbytes, "gbs": nbytes / us * 1e-3, "frac_of_hbm_peak": nbytes / us * 1e-3 / peak,
             "peak_kind": f"of {kind}", "tflops": flops / us * 1e-6, "note": "weights (210 MB) exceed L2; lazy graph build + resolve each forward"}
 
 
@@ -431,13 +454,14 @@ def whisper_encoder_bench(dev, torch, stream, mode="f32"):
     enc.schedule(mel).resolve()
     launches = dev.launches - l0
     us = _lazy_forward_us(torch, stream, lambda: enc.schedule(mel).resolve(), 20)
+    dev_us = _lazy_forward_device_us(torch, stream, lambda: enc.schedule(mel).resolve(), 20)
     # flops: conv stem + per block (4 projections, QK^T, PV, two MLP matmuls)
     flops = 2.0 * 3000 * d * 80 * 3 + 2.0 * n_ctx * d * d * 3 + 4 * (2.0 * n_ctx * d * d * 4 + 2 * 2.0 * n_ctx * n_ctx * d + 2 * 2.0 * n_ctx * d * mlp)
     what = {"f32": "f32 activations and weights",
             "q8f": "f32 activations, Q8_0F Linear weights (dequantised into pooled scratch, then the f32 tensor-core GEMM)",
             "q8h": "f16 activations, Q8_0H Linear weights (tcgen05 f16 GEMM)"}[mode]
     score_mb = 6 * n_ctx * n_ctx * (2 if mode == "q8h" else 4) * 3 / 1e6
-    return {"us_per_forward": us, "kernels_per_forward": int(launches), "tflops": flops / us * 1e-6,
+    return {"us_per_forward": us, "device_us_per_forward": dev_us, "kernels_per_forward": int(launches), "tflops": flops / us * 1e-6,
             "note": what + f"; mixed launch- and compute-bound ({score_mb:.0f} MB of 1500x1500 score matrices per layer pass through L2)"}
 
 
@@ -561,9 +585,11 @@ def phi3_decode_bench(dev, torch, stream, steps, warmup, rank=0, world=1, dist=N
 
 
 def sharded_decode_check(dev, torch, rank, world, dist):
-    """Two Phi-3-mini layers at full width, three greedy steps: the sharded decoder's logits must equal the
-    single-GPU decoder's bit for bit on every rank (each output element is computed by one rank with the
-    single-GPU arithmetic).  Run outside every timed region."""
+    """Two Phi-3-mini layers at full width, three greedy steps: the sharded decoder's logits against the
+    single-GPU decoder's on every rank.  Each output element is computed by one rank with the single-GPU
+    arithmetic, so where both take the same kernels (up to four ranks) the logits are equal bit for bit; on
+    eight ranks the sharded step runs one kernel per phase, whose GEMVs sum in another order, and the
+    comparison is the quantised-matmul bar (1e-2 of the logits' scale).  Run outside every timed region."""
     from ratchet_b200 import capi
     from ratchet_b200.comm import Comm, decoder_shard_ranges, take_rows_q8
     from ratchet_b200.decoder import Decoder, DecoderConfig, DecoderLayer
@@ -618,12 +644,16 @@ def sharded_decode_check(dev, torch, rank, world, dist):
     shard = build(True, comm)
     got = run(shard)
     same = all(np.array_equal(a.view(np.uint16), b.view(np.uint16)) for a, b in zip(got, ref))
+    rel = max(float(np.abs(a.astype(np.float32) - b.astype(np.float32)).max() / np.sqrt(np.mean(b.astype(np.float32) ** 2))) for a, b in zip(got, ref))
     flag = torch.tensor([1 if same else 0], dtype=torch.int32, device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    worst = torch.tensor([rel], dtype=torch.float64, device="cuda")
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     dist.barrier()
     shard.close()
     comm.close()
-    return {"sharded_logits_equal_single_gpu_bits": bool(int(flag.item())), "layers": L, "steps": 3, "ranks": world}
+    return {"sharded_logits_equal_single_gpu_bits": bool(int(flag.item())), "max_abs_diff_over_rms": float(worst.item()),
+            "within_1e-2": bool(float(worst.item()) <= 1e-2), "layers": L, "steps": 3, "ranks": world}
 
 
 def run_ours(args):

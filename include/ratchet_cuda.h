@@ -87,12 +87,16 @@ uint64_t rcu_launch_count(rcu_device* dev);
 int rcu_sm_count(rcu_device* dev);
 
 /* Debug switches of a device (also read from the environment when the device is created: RCU_NO_REUSE=1,
- * RCU_PROFILE=1).  RCU_DEBUG_NO_REUSE: the lazy resolver gives every tensor a buffer of its own and runs nothing
+ * RCU_PROFILE=1, RCU_LOG=1).  RCU_DEBUG_NO_REUSE: the lazy resolver gives every tensor a buffer of its own and runs nothing
  * in place (the reference's RATCHET_DEBUG, gpu/buffer_allocator/allocator.rs:121).  RCU_DEBUG_PROFILE: the lazy
  * resolver brackets every node with an event pair and blocks at the end of each resolve, filling a per-op table
- * (the reference's `gpu-profiling` feature, gpu/profiler.rs:95-237, executable.rs:140-179). */
+ * (the reference's `gpu-profiling` feature, gpu/profiler.rs:95-237, executable.rs:140-179).  RCU_DEBUG_LOG: every
+ * resolve writes one line per launching node (op, dtype, shape, in place or not) and a summary (nodes, launches,
+ * buffers, planned against unshared bytes) to stderr, where the reference logs its kernel keys and allocation totals
+ * (op.rs:312, gpu/buffer_allocator/allocator.rs:330-337). */
 #define RCU_DEBUG_NO_REUSE 1u
 #define RCU_DEBUG_PROFILE 2u
+#define RCU_DEBUG_LOG 4u
 rcu_status rcu_set_debug(rcu_device* dev, uint32_t flags);
 /* The per-op table as text — kernel key (op and operand dtype), count, total microseconds, share, GB/s over the
  * operands' bytes — sorted by time.  Returns the bytes needed (with the terminator); writes at most `capacity`.

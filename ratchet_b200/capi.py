@@ -31,7 +31,7 @@ BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3}
 UNARY_OPS = {"gelu": 0, "tanh": 1, "exp": 2, "log": 3, "sin": 4, "cos": 5, "abs": 6, "sqrt": 7, "relu": 8, "floor": 9,
              "ceil": 10, "neg": 11, "silu": 12, "sigmoid": 13}
 LAYER_NORM, RMS_NORM, GROUP_NORM = 0, 1, 2
-DEBUG_NO_REUSE, DEBUG_PROFILE = 1, 2
+DEBUG_NO_REUSE, DEBUG_PROFILE, DEBUG_LOG = 1, 2, 4
 REDUCE_SUM, REDUCE_MAX, REDUCE_MEAN = 0, 1, 2
 
 

@@ -774,8 +774,12 @@ void setup_flow(rcu_decoder* d) {
     const int H = (int)c.n_heads, Hl = H / W, Hkvl = (int)c.n_kv_heads / W;
     const int qkv_nl = (Hl + 2 * Hkvl) * HD, A = H * HD;
     const int ss = c.weight_dt == RCU_Q8_0H ? 2 : 4;
-    static const bool off = [] { const char* e = std::getenv("RCU_DECODE_FLOW"); return e && std::atoi(e) == 0; }();
-    if (off) return;
+    // RCU_DECODE_FLOW=0 forces the kernel-per-phase step, =1 the data-flow kernel wherever it is eligible.  By default
+    // eight ranks and more take the kernel-per-phase step: a rank then streams only 2 us of weights per layer, and what
+    // one persistent kernel saves on launches no longer pays for its hand-overs across NVLink (measured on Phi-3-mini:
+    // 821 tokens/s for the data-flow kernel on 8 ranks against 964; on 4 ranks 948 against 941).
+    static const int mode = [] { const char* e = std::getenv("RCU_DECODE_FLOW"); return e ? std::atoi(e) : -1; }();
+    if (mode == 0 || (mode < 0 && W >= 8)) return;
     int coop = 0;
     if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal) != cudaSuccess || !coop) return;
     const int grid = dev->sm_count;

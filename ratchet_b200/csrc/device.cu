@@ -46,6 +46,7 @@ static rcu_status create_common(int ordinal, cudaStream_t stream, bool own, rcu_
     }
     if (const char* e = std::getenv("RCU_NO_REUSE")) dev->debug_flags |= std::atoi(e) ? RCU_DEBUG_NO_REUSE : 0;
     if (const char* e = std::getenv("RCU_PROFILE")) dev->debug_flags |= std::atoi(e) ? RCU_DEBUG_PROFILE : 0;
+    if (const char* e = std::getenv("RCU_LOG")) dev->debug_flags |= std::atoi(e) ? RCU_DEBUG_LOG : 0;
     cudaMemsetAsync(dev->d_status, 0, kStatusBlockBytes, dev->stream);
     cudaMemcpyAsync(reinterpret_cast<char*>(dev->d_status) + 8, &dev->wait_limit_ns, 8, cudaMemcpyHostToDevice, dev->stream);
     cudaStreamSynchronize(dev->stream);

@@ -23,6 +23,8 @@
 #include <memory>
 #include <unordered_set>
 
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace {
@@ -297,6 +299,7 @@ rcu_status resolve(rcu_lazy* out) {
     // of its own and nothing runs in place, so a wrong result that goes away points at the planner.
     const bool no_reuse = (dev->debug_flags & RCU_DEBUG_NO_REUSE) != 0;
     const bool profile = (dev->debug_flags & RCU_DEBUG_PROFILE) != 0;
+    const bool log = (dev->debug_flags & RCU_DEBUG_LOG) != 0;
 
     // how many references to each node come from inside this graph
     std::unordered_map<uint64_t, uint32_t> internal_refs;
@@ -399,6 +402,11 @@ rcu_status resolve(rcu_lazy* out) {
         if (!t->storage) return rcu_fail(dev, RCU_ERR_INVALID_ARG, "resolve: tensor %llu has no storage", (unsigned long long)t->id);   // TensorError::NoStorage
         if (t->kind == K_VIEW || t->kind == K_CONST) continue;
         if (inplace[i]) ++n_inplace;
+        if (log) {
+            std::fprintf(stderr, "[rcu] node %llu %s %s [", (unsigned long long)t->id, kind_name(t->kind), dt_name(t->dt));
+            for (uint32_t a = 0; a < t->rank; ++a) std::fprintf(stderr, a ? ", %llu" : "%llu", (unsigned long long)t->shape[a]);
+            std::fprintf(stderr, "]%s\n", inplace[i] ? " in place" : "");
+        }
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         if (profile) {
             // one event pair per node, as the reference's timestamp-query pairs (gpu/profiler.rs:95-133)
@@ -436,6 +444,9 @@ rcu_status resolve(rcu_lazy* out) {
     dev->last_resolve.planned_bytes = planned;
     dev->last_resolve.naive_bytes = naive;
     (void)launched;
+    if (log)
+        std::fprintf(stderr, "[rcu] resolve: %zu nodes, %u launches, %u in place, %zu buffers, %llu bytes planned (%llu unshared)\n", n,
+                     dev->last_resolve.launched, n_inplace, objects.size(), (unsigned long long)planned, (unsigned long long)naive);
     return RCU_OK;
 }
 

@@ -188,10 +188,11 @@ class Device:
         self.check(self._lib.rcu_dequantize(self.handle, self._ref(src), self._ref(out)))
         return out
 
-    def set_debug(self, no_reuse: bool = False, profile: bool = False) -> None:
+    def set_debug(self, no_reuse: bool = False, profile: bool = False, log: bool = False) -> None:
         """Debug switches of the lazy resolver: one buffer per tensor and nothing in place (the reference's
         RATCHET_DEBUG), and a per-op timing table (its `gpu-profiling` feature)."""
-        self.check(self._lib.rcu_set_debug(self.handle, (capi.DEBUG_NO_REUSE if no_reuse else 0) | (capi.DEBUG_PROFILE if profile else 0)))
+        self.check(self._lib.rcu_set_debug(self.handle, (capi.DEBUG_NO_REUSE if no_reuse else 0) | (capi.DEBUG_PROFILE if profile else 0) |
+                                            (capi.DEBUG_LOG if log else 0)))
 
     def profile_report(self, reset: bool = True) -> str:
         """The per-op table collected while the profile switch was on: kernel, count, total us, %, GB/s."""

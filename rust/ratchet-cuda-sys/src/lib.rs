@@ -63,6 +63,7 @@ pub const RCU_REDUCE_MAX: c_int = 1;
 pub const RCU_REDUCE_MEAN: c_int = 2;
 pub const RCU_DEBUG_NO_REUSE: u32 = 1;
 pub const RCU_DEBUG_PROFILE: u32 = 2;
+pub const RCU_DEBUG_LOG: u32 = 4;
 
 /// StorageView + storage pointer of a resolved tensor.
 #[repr(C)]

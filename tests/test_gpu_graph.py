@@ -128,8 +128,8 @@ def test_buffer_planning_reuses_memory(dev):
     assert np.allclose(h.to_numpy(), ref, atol=1e-4)
 
 
-def test_debug_switches_no_reuse_and_profile(dev):
-    """The resolver's two debug aids: with no-reuse every tensor gets a buffer of its own and nothing runs in
+def test_debug_switches_no_reuse_and_profile(dev, capfd):
+    """The resolver's debug aids: with no-reuse every tensor gets a buffer of its own and nothing runs in
     place (same results); with profiling every node is bracketed by an event pair and the table names each
     kernel with its count, time and bandwidth."""
     from ratchet_b200 import Tensor, last_resolve_stats
@@ -158,6 +158,13 @@ def test_debug_switches_no_reuse_and_profile(dev):
         assert int(rows["matmul f32"][2]) == 3 and int(rows["unary f32"][2]) == 3
         assert float(rows["matmul f32"][3]) > 0 and abs(float(rows["matmul f32"][4]) + float(rows["unary f32"][4]) - 100.0) < 0.2
         assert dev.profile_report() .count("\n") == 1          # cleared
+        # the log switch: one line per launching node and a summary per resolve, on stderr
+        dev.set_debug(log=True)
+        capfd.readouterr()
+        run()
+        err = capfd.readouterr().err
+        assert err.count("[rcu] node") == 6 and "matmul f32 [64, 256]" in err and "unary f32 [64, 256] in place" in err, err
+        assert "[rcu] resolve: " in err and "6 launches, 3 in place" in err, err
     finally:
         dev.set_debug()
 
