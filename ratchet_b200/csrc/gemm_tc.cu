@@ -58,7 +58,7 @@ __host__ __device__ constexpr int conv_warps(int bn) { return bn >= 128 ? 8 : 4;
 template <int BN, int WK, int STAGES>
 __global__ void __launch_bounds__(WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QuantArgs qa,
-               const __half* __restrict__ bias, __half* __restrict__ out, int M, int N, int K, int* status) {
+               const __half* __restrict__ bias, __half* __restrict__ out, int M, int N, int K, int* status, int splits, float* __restrict__ partial) {
     constexpr int A_BYTES = TM * TK * 2;          // 16 KiB
     constexpr int B_BYTES = BN * TK * 2;
     constexpr int STAGE = A_BYTES + B_BYTES;
@@ -76,8 +76,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * BN;
-    const int nk = (K + TK - 1) / TK;
-    const int bz = blockIdx.z;                       // independent problem (batched f16 products); 0 otherwise
+    // blockIdx.z is an independent problem (batched f16 products), or - splits > 1 - a slice of K: the CTA then runs
+    // k-steps [it_base, it_base + nk) and leaves f32 partial sums for sum_k_slices_kernel
+    const int nk_all = (K + TK - 1) / TK;
+    const int nk_per = splits > 1 ? (((nk_all + splits - 1) / splits + 3) & ~3) : nk_all;     // whole Q4_K super-blocks per slice
+    const int sp = splits > 1 ? (int)blockIdx.z : 0;
+    const int it_base = sp * nk_per;
+    const int nk = max(0, min(nk_all - it_base, nk_per));
+    const int bz = splits > 1 ? 0 : (int)blockIdx.z;
     out += (size_t)bz * M * N;
 
     if (threadIdx.x == 0) {
@@ -108,12 +114,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 unsigned char* st = smem + s * STAGE;
                 if (WK == WK_F16) {
                     mbar_expect_tx(&full[s], STAGE);
-                    tma_load_3d(st, &xmap, it * TK, m0, bz, &full[s]);             // activations: rows m0.., k it*64..
-                    tma_load_3d(st + A_BYTES, &wmap, it * TK, n0, bz, &full[s]);   // weights: rows n0..
+                    tma_load_3d(st, &xmap, (it_base + it) * TK, m0, bz, &full[s]);             // activations: rows m0.., k it*64..
+                    tma_load_3d(st + A_BYTES, &wmap, (it_base + it) * TK, n0, bz, &full[s]);   // weights: rows n0..
                 } else {
                     mbar_expect_tx(&raw_full[s], A_BYTES + RAW_BYTES);
-                    tma_load_3d(st, &xmap, it * TK, m0, 0, &raw_full[s]);
-                    tma_load_2d(st + STAGE - RAW_BYTES, &wmap, it * RAW_ROW, n0, &raw_full[s]);   // packed bytes of 64 weights per row
+                    tma_load_3d(st, &xmap, (it_base + it) * TK, m0, 0, &raw_full[s]);
+                    tma_load_2d(st + STAGE - RAW_BYTES, &wmap, (it_base + it) * RAW_ROW, n0, &raw_full[s]);   // packed bytes of 64 weights per row
                 }
             }
         }
@@ -149,7 +155,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-                if (row < M) {
+                if (row < M && splits > 1) {         // a K slice: f32 partial sums, bias and rounding in the summing kernel (N % 8 == 0)
+                    float* prow = partial + ((size_t)sp * M + row) * N + n0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        if (n0 + c + j + 4 <= N) *reinterpret_cast<float4*>(prow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else if (row < M) {
                     __half* orow = out + (size_t)row * N + n0 + c;
                     if ((N & 7) == 0) {              // rows start on 16-byte boundaries
 #pragma unroll
@@ -216,9 +227,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         for (int t = 0; t < TPT; ++t) {
             if (WK == WK_Q8) {
 #pragma unroll
-                for (int p = 0; p < PF; ++p) q8_queue[p][t] = q8_fetch(p, t);
+                for (int p = 0; p < PF; ++p) q8_queue[p][t] = q8_fetch(it_base + p, t);
             } else {
-                q4_fetch(0, t, pk_next[t], dd_next[t]);
+                q4_fetch(it_base >> 2, t, pk_next[t], dd_next[t]);
             }
         }
         bool stop = false;
@@ -228,7 +239,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             const int it = it0 + u;
             if (it >= nk || stop) break;
             const int s = it % STAGES;
-            const int k0 = it * TK;
+            const int itg = it_base + it;                // k-step of the whole problem
+            const int k0 = itg * TK;
             __half2 mul2[TPT], neg2[TPT];
             bool valid[TPT];
 #pragma unroll
@@ -239,17 +251,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 neg2[t] = __float2half2_rn(0.f);
                 if (WK == WK_Q8) {
                     mul2[t] = __half2half2(q8_queue[u][t]);
-                    q8_queue[u][t] = q8_fetch(it + PF, t);     // consumed PF stages from now
+                    q8_queue[u][t] = q8_fetch(itg + PF, t);    // consumed PF stages from now
                 } else {
-                    if ((it & 3) == 0) {
+                    if ((itg & 3) == 0) {
 #pragma unroll
                         for (int i = 0; i < 3; ++i) pk_cur[t][i] = pk_next[t][i];
                         dd_cur[t][0] = dd_next[t][0];
                         dd_cur[t][1] = dd_next[t][1];
-                        q4_fetch((it >> 2) + 1, t, pk_next[t], dd_next[t]);
+                        q4_fetch((itg >> 2) + 1, t, pk_next[t], dd_next[t]);
                     }
                     const uint32_t* w = pk_cur[t];
-                    const int j = (it & 3) * 2 + h;
+                    const int j = (itg & 3) * 2 + h;
                     uint32_t sc, mn;
                     if (j < 4) {                                   // quantized.rs:158-204
                         sc = pack_byte(w, j) & 63u;
@@ -317,6 +329,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     }
 }
 
+// out[m, n] = f16(sum over slices, in order, of partial[s, m, n] + bias[n]); eight outputs per thread
+__global__ void __launch_bounds__(256) sum_k_slices_kernel(const float* __restrict__ partial, const __half* __restrict__ bias, __half* __restrict__ out,
+                                                          size_t MN, int N, int splits) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i >= MN) return;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(partial + (size_t)s * MN + i), b = *reinterpret_cast<const float4*>(partial + (size_t)s * MN + i + 4);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    __align__(16) __half h[8];
+    const int col = (int)(i % (size_t)N);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) h[e] = __float2half_rn(acc[e] + (bias ? __half2float(bias[col + e]) : 0.f));
+    *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(h);
+}
+
 template <int BN, int WK>
 rcu_status launch_tc(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const QuantArgs& qa, const void* bias, void* out,
                      int M, int N, int K, int batch = 1) {
@@ -326,8 +358,30 @@ rcu_status launch_tc(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap
     auto kern = gemm_tc_kernel<BN, WK, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batch);
-    kern<<<grid, WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, smem, dev->stream>>>(xmap, wmap, qa, (const __half*)bias, (__half*)out, M, N, K,
-                                                                                      dev->d_status);
+    const int threads = WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32;
+    // Few tiles and a long K (a Linear at a few hundred token rows): every CTA's k loop is a chain of TMA -> convert -> MMA
+    // hand-overs about half a microsecond per step long, so K is cut into slices that run side by side (two CTAs fit an SM).
+    const int nk = (K + TK - 1) / TK;
+    const long long tiles = (long long)grid.x * grid.y;
+    int splits = 1;
+    if (batch == 1 && N % 8 == 0 && tiles <= dev->sm_count && nk >= 16) {
+        splits = (int)std::min<long long>(4, (2ll * dev->sm_count) / tiles);
+        while (splits > 1 && (((nk + splits - 1) / splits + 3) & ~3) * (splits - 1) >= nk) --splits;     // every slice gets k-steps
+    }
+    if (splits > 1) {
+        void* partial = nullptr;
+        rcu_status st = rcu_alloc(dev, (uint64_t)splits * M * N * 4, &partial);
+        if (st != RCU_OK) return st;
+        grid.z = splits;
+        kern<<<grid, threads, smem, dev->stream>>>(xmap, wmap, qa, nullptr, (__half*)out, M, N, K, dev->d_status, splits, (float*)partial);
+        dev->launches++;
+        const size_t MN = (size_t)M * N;
+        sum_k_slices_kernel<<<(unsigned)((MN / 8 + 255) / 256), 256, 0, dev->stream>>>((const float*)partial, (const __half*)bias, (__half*)out, MN, N, splits);
+        rcu_free(dev, partial);      // the pool reuses blocks in stream order
+        RCU_LAUNCH_CHECK(dev);
+        return RCU_OK;
+    }
+    kern<<<grid, threads, smem, dev->stream>>>(xmap, wmap, qa, (const __half*)bias, (__half*)out, M, N, K, dev->d_status, 1, nullptr);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }

@@ -29,7 +29,9 @@ def check(got, ref, tol, what):
 SHAPES = [(128, 256, 256), (512, 512, 1024), (100, 200, 136), (37, 64, 64), (2048, 256, 512), (130, 1032, 3072), (1500, 384, 384),
           # the CTA-pair kernel (at least 37 tiles of 256 x 256): full tiles; ragged M, N and K; more tiles than CTA pairs
           # (persistent loop, both accumulator buffers, the stage ring wrapping across tiles); one k-step only
-          (1024, 2560, 320), (1000, 2504, 328), (2048, 4096, 512), (1300, 5000, 136), (2048, 8192, 64)]
+          (1024, 2560, 320), (1000, 2504, 328), (2048, 4096, 512), (1300, 5000, 136), (2048, 8192, 64),
+          # few tiles and a long K: K is cut into slices (the last one a single k-step) that a second kernel sums
+          (128, 512, 1088), (300, 640, 4096)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -61,7 +63,7 @@ def test_gemm_tc_batched_f16(dev, b, M, K, N, trans_rhs):
 
 
 @pytest.mark.parametrize("kind", ["Q8_0H", "Q4_KH"])
-@pytest.mark.parametrize("M,N,K", [(128, 512, 768), (512, 256, 3072), (77, 96, 512)])
+@pytest.mark.parametrize("M,N,K", [(128, 512, 768), (512, 256, 3072), (77, 96, 512), (64, 512, 2048), (48, 1024, 4096)])
 def test_gemm_tc_quantised(dev, kind, M, N, K):
     from ratchet_b200 import capi
     g = np.random.Generator(np.random.PCG64(M + N + K))
