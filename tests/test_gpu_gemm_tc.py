@@ -30,6 +30,8 @@ SHAPES = [(128, 256, 256), (512, 512, 1024), (100, 200, 136), (37, 64, 64), (204
           # the CTA-pair kernel (at least 37 tiles of 256 x 256): full tiles; ragged M, N and K; more tiles than CTA pairs
           # (persistent loop, both accumulator buffers, the stage ring wrapping across tiles); one k-step only
           (1024, 2560, 320), (1000, 2504, 328), (2048, 4096, 512), (1300, 5000, 136), (2048, 8192, 64),
+          # 88 tiles on 74 pairs (a short last round) with a ragged last N tile
+          (1024, 5600, 320),
           # few tiles and a long K: K is cut into slices (the last one a single k-step) that a second kernel sums
           (128, 512, 1088), (300, 640, 4096)]
 
