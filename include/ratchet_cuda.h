@@ -134,6 +134,14 @@ rcu_status rcu_sync(rcu_device* dev);
  * two seconds.  The reference has no counterpart (its only wait is device.poll).  Applies to kernels
  * launched after the call. */
 rcu_status rcu_set_wait_limit_ns(rcu_device* dev, uint64_t nanoseconds);
+/* A promise about the weight operand (lhs) of the matrix-vector products that follow: on != 0 says that no work
+ * still in flight on this handle's stream writes those buffers (a loaded model's Linear weights,
+ * ratchet-nn/src/linear.rs:10-24).  The GEMV kernels are then launched as programmatic dependents of their
+ * predecessor and request their first weight rows while it drains; activations, bias and output are touched only
+ * after the predecessor has completed, as always.  Off by default: through rcu_matmul the predecessor may be the
+ * kernel that produced the weights.  The lazy resolver switches it on by itself for weights that were uploaded with
+ * rcu_lazy_from_host (resident before the call returned).  No counterpart in the reference. */
+rcu_status rcu_set_constant_weights(rcu_device* dev, int on);
 
 /* ------------------------------------------------------------------ layouts (dtype/blocks.rs) */
 /* DType::segments total: bytes of the single buffer that holds `numel` elements of `dt`. */

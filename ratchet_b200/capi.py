@@ -95,6 +95,7 @@ SIGNATURES = {
     "rcu_memset": (C.c_int, [_DEV, C.c_void_p, C.c_int, C.c_uint64]),
     "rcu_sync": (C.c_int, [_DEV]),
     "rcu_set_wait_limit_ns": (C.c_int, [_DEV, C.c_uint64]),
+    "rcu_set_constant_weights": (C.c_int, [_DEV, C.c_int]),
     "rcu_dtype_nbytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
     "rcu_dtype_segments": (C.c_int, [C.c_int32, C.c_uint64, _u64p]),
     "rcu_activation_dtype": (C.c_int32, [C.c_int32]),

@@ -39,6 +39,7 @@ struct rcu_device {
     rcu_pool pool;
     int* d_status = nullptr;     // device-side status block: [0] bounds / timeout flags raised by kernels, [2..3] wait limit in ns (u64)
     uint64_t wait_limit_ns = 2000000000ull;
+    bool const_weights = false;  // rcu_set_constant_weights: GEMVs may request weight rows before their predecessor ends
     int* h_status = nullptr;     // pinned host mirror
     rcu_resolve_stats last_resolve = {};   // counters of the last lazy-graph resolve (graph.cu)
     uint32_t debug_flags = 0;    // RCU_DEBUG_* (rcu_set_debug; RCU_NO_REUSE / RCU_PROFILE in the environment at creation)

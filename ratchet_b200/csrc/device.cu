@@ -218,6 +218,12 @@ rcu_status rcu_sync(rcu_device* dev) {
     return check_status_word(dev);
 }
 
+rcu_status rcu_set_constant_weights(rcu_device* dev, int on) {
+    if (!dev) return RCU_ERR_INVALID_ARG;
+    dev->const_weights = on != 0;
+    return RCU_OK;
+}
+
 rcu_status rcu_set_wait_limit_ns(rcu_device* dev, uint64_t nanoseconds) {
     if (!dev || nanoseconds == 0) return RCU_ERR_INVALID_ARG;
     DevGuard g(dev->ordinal);

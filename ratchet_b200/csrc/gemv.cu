@@ -127,16 +127,16 @@ rcu_status launch_q8(rcu_device* dev, const int8_t* qs, const void* scales, cons
         // (long streams only: a launch that streams a few MB ends before a ring of 200 KB per SM has paid for its start)
         if (K >= 2048 && (size_t)N * K >= ((size_t)96 << 20)) {
             ringq8::PlainPlanes<ringq8::VecSource> rpro{{(const __half*)x}};
-            const rcu_status st = ringq8::launch<ScaleT>(dev, qs, scales, rpro, epi, N, K, false);
+            const rcu_status st = ringq8::launch<ScaleT>(dev, qs, scales, rpro, epi, N, K, dev->const_weights);
             if (st != RCU_ERR_UNSUPPORTED) return st;
         }
     }
     const int ctas = 3;
     // short streams (tens of MB) gain from the pre-loaded, double-buffered variant; long ones from occupancy
     const bool pipe = (size_t)N * K < (size_t)128 << 20;
-    // No programmatic dependent launch here: the pipelined kernel reads weights before it waits for its
-    // predecessor, and through this entry point the predecessor may be the kernel that produced them.
-    const bool overlap = false;
+    // Programmatic dependent launch only on the caller's word (rcu_set_constant_weights): the kernels read weights
+    // before they wait for their predecessor, and through this entry point the predecessor may have produced them.
+    const bool overlap = dev->const_weights;
     // f16 activations: dp4a on 16-bit fixed-point planes with 16-element scales (the conversions of an f16
     // fma path saturate the XU pipe: 4.4 TB/s against 6.6); f32 activations: exact int8 -> f32 and FFMA.
     constexpr int MODE = sizeof(ActT) == 2 ? 2 : 1;

@@ -67,6 +67,7 @@ struct rcu_lazy {
     uint64_t a[RCU_MAX_RANK] = {0, 0, 0, 0}, b[RCU_MAX_RANK] = {0, 0, 0, 0};   // slice start/stop, index_write start
     float f[2] = {0.f, 0.f};       // eps, rope base
     std::shared_ptr<Storage> storage;
+    bool resident_const = false;   // uploaded from the host and waited for: nothing in flight writes it
 
     bool resolved() const { return storage != nullptr; }
     uint64_t numel() const {
@@ -237,7 +238,12 @@ rcu_status run_node(rcu_lazy* n) {
         case K_MATMUL: {
             rcu_tensor l = S(0), r = S(1), bias;
             if (n->srcs.size() > 2) bias = S(2);
-            return rcu_matmul(dev, &l, &r, n->srcs.size() > 2 ? &bias : nullptr, n->flags[0], n->flags[1], n->flags[2], &dst);
+            // weights that were uploaded and waited for cannot be written by anything in flight: the GEMV may start early
+            const bool before = dev->const_weights;
+            if (n->srcs[0]->resident_const) dev->const_weights = true;
+            const rcu_status st = rcu_matmul(dev, &l, &r, n->srcs.size() > 2 ? &bias : nullptr, n->flags[0], n->flags[1], n->flags[2], &dst);
+            dev->const_weights = before;
+            return st;
         }
         case K_NORM: {
             rcu_tensor x = S(0), sc = S(1), bias;
@@ -473,6 +479,7 @@ rcu_status rcu_lazy_from_host(rcu_device* dev, int32_t dt, uint32_t rank, const 
         // the host buffer is borrowed for the call only: wait for the copy before returning
         if (st == RCU_OK) st = rcu_sync(dev);
         if (st != RCU_OK) { release(n); return st; }
+        n->resident_const = true;
     }
     *out = n;
     return RCU_OK;

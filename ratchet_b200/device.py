@@ -201,6 +201,11 @@ class Device:
         self._lib.rcu_profile_report(self.handle, buf, n, int(reset))
         return buf.value.decode()
 
+    def set_constant_weights(self, on: bool = True) -> None:
+        """Promise that nothing in flight writes the weight operands of the GEMVs that follow (a loaded model's
+        Linear weights): they are then launched as programmatic dependents and start fetching weights early."""
+        self.check(self._lib.rcu_set_constant_weights(self.handle, int(bool(on))))
+
     def set_wait_limit_ns(self, ns: int) -> None:
         """How long a device-side wait may last before it gives up (default two seconds)."""
         self.check(self._lib.rcu_set_wait_limit_ns(self.handle, int(ns)))

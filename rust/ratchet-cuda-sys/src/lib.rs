@@ -154,6 +154,7 @@ extern "C" {
     pub fn rcu_memset(dev: *mut rcu_device, dst: *mut c_void, value: c_int, nbytes: u64) -> rcu_status;
     pub fn rcu_sync(dev: *mut rcu_device) -> rcu_status;
     pub fn rcu_set_wait_limit_ns(dev: *mut rcu_device, nanoseconds: u64) -> rcu_status;
+    pub fn rcu_set_constant_weights(dev: *mut rcu_device, on: c_int) -> rcu_status;
     pub fn rcu_dtype_nbytes(dt: i32, numel: u64) -> u64;
     pub fn rcu_dtype_segments(dt: i32, numel: u64, offsets: *mut u64) -> c_int;
     pub fn rcu_activation_dtype(dt: i32) -> i32;

@@ -109,6 +109,37 @@ def test_gemv_q8(dev, pair, N, K):
         assert_matmul_close(y.to_numpy().reshape(-1), ref, 1e-2 if half_x else 1e-4, f"gemv {pair} {N}x{K}")
 
 
+def test_gemv_back_to_back_with_constant_weights(dev):
+    """The caller's promise that its weights are not being written (rcu_set_constant_weights) lets consecutive
+    GEMVs overlap: each is launched as a programmatic dependent and asks for weight rows before its predecessor
+    has ended, while activations and outputs still wait for it.  A chain y1 = W1 x, y2 = W2 y1, y3 = W3 y2 launched
+    without any synchronisation in between must give what the same chain gives without the promise."""
+    from ratchet_b200 import capi
+    g = rng(99)
+    K = 3072
+    ws = [orc.quantize_q8((g.standard_normal((K, K)) * 0.02).astype(np.float16)) for _ in range(3)]
+    dws = [dev.from_quantized(w, capi.Q8_0H, (K, K)) for w in ws]
+    x = dev.from_numpy(g.standard_normal((1, K)).astype(np.float16))
+
+    def chain():
+        h = x
+        for dw in dws:
+            h = dev.matmul(dw, h, None, False, True, True)
+        return h.to_numpy()
+
+    base = chain()
+    dev.set_constant_weights(True)
+    try:
+        for _ in range(3):
+            assert np.array_equal(chain().view(np.uint16), base.view(np.uint16))
+    finally:
+        dev.set_constant_weights(False)
+    h = x.to_numpy().reshape(-1)
+    for w in ws:
+        h = orc.gemv_q8(w, K, K, True, h).astype(np.float16)
+    assert_matmul_close(base.reshape(-1), h, 2e-2, "chain of three GEMVs")
+
+
 def test_gemv_q8_headline_shape(dev):
     """The benchmark's shape, K = 16384 x N = 65536 with f32 block scales and f16 activations (1.2 GB of
     weights: the plain streaming kernel with its K split of 8).  The matrix is 4096 distinct random rows
