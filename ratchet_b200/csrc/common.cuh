@@ -1,5 +1,6 @@
 // Internal helpers shared by every translation unit of libratchet_cuda.so.
 #pragma once
+#include <cstdlib>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -71,6 +72,33 @@ rcu_status rcu_fail(rcu_device* dev, rcu_status st, const char* fmt, ...);
         (dev)->launches++;                                                                      \
         RCU_CUDA((dev), cudaGetLastError());                                                    \
     } while (0)
+
+// Every kernel of the library begins with this: wait for the kernel before it in the stream (a no-op unless this
+// one was launched as its programmatic dependent), then let the next kernel's blocks be scheduled.  Launched through
+// rcu_launch, consecutive kernels overlap their launch and start-up with the predecessor's tail; nothing of a kernel's
+// own work precedes the wait, so stream order is what the memory sees.
+__device__ __forceinline__ void rcu_kernel_entry() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// kern<<<grid, block, smem, dev->stream>>>(args...) as a programmatic dependent of the kernel before it
+// (RCU_NO_PDL in the environment launches it plainly).  The kernel must call rcu_kernel_entry() first.
+template <class... P, class... A>
+inline cudaError_t rcu_launch(rcu_device* dev, void (*kern)(P...), dim3 grid, dim3 block, size_t smem, A&&... args) {
+    static const bool pdl = std::getenv("RCU_NO_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
 
 struct DevGuard {
     int prev = -1;

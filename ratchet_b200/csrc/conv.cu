@@ -25,6 +25,7 @@ template <class T, int STRIDE>
 __global__ void __launch_bounds__(256)
 conv1d_k3_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
                  int Cin, int Lin, int Cout, int Lout, int pad) {
+    rcu_kernel_entry();
     constexpr int WIN = (TLO - 1) * STRIDE + 3;           // input positions needed by the tile
     __shared__ float xs[TCI][WIN + 1];
     __shared__ float ws[TCI][3][TCO + 1];
@@ -91,6 +92,7 @@ conv1d_k3_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __re
 template <int STRIDE>
 __global__ void __launch_bounds__(256)
 unfold_k3_kernel(const float* __restrict__ x, float* __restrict__ col, int Cin, int Lin, int Lout, int pad) {
+    rcu_kernel_entry();
     constexpr int WIN = 31 * STRIDE + 3;
     __shared__ float win[32][WIN + 1];
     const int l0 = blockIdx.x * 32, ci0 = blockIdx.y * 32;
@@ -139,8 +141,8 @@ extern "C" rcu_status rcu_conv1d(rcu_device* dev, const rcu_tensor* x, const rcu
         const dim3 ugrid((unsigned)((Lout + 31) / 32), (unsigned)((Cin + 31) / 32));
         for (uint64_t b = 0; b < B && st == RCU_OK; ++b) {
             const float* xb = (const float*)x->data + b * Cin * Lin;
-            if (stride == 1) unfold_k3_kernel<1><<<ugrid, 256, 0, dev->stream>>>(xb, (float*)col, (int)Cin, (int)Lin, (int)Lout, (int)padding);
-            else unfold_k3_kernel<2><<<ugrid, 256, 0, dev->stream>>>(xb, (float*)col, (int)Cin, (int)Lin, (int)Lout, (int)padding);
+            if (stride == 1) rcu_launch(dev, unfold_k3_kernel<1>, ugrid, 256, 0, xb, (float*)col, (int)Cin, (int)Lin, (int)Lout, (int)padding);
+            else rcu_launch(dev, unfold_k3_kernel<2>, ugrid, 256, 0, xb, (float*)col, (int)Cin, (int)Lin, (int)Lout, (int)padding);
             st = rcu_gemm_tc_f32_dispatch(dev, col, w->data, nullptr, (float*)dst->data + b * Cout * Lout, Cout, Lout, 3 * Cin, 1, bp);
         }
         rcu_free(dev, col);       // the pool reuses blocks in stream order
@@ -149,7 +151,7 @@ extern "C" rcu_status rcu_conv1d(rcu_device* dev, const rcu_tensor* x, const rcu
             return st;
         }
     }
-#define RCU_CONV(T, S) conv1d_k3_kernel<T, S><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (const T*)w->data, (const T*)bp, (T*)dst->data, (int)Cin, (int)Lin, (int)Cout, (int)Lout, (int)padding)
+#define RCU_CONV(T, S) rcu_launch(dev, conv1d_k3_kernel<T, S>, grid, 256, 0, (const T*)x->data, (const T*)w->data, (const T*)bp, (T*)dst->data, (int)Cin, (int)Lin, (int)Cout, (int)Lout, (int)padding)
     if (x->dt == RCU_F32) { if (stride == 1) RCU_CONV(float, 1); else RCU_CONV(float, 2); }
     else if (x->dt == RCU_F16) { if (stride == 1) RCU_CONV(__half, 1); else RCU_CONV(__half, 2); }
     else return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "conv1d: dtype %d", x->dt);

@@ -83,6 +83,7 @@ __device__ __forceinline__ __half2 gelu_h2(__half2 x) {
 // Two 16-byte vectors per operand are in flight per thread before the first is used.
 template <class T, int V>
 __global__ void __launch_bounds__(256) binary_same_kernel(int op, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t n) {
+    rcu_kernel_entry();
     typedef Vec<T, V> VT;
     const size_t nvec = n / V;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -124,6 +125,7 @@ struct Bcast4 {
 // and repeated.  I is the index type: 32-bit division whenever the vector count allows it.
 template <class T, int V, class I>
 __global__ void __launch_bounds__(256) binary_bcast_kernel(int op, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, size_t nvec, Bcast4 p) {
+    rcu_kernel_entry();
     typedef Vec<T, V> VT;
     const I row_units = (I)(p.d[3] / V);
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -171,6 +173,7 @@ template <> __device__ __forceinline__ Vec<__half, 8> unary_vec<__half, 8, RCU_G
 
 template <class T, int V, int OP>
 __global__ void __launch_bounds__(256) unary_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n) {
+    rcu_kernel_entry();
     typedef Vec<T, V> VT;
     const size_t nvec = n / V;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -190,6 +193,7 @@ __global__ void __launch_bounds__(256) unary_kernel(const T* __restrict__ x, T* 
 
 template <class S, class D, int V>
 __global__ void __launch_bounds__(256) cast_kernel(const S* __restrict__ x, D* __restrict__ out, size_t n) {
+    rcu_kernel_entry();
     const size_t nvec = n / V;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -228,9 +232,9 @@ template <class T>
 rcu_status launch_binary_same(rcu_device* dev, int op, const void* a, const void* b, void* out, size_t n) {
     constexpr int V = 16 / sizeof(T);
     if (aligned16(a) && aligned16(b) && aligned16(out)) {
-        binary_same_kernel<T, V><<<ew_grid(dev, n / V / 2 + 1), 256, 0, dev->stream>>>(op, (const T*)a, (const T*)b, (T*)out, n);
+        rcu_launch(dev, binary_same_kernel<T, V>, ew_grid(dev, n / V / 2 + 1), 256, 0, op, (const T*)a, (const T*)b, (T*)out, n);
     } else {
-        binary_same_kernel<T, 1><<<ew_grid(dev, n / 2 + 1), 256, 0, dev->stream>>>(op, (const T*)a, (const T*)b, (T*)out, n);
+        rcu_launch(dev, binary_same_kernel<T, 1>, ew_grid(dev, n / 2 + 1), 256, 0, op, (const T*)a, (const T*)b, (T*)out, n);
     }
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
@@ -240,9 +244,9 @@ template <class T, int OP>
 rcu_status launch_unary_op(rcu_device* dev, const void* x, void* out, size_t n) {
     constexpr int V = 16 / sizeof(T);
     if (aligned16(x) && aligned16(out)) {
-        unary_kernel<T, V, OP><<<ew_grid(dev, n / V / 2 + 1), 256, 0, dev->stream>>>((const T*)x, (T*)out, n);
+        rcu_launch(dev, unary_kernel<T, V, OP>, ew_grid(dev, n / V / 2 + 1), 256, 0, (const T*)x, (T*)out, n);
     } else {
-        unary_kernel<T, 1, OP><<<ew_grid(dev, n / 2 + 1), 256, 0, dev->stream>>>((const T*)x, (T*)out, n);
+        rcu_launch(dev, unary_kernel<T, 1, OP>, ew_grid(dev, n / 2 + 1), 256, 0, (const T*)x, (T*)out, n);
     }
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
@@ -265,8 +269,8 @@ template <class S, class D>
 rcu_status launch_cast(rcu_device* dev, const void* x, void* out, size_t n) {
     constexpr int V = 4;  // 16-byte vectors on the 4-byte side, 8-byte on the 2-byte side
     const bool ok = (reinterpret_cast<uintptr_t>(x) % (sizeof(S) * V) == 0) && (reinterpret_cast<uintptr_t>(out) % (sizeof(D) * V) == 0);
-    if (ok) cast_kernel<S, D, V><<<ew_grid(dev, n / V / 2 + 1), 256, 0, dev->stream>>>((const S*)x, (D*)out, n);
-    else cast_kernel<S, D, 1><<<ew_grid(dev, n / 2 + 1), 256, 0, dev->stream>>>((const S*)x, (D*)out, n);
+    if (ok) rcu_launch(dev, cast_kernel<S, D, V>, ew_grid(dev, n / V / 2 + 1), 256, 0, (const S*)x, (D*)out, n);
+    else rcu_launch(dev, cast_kernel<S, D, 1>, ew_grid(dev, n / 2 + 1), 256, 0, (const S*)x, (D*)out, n);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -296,8 +300,8 @@ void launch_binary_bcast(rcu_device* dev, int op, const void* a, const void* b, 
     const bool narrow = nvec <= 0xffffffffull;
     const int grid = ew_grid(dev, nvec);
 #define RCU_BCAST(VV)                                                                                                         \
-    if (narrow) binary_bcast_kernel<T, VV, uint32_t><<<grid, 256, 0, dev->stream>>>(op, (const T*)a, (const T*)b, (T*)out, nvec, p); \
-    else binary_bcast_kernel<T, VV, uint64_t><<<grid, 256, 0, dev->stream>>>(op, (const T*)a, (const T*)b, (T*)out, nvec, p)
+    if (narrow) rcu_launch(dev, binary_bcast_kernel<T, VV, uint32_t>, grid, 256, 0, op, (const T*)a, (const T*)b, (T*)out, nvec, p); \
+    else rcu_launch(dev, binary_bcast_kernel<T, VV, uint64_t>, grid, 256, 0, op, (const T*)a, (const T*)b, (T*)out, nvec, p)
     if (v == VMAX) { RCU_BCAST(VMAX); }
     else if (v >= 2 && VMAX >= 4 && v == VMAX / 2) { RCU_BCAST((VMAX >= 4 ? VMAX / 2 : 1)); }
     else if (v >= 2) { RCU_BCAST(2); }

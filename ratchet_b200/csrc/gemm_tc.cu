@@ -59,6 +59,7 @@ template <int BN, int WK, int STAGES>
 __global__ void __launch_bounds__(WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QuantArgs qa,
                const __half* __restrict__ bias, __half* __restrict__ out, int M, int N, int K, int* status, int splits, float* __restrict__ partial) {
+    rcu_kernel_entry();
     constexpr int A_BYTES = TM * TK * 2;          // 16 KiB
     constexpr int B_BYTES = BN * TK * 2;
     constexpr int STAGE = A_BYTES + B_BYTES;
@@ -332,6 +333,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 // out[m, n] = f16(sum over slices, in order, of partial[s, m, n] + bias[n]); eight outputs per thread
 __global__ void __launch_bounds__(256) sum_k_slices_kernel(const float* __restrict__ partial, const __half* __restrict__ bias, __half* __restrict__ out,
                                                           size_t MN, int N, int splits) {
+    rcu_kernel_entry();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= MN) return;
     float acc[8];
@@ -373,15 +375,15 @@ rcu_status launch_tc(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap
         rcu_status st = rcu_alloc(dev, (uint64_t)splits * M * N * 4, &partial);
         if (st != RCU_OK) return st;
         grid.z = splits;
-        kern<<<grid, threads, smem, dev->stream>>>(xmap, wmap, qa, nullptr, (__half*)out, M, N, K, dev->d_status, splits, (float*)partial);
+        rcu_launch(dev, kern, grid, threads, smem, xmap, wmap, qa, nullptr, (__half*)out, M, N, K, dev->d_status, splits, (float*)partial);
         dev->launches++;
         const size_t MN = (size_t)M * N;
-        sum_k_slices_kernel<<<(unsigned)((MN / 8 + 255) / 256), 256, 0, dev->stream>>>((const float*)partial, (const __half*)bias, (__half*)out, MN, N, splits);
+        rcu_launch(dev, sum_k_slices_kernel, (unsigned)((MN / 8 + 255) / 256), 256, 0, (const float*)partial, (const __half*)bias, (__half*)out, MN, N, splits);
         rcu_free(dev, partial);      // the pool reuses blocks in stream order
         RCU_LAUNCH_CHECK(dev);
         return RCU_OK;
     }
-    kern<<<grid, threads, smem, dev->stream>>>(xmap, wmap, qa, (const __half*)bias, (__half*)out, M, N, K, dev->d_status, 1, nullptr);
+    rcu_launch(dev, kern, grid, threads, smem, xmap, wmap, qa, (const __half*)bias, (__half*)out, M, N, K, dev->d_status, 1, nullptr);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }

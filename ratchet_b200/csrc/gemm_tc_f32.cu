@@ -62,6 +62,7 @@ __global__ void __launch_bounds__(kThreadsF32, 1)
 gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ bias,
                    const float* __restrict__ bias_rows,
                    float* __restrict__ out, int M, int N, int K, int kb_per_split, int* status) {
+    rcu_kernel_entry();
     constexpr int A_BYTES = TM * TK32 * 4;        // 16 KiB
     constexpr int B_BYTES = BN * TK32 * 4;
     constexpr int RAW = A_BYTES + B_BYTES;        // hi tiles (A then B); the lo tiles follow in the same order
@@ -225,6 +226,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 __global__ void __launch_bounds__(256)
 sum_splits_kernel(const float4* __restrict__ part, int splits, size_t slab4, const float* __restrict__ bias,
                   const float* __restrict__ bias_rows, float4* __restrict__ out, int N4) {
+    rcu_kernel_entry();
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < slab4; i += (size_t)gridDim.x * 256) {
         float4 a = part[i];
         for (int s = 1; s < splits; ++s) {
@@ -252,7 +254,7 @@ rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMa
     auto kern = gemm_tc_f32_kernel<BN, STAGES>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batches);
-    kern<<<grid, kThreadsF32, smem, dev->stream>>>(xmap, wmap, (const float*)bias, (const float*)bias_rows, (float*)out, M, N, K, kb_per_split, dev->d_status);
+    rcu_launch(dev, kern, grid, kThreadsF32, smem, xmap, wmap, (const float*)bias, (const float*)bias_rows, (float*)out, M, N, K, kb_per_split, dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -314,7 +316,7 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
         if (st == RCU_OK) {
             const size_t slab4 = (size_t)(M * N / 4);
             const int grid = (int)std::min<size_t>((slab4 + 255) / 256, (size_t)dev->sm_count * 8);
-            sum_splits_kernel<<<grid, 256, 0, dev->stream>>>((const float4*)part, (int)splits, slab4, (const float*)bias, (const float*)bias_rows,
+            rcu_launch(dev, sum_splits_kernel, grid, 256, 0, (const float4*)part, (int)splits, slab4, (const float*)bias, (const float*)bias_rows,
                                                              (float4*)y, (int)(N / 4));
             RCU_LAUNCH_CHECK(dev);
         }

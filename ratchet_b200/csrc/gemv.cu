@@ -17,6 +17,7 @@ template <class T, int ROWS, int KSPLIT, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 gemv_float_kernel(const T* __restrict__ Wm, const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ y,
                   int N, int K) {
+    rcu_kernel_entry();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* xs = reinterpret_cast<T*>(smem_raw);
     float* red = reinterpret_cast<float*>(smem_raw + (((size_t)K * sizeof(T) + 15) / 16) * 16);
@@ -153,7 +154,7 @@ rcu_status launch_float(rcu_device* dev, const void* Wm, const void* x, const vo
     case KS: {                                                                                             \
         auto kern = gemv_float_kernel<T, ROWS, KS, UNROLL>;                                                \
         if (smem > 48 * 1024) RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kern<<<p.grid, kThreads, smem, dev->stream>>>((const T*)Wm, (const T*)x, (const T*)bias, (T*)y, N, K); \
+        rcu_launch(dev, kern, p.grid, kThreads, smem, (const T*)Wm, (const T*)x, (const T*)bias, (T*)y, N, K); \
         break;                                                                                             \
     }
     switch (p.ksplit) {

@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(kThreadsQ4, 2)
 gemv_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scales, const FP* __restrict__ dmin,
                 const FP* __restrict__ d, const ActT* __restrict__ x, const ActT* __restrict__ bias, ActT* __restrict__ y,
                 int N, int K) {
+    rcu_kernel_entry();
     constexpr int P = sizeof(ActT) == 4 ? 3 : 2;                   // byte planes of the fixed-point activations
     constexpr float kXmax = P == 3 ? 8388607.f : 32767.f;
     extern __shared__ __align__(16) unsigned char smem_q4[];
@@ -326,7 +327,7 @@ rcu_status launch_q4k(rcu_device* dev, const void* w, const void* x, const void*
     case KS: {                                                                                                             \
         auto kern = gemv_q4k_kernel<FP, ActT, KS>;                                                                         \
         if (smem > 48 * 1024) RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kern<<<grid, kThreadsQ4, smem, dev->stream>>>(base, base + off[1], (const FP*)(base + off[2]), (const FP*)(base + off[3]), \
+        rcu_launch(dev, kern, grid, kThreadsQ4, smem, base, base + off[1], (const FP*)(base + off[2]), (const FP*)(base + off[3]), \
                                                       (const ActT*)x, (const ActT*)bias, (ActT*)y, N, K);                  \
         break;                                                                                                             \
     }

@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(ALoad A, const BT* __restrict__ B, const BT* __restrict__ bias, BT* __restrict__ C, int M, int N, int K,
                  long long a_rs, long long a_cs, long long a_ss, long long b_rs, long long b_cs, long long b_ss,
                  long long c_rs, long long c_cs, long long c_ss, int bias_on_rows) {
+    rcu_kernel_entry();
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -189,7 +190,7 @@ rcu_status launch_simt(rcu_device* dev, ALoad A, const void* B, const void* bias
     RCU_REQUIRE(dev, d.dstack <= 65535, "matmul: more than 65535 stacks");
     dim3 grid((unsigned)((d.n + BN - 1) / BN), (unsigned)((d.m + BM - 1) / BM), (unsigned)d.dstack);
     RCU_REQUIRE(dev, grid.y <= 65535, "matmul: M too large for the SIMT kernel");
-    gemm_simt_kernel<ALoad, BT><<<grid, 256, 0, dev->stream>>>(A, (const BT*)B, (const BT*)bias, (BT*)C, (int)d.m, (int)d.n,
+    rcu_launch(dev, gemm_simt_kernel<ALoad, BT>, grid, 256, 0, A, (const BT*)B, (const BT*)bias, (BT*)C, (int)d.m, (int)d.n,
                                                                (int)d.k, a_rs, a_cs, a_ss, b_rs, b_cs, b_ss, c_rs, c_cs,
                                                                c_ss, td ? 1 : 0);
     RCU_LAUNCH_CHECK(dev);

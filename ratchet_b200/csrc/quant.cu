@@ -27,6 +27,7 @@ template <> struct Pack8<float> {
 template <class ScaleT>
 __global__ void __launch_bounds__(256)
 dequant_q8_kernel(const uint2* __restrict__ q, const ScaleT* __restrict__ d, ScaleT* __restrict__ out, size_t n8) {
+    rcu_kernel_entry();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
         const uint2 w = q[i];
@@ -59,6 +60,7 @@ template <class FP>
 __global__ void __launch_bounds__(256)
 dequant_q4k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ scales, const FP* __restrict__ dmin,
                    const FP* __restrict__ d, FP* __restrict__ out, size_t nthreads) {
+    rcu_kernel_entry();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nthreads; i += stride) {
         const size_t b = i >> 4;
@@ -115,14 +117,14 @@ extern "C" rcu_status rcu_dequantize(rcu_device* dev, const rcu_tensor* src, rcu
         RCU_REQUIRE(dev, n % 32 == 0, "dequantize: Q8_0 needs a multiple of 32 elements");   // quant.rs:102-103
         const size_t n8 = n / 8;
         const int grid = (int)std::min<size_t>((n8 + 255) / 256, (size_t)cap);
-        if (src->dt == RCU_Q8_0F) dequant_q8_kernel<float><<<grid, 256, 0, dev->stream>>>((const uint2*)base, (const float*)(base + off[1]), (float*)dst->data, n8);
-        else dequant_q8_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint2*)base, (const __half*)(base + off[1]), (__half*)dst->data, n8);
+        if (src->dt == RCU_Q8_0F) rcu_launch(dev, dequant_q8_kernel<float>, grid, 256, 0, (const uint2*)base, (const float*)(base + off[1]), (float*)dst->data, n8);
+        else rcu_launch(dev, dequant_q8_kernel<__half>, grid, 256, 0, (const uint2*)base, (const __half*)(base + off[1]), (__half*)dst->data, n8);
     } else {
         RCU_REQUIRE(dev, n % 256 == 0, "dequantize: Q4_K needs a multiple of 256 elements");
         const size_t nsub = n / 16;
         const int grid = (int)std::min<size_t>((nsub + 255) / 256, (size_t)cap);
-        if (src->dt == RCU_Q4_KF) dequant_q4k_kernel<float><<<grid, 256, 0, dev->stream>>>((const uint8_t*)base, (const uint8_t*)base + off[1], (const float*)(base + off[2]), (const float*)(base + off[3]), (float*)dst->data, nsub);
-        else dequant_q4k_kernel<__half><<<grid, 256, 0, dev->stream>>>((const uint8_t*)base, (const uint8_t*)base + off[1], (const __half*)(base + off[2]), (const __half*)(base + off[3]), (__half*)dst->data, nsub);
+        if (src->dt == RCU_Q4_KF) rcu_launch(dev, dequant_q4k_kernel<float>, grid, 256, 0, (const uint8_t*)base, (const uint8_t*)base + off[1], (const float*)(base + off[2]), (const float*)(base + off[3]), (float*)dst->data, nsub);
+        else rcu_launch(dev, dequant_q4k_kernel<__half>, grid, 256, 0, (const uint8_t*)base, (const uint8_t*)base + off[1], (const __half*)(base + off[2]), (const __half*)(base + off[3]), (__half*)dst->data, nsub);
     }
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;

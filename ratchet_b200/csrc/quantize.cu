@@ -96,6 +96,7 @@ void for_block_ranges(uint64_t n_blocks, const Fn& fn) {
 // One thread per packed word; the eight threads of a block share its maximum through shuffles.
 template <bool HALF>
 __global__ void quantize_q8_kernel(const void* __restrict__ src, uint64_t n_words, uint32_t* __restrict__ codes, void* __restrict__ scales) {
+    rcu_kernel_entry();
     const uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = w < n_words;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -172,8 +173,8 @@ rcu_status rcu_quantize_device(rcu_device* dev, const rcu_tensor* src, rcu_tenso
     const unsigned grid = (unsigned)((n_words + 255) / 256);
     uint32_t* codes = reinterpret_cast<uint32_t*>(dst->data);
     void* scales = reinterpret_cast<char*>(dst->data) + off[1];
-    if (half) quantize_q8_kernel<true><<<grid, 256, 0, dev->stream>>>(src->data, n_words, codes, scales);
-    else quantize_q8_kernel<false><<<grid, 256, 0, dev->stream>>>(src->data, n_words, codes, scales);
+    if (half) rcu_launch(dev, quantize_q8_kernel<true>, grid, 256, 0, src->data, n_words, codes, scales);
+    else rcu_launch(dev, quantize_q8_kernel<false>, grid, 256, 0, src->data, n_words, codes, scales);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }

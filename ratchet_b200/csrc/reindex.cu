@@ -24,6 +24,7 @@ inline int copy_grid(const rcu_device* dev, size_t work) {
 template <class U, class I>
 __global__ void __launch_bounds__(256)
 copy2d_kernel(const char* __restrict__ src, char* __restrict__ dst, size_t rows, size_t row_units, size_t spitch, size_t dpitch) {
+    rcu_kernel_entry();
     const size_t total = rows * row_units;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const I ru = (I)row_units;
@@ -46,8 +47,8 @@ template <class U>
 void launch_copy2d(rcu_device* dev, const char* s, char* d, size_t rows, size_t row_units, size_t spitch, size_t dpitch) {
     const size_t total = rows * row_units;
     const int grid = copy_grid(dev, total / 2 + 1);
-    if (total <= 0xffffffffull) copy2d_kernel<U, uint32_t><<<grid, 256, 0, dev->stream>>>(s, d, rows, row_units, spitch, dpitch);
-    else copy2d_kernel<U, uint64_t><<<grid, 256, 0, dev->stream>>>(s, d, rows, row_units, spitch, dpitch);
+    if (total <= 0xffffffffull) rcu_launch(dev, copy2d_kernel<U, uint32_t>, grid, 256, 0, s, d, rows, row_units, spitch, dpitch);
+    else rcu_launch(dev, copy2d_kernel<U, uint64_t>, grid, 256, 0, s, d, rows, row_units, spitch, dpitch);
 }
 
 rcu_status copy2d(rcu_device* dev, const void* src, void* dst, size_t rows, size_t row_bytes, size_t spitch, size_t dpitch) {
@@ -74,6 +75,7 @@ struct Remap4 {
 // U is the unit a thread moves (strides, extents and the offset are in units); I the index type.
 template <class U, class I>
 __global__ void __launch_bounds__(256) remap4_kernel(const U* __restrict__ src, U* __restrict__ dst, size_t n, Remap4 p) {
+    rcu_kernel_entry();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         I r = (I)i;
@@ -88,6 +90,7 @@ __global__ void __launch_bounds__(256) remap4_kernel(const U* __restrict__ src, 
 // Innermost axis broadcast (source stride 0): one element read, V copies stored as one vector.
 template <class E, int V, class I>
 __global__ void __launch_bounds__(256) remap4_fill_kernel(const E* __restrict__ src, E* __restrict__ dst, size_t nvec, Remap4 p) {
+    rcu_kernel_entry();
     struct alignas(sizeof(E) * V) VT { E v[V]; };
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const uint32_t row_units = p.d[3] / V;
@@ -109,6 +112,7 @@ __global__ void __launch_bounds__(256) remap4_fill_kernel(const E* __restrict__ 
 // dst[b, c, r] = src[b, r, c].  Used when a permutation swaps the last two (collapsed) axes.
 template <class E>
 __global__ void __launch_bounds__(256) transpose_kernel(const E* __restrict__ src, E* __restrict__ dst, int R, int C) {
+    rcu_kernel_entry();
     __shared__ E tile[32][33];
     const size_t b = blockIdx.z;
     const E* s = src + b * (size_t)R * C;
@@ -127,6 +131,7 @@ __global__ void __launch_bounds__(256) transpose_kernel(const E* __restrict__ sr
 // both pointers aligned to a pair.
 template <class E, class P>
 __global__ void __launch_bounds__(256) transpose_pair_kernel(const E* __restrict__ src, E* __restrict__ dst, int R, int C) {
+    rcu_kernel_entry();
     constexpr int PITCH = sizeof(E) == 2 ? 66 : 65;
     __shared__ E tile[64 * PITCH];
     const size_t b = blockIdx.z;
@@ -162,15 +167,15 @@ __global__ void __launch_bounds__(256) transpose_pair_kernel(const E* __restrict
 
 template <class U>
 void launch_remap(rcu_device* dev, const void* src, void* dst, size_t n, const Remap4& p) {
-    if (n <= 0xffffffffull) remap4_kernel<U, uint32_t><<<copy_grid(dev, n), 256, 0, dev->stream>>>((const U*)src, (U*)dst, n, p);
-    else remap4_kernel<U, uint64_t><<<copy_grid(dev, n), 256, 0, dev->stream>>>((const U*)src, (U*)dst, n, p);
+    if (n <= 0xffffffffull) rcu_launch(dev, remap4_kernel<U, uint32_t>, copy_grid(dev, n), 256, 0, (const U*)src, (U*)dst, n, p);
+    else rcu_launch(dev, remap4_kernel<U, uint64_t>, copy_grid(dev, n), 256, 0, (const U*)src, (U*)dst, n, p);
 }
 
 template <class E>
 void launch_fill(rcu_device* dev, const void* src, void* dst, size_t nvec, const Remap4& p) {
     constexpr int V = 16 / sizeof(E);
-    if (nvec <= 0xffffffffull) remap4_fill_kernel<E, V, uint32_t><<<copy_grid(dev, nvec), 256, 0, dev->stream>>>((const E*)src, (E*)dst, nvec, p);
-    else remap4_fill_kernel<E, V, uint64_t><<<copy_grid(dev, nvec), 256, 0, dev->stream>>>((const E*)src, (E*)dst, nvec, p);
+    if (nvec <= 0xffffffffull) rcu_launch(dev, remap4_fill_kernel<E, V, uint32_t>, copy_grid(dev, nvec), 256, 0, (const E*)src, (E*)dst, nvec, p);
+    else rcu_launch(dev, remap4_fill_kernel<E, V, uint64_t>, copy_grid(dev, nvec), 256, 0, (const E*)src, (E*)dst, nvec, p);
 }
 
 // `p` is in elements of `es` bytes.  When the innermost destination axis is contiguous in the source
@@ -219,6 +224,7 @@ template <class E>
 __global__ void __launch_bounds__(256)
 gather_kernel(const E* __restrict__ src, const int32_t* __restrict__ ids, E* __restrict__ dst, size_t left, size_t n_ids,
               size_t right, size_t src_dim, int* status) {
+    rcu_kernel_entry();
     const size_t total = left * n_ids * right;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -239,6 +245,7 @@ template <class ScaleT>
 __global__ void __launch_bounds__(256)
 gather_q8_kernel(const uint32_t* __restrict__ q, const ScaleT* __restrict__ d, const int32_t* __restrict__ ids,
                  ScaleT* __restrict__ dst, size_t left, size_t n_ids, size_t right, size_t src_dim, int* status) {
+    rcu_kernel_entry();
     // element (l, id, r) of the table has flat index (l*src_dim + id)*right + r; right % 4 == 0 is required
     const size_t right4 = right >> 2;
     const size_t total = left * n_ids * right4;
@@ -269,6 +276,7 @@ template <class U, class I>
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const U* __restrict__ src, const int32_t* __restrict__ ids, U* __restrict__ dst, size_t n_ids, size_t row_units,
                    size_t src_dim, int* status) {
+    rcu_kernel_entry();
     const size_t total = n_ids * row_units;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const I ru = (I)row_units;
@@ -317,6 +325,7 @@ template <class ScaleT>
 __global__ void __launch_bounds__(256)
 gather_q8_rows16_kernel(const uint4* __restrict__ q, const ScaleT* __restrict__ d, const int32_t* __restrict__ ids,
                         ScaleT* __restrict__ dst, size_t n_ids, uint32_t row16, size_t src_dim, int* status) {
+    rcu_kernel_entry();
     const size_t total = n_ids * row16;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -397,15 +406,15 @@ rcu_status rcu_permute(rcu_device* dev, const rcu_tensor* src, const uint32_t* p
                               ((reinterpret_cast<uintptr_t>(src->data) | reinterpret_cast<uintptr_t>(dst->data)) & (pair - 1)) == 0;
         if (pairs_ok && (R + 63) / 64 <= 65535) {
             dim3 g64((C + 63) / 64, (R + 63) / 64, (unsigned)(s4[0] * s4[1]));
-            if (pair == 4) transpose_pair_kernel<uint16_t, uint32_t><<<g64, 256, 0, dev->stream>>>((const uint16_t*)src->data, (uint16_t*)dst->data, R, C);
-            else transpose_pair_kernel<uint32_t, uint2><<<g64, 256, 0, dev->stream>>>((const uint32_t*)src->data, (uint32_t*)dst->data, R, C);
+            if (pair == 4) rcu_launch(dev, transpose_pair_kernel<uint16_t, uint32_t>, g64, 256, 0, (const uint16_t*)src->data, (uint16_t*)dst->data, R, C);
+            else rcu_launch(dev, transpose_pair_kernel<uint32_t, uint2>, g64, 256, 0, (const uint32_t*)src->data, (uint32_t*)dst->data, R, C);
             RCU_LAUNCH_CHECK(dev);
             return RCU_OK;
         }
         dim3 grid((C + 31) / 32, (R + 31) / 32, (unsigned)(s4[0] * s4[1]));
         if (grid.y <= 65535) {
-            if (dt_esize(src->dt) == 2) transpose_kernel<uint16_t><<<grid, 256, 0, dev->stream>>>((const uint16_t*)src->data, (uint16_t*)dst->data, R, C);
-            else transpose_kernel<uint32_t><<<grid, 256, 0, dev->stream>>>((const uint32_t*)src->data, (uint32_t*)dst->data, R, C);
+            if (dt_esize(src->dt) == 2) rcu_launch(dev, transpose_kernel<uint16_t>, grid, 256, 0, (const uint16_t*)src->data, (uint16_t*)dst->data, R, C);
+            else rcu_launch(dev, transpose_kernel<uint32_t>, grid, 256, 0, (const uint32_t*)src->data, (uint32_t*)dst->data, R, C);
             RCU_LAUNCH_CHECK(dev);
             return RCU_OK;
         }
@@ -534,14 +543,14 @@ rcu_status rcu_index_select(rcu_device* dev, const rcu_tensor* src, const rcu_te
         if (left == 1 && right % 16 == 0 && (reinterpret_cast<uintptr_t>(dst->data) & 15) == 0 && right / 16 <= 0xffffffffull) {
             const uint32_t row16 = (uint32_t)(right / 16);
             const int g16 = copy_grid(dev, n_ids * row16);
-            if (src->dt == RCU_Q8_0F) gather_q8_rows16_kernel<float><<<g16, 256, 0, dev->stream>>>((const uint4*)q, (const float*)d, (const int32_t*)ids->data, (float*)dst->data, n_ids, row16, src_dim, dev->d_status);
-            else gather_q8_rows16_kernel<__half><<<g16, 256, 0, dev->stream>>>((const uint4*)q, (const __half*)d, (const int32_t*)ids->data, (__half*)dst->data, n_ids, row16, src_dim, dev->d_status);
+            if (src->dt == RCU_Q8_0F) rcu_launch(dev, gather_q8_rows16_kernel<float>, g16, 256, 0, (const uint4*)q, (const float*)d, (const int32_t*)ids->data, (float*)dst->data, n_ids, row16, src_dim, dev->d_status);
+            else rcu_launch(dev, gather_q8_rows16_kernel<__half>, g16, 256, 0, (const uint4*)q, (const __half*)d, (const int32_t*)ids->data, (__half*)dst->data, n_ids, row16, src_dim, dev->d_status);
             RCU_LAUNCH_CHECK(dev);
             return RCU_OK;
         }
         const int grid = copy_grid(dev, total / 4);
-        if (src->dt == RCU_Q8_0F) gather_q8_kernel<float><<<grid, 256, 0, dev->stream>>>(q, (const float*)d, (const int32_t*)ids->data, (float*)dst->data, left, n_ids, right, src_dim, dev->d_status);
-        else gather_q8_kernel<__half><<<grid, 256, 0, dev->stream>>>(q, (const __half*)d, (const int32_t*)ids->data, (__half*)dst->data, left, n_ids, right, src_dim, dev->d_status);
+        if (src->dt == RCU_Q8_0F) rcu_launch(dev, gather_q8_kernel<float>, grid, 256, 0, q, (const float*)d, (const int32_t*)ids->data, (float*)dst->data, left, n_ids, right, src_dim, dev->d_status);
+        else rcu_launch(dev, gather_q8_kernel<__half>, grid, 256, 0, q, (const __half*)d, (const int32_t*)ids->data, (__half*)dst->data, left, n_ids, right, src_dim, dev->d_status);
         RCU_LAUNCH_CHECK(dev);
         return RCU_OK;
     }
@@ -553,8 +562,8 @@ rcu_status rcu_index_select(rcu_device* dev, const rcu_tensor* src, const rcu_te
         {                                                                                                                                     \
             const size_t ru = row_bytes / sizeof(U);                                                                                          \
             const int gr = copy_grid(dev, n_ids * ru / 2 + 1);                                                                                \
-            if (n_ids * ru <= 0xffffffffull) gather_rows_kernel<U, uint32_t><<<gr, 256, 0, dev->stream>>>((const U*)src->data, (const int32_t*)ids->data, (U*)dst->data, n_ids, ru, src_dim, dev->d_status); \
-            else gather_rows_kernel<U, uint64_t><<<gr, 256, 0, dev->stream>>>((const U*)src->data, (const int32_t*)ids->data, (U*)dst->data, n_ids, ru, src_dim, dev->d_status); \
+            if (n_ids * ru <= 0xffffffffull) rcu_launch(dev, gather_rows_kernel<U, uint32_t>, gr, 256, 0, (const U*)src->data, (const int32_t*)ids->data, (U*)dst->data, n_ids, ru, src_dim, dev->d_status); \
+            else rcu_launch(dev, gather_rows_kernel<U, uint64_t>, gr, 256, 0, (const U*)src->data, (const int32_t*)ids->data, (U*)dst->data, n_ids, ru, src_dim, dev->d_status); \
         }
         if ((bits & 15) == 0) RCU_GATHER_ROWS(uint4)
         else if ((bits & 3) == 0) RCU_GATHER_ROWS(uint32_t)
@@ -564,8 +573,8 @@ rcu_status rcu_index_select(rcu_device* dev, const rcu_tensor* src, const rcu_te
         return RCU_OK;
     }
     const int grid = copy_grid(dev, total);
-    if (dt_esize(src->dt) == 2) gather_kernel<uint16_t><<<grid, 256, 0, dev->stream>>>((const uint16_t*)src->data, (const int32_t*)ids->data, (uint16_t*)dst->data, left, n_ids, right, src_dim, dev->d_status);
-    else gather_kernel<uint32_t><<<grid, 256, 0, dev->stream>>>((const uint32_t*)src->data, (const int32_t*)ids->data, (uint32_t*)dst->data, left, n_ids, right, src_dim, dev->d_status);
+    if (dt_esize(src->dt) == 2) rcu_launch(dev, gather_kernel<uint16_t>, grid, 256, 0, (const uint16_t*)src->data, (const int32_t*)ids->data, (uint16_t*)dst->data, left, n_ids, right, src_dim, dev->d_status);
+    else rcu_launch(dev, gather_kernel<uint32_t>, grid, 256, 0, (const uint32_t*)src->data, (const int32_t*)ids->data, (uint32_t*)dst->data, left, n_ids, right, src_dim, dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }

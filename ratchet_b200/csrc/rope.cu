@@ -21,6 +21,7 @@ template <class T, int V> struct alignas(sizeof(T) * V) RopeVec { T v[V]; };
 template <class T, int V>
 __global__ void __launch_bounds__(128)
 rope_kernel(const T* x, T* out, int BH, int S, int D, int dim, float ln_base, int offset) {
+    rcu_kernel_entry();
     typedef RopeVec<T, V> VT;
     const int half = dim >> 1;
     const int hv = half / V;
@@ -81,8 +82,8 @@ void launch_rope(rcu_device* dev, const void* x, void* out, int BH, int S, int D
     // enough (batch, head) slices per thread to amortise the angle evaluation, enough CTAs to fill the GPU
     const int want = (dev->sm_count * 16 + gx - 1) / gx;
     dim3 grid(gx, (unsigned)std::max(1, std::min(BH, want)));
-    if (vec) rope_kernel<T, VF><<<grid, 128, 0, dev->stream>>>((const T*)x, (T*)out, BH, S, D, dim, ln_base, offset);
-    else rope_kernel<T, 1><<<grid, 128, 0, dev->stream>>>((const T*)x, (T*)out, BH, S, D, dim, ln_base, offset);
+    if (vec) rcu_launch(dev, rope_kernel<T, VF>, grid, 128, 0, (const T*)x, (T*)out, BH, S, D, dim, ln_base, offset);
+    else rcu_launch(dev, rope_kernel<T, 1>, grid, 128, 0, (const T*)x, (T*)out, BH, S, D, dim, ln_base, offset);
 }
 
 }  // namespace

@@ -227,6 +227,7 @@ template <class T, int MODE, int G, int V, int kPer>
 __global__ void __launch_bounds__(G > kCtaThreads ? G : kCtaThreads)
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
            size_t rows, int N, float eps) {
+    rcu_kernel_entry();
     typedef RowVec<T, V> VT;
     typedef RowMath<T, V> Math;
     constexpr int CTA = G > kCtaThreads ? G : kCtaThreads;
@@ -310,6 +311,7 @@ template <class T, int MODE>
 __global__ void __launch_bounds__(kCtaThreads)
 row_kernel_long(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
                 size_t rows, int N, float eps) {
+    rcu_kernel_entry();
     __shared__ float scratch[32];
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T* xr = x + row * (size_t)N;
@@ -354,7 +356,7 @@ rcu_status launch_rows_v(rcu_device* dev, const T* xp, const T* gp, const T* bp,
         constexpr int cta = G > kCtaThreads ? G : kCtaThreads;                                             \
         const size_t groups = cta / G;                                                                     \
         const int grid = (int)std::min<size_t>((rows + groups - 1) / groups, cap);                         \
-        row_kernel<T, MODE, G, V, PER><<<grid, cta, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);       \
+        rcu_launch(dev, row_kernel<T, MODE, G, V, PER>, grid, cta, 0, xp, gp, bp, op, rows, N, eps);       \
     }
     if (nvec <= 32 * 4) RCU_ROW(32, 4)
     else if (nvec <= 32 * 8) RCU_ROW(32, 8)
@@ -380,7 +382,7 @@ rcu_status launch_rows(rcu_device* dev, const void* x, const void* gamma, const 
     if (kVector && fits(VHALF)) return launch_rows_v<T, MODE, kVector ? VHALF : 1>(dev, xp, gp, bp, op, rows, N, eps);
     if (fits(1)) return launch_rows_v<T, MODE, 1>(dev, xp, gp, bp, op, rows, N, eps);
     const int grid = (int)std::min<size_t>(rows, (size_t)dev->sm_count * 8);
-    row_kernel_long<T, MODE><<<grid, kCtaThreads, 0, dev->stream>>>(xp, gp, bp, op, rows, N, eps);
+    rcu_launch(dev, row_kernel_long<T, MODE>, grid, kCtaThreads, 0, xp, gp, bp, op, rows, N, eps);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
 }
@@ -401,6 +403,7 @@ template <class T>
 __global__ void __launch_bounds__(kCtaThreads)
 group_norm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
                   int C, int L, int groups, float eps) {
+    rcu_kernel_entry();
     __shared__ float scratch[32];
     const int cpg = C / groups;
     const size_t base = (size_t)blockIdx.x * cpg * L;   // blockIdx.x = b * groups + g
@@ -424,6 +427,7 @@ group_norm_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T*
 // Warp per row; V elements per load (N % V == 0), four loads in flight per lane.
 template <class T, int KIND, int V>
 __global__ void __launch_bounds__(256) reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int N) {
+    rcu_kernel_entry();
     typedef RowVec<T, V> VT;
     const int lane = threadIdx.x & 31;
     const size_t wpc = blockDim.x >> 5;
@@ -475,8 +479,8 @@ rcu_status rcu_norm(rcu_device* dev, int kind, const rcu_tensor* x, const rcu_te
         const int grid = (int)(x->shape[0] * groups);
         const void* bp = bias ? bias->data : nullptr;
         switch (x->dt) {
-            case RCU_F32: group_norm_kernel<float><<<grid, kCtaThreads, 0, dev->stream>>>((const float*)x->data, (const float*)scale->data, (const float*)bp, (float*)dst->data, (int)x->shape[1], (int)x->shape[2], (int)groups, eps); break;
-            case RCU_F16: group_norm_kernel<__half><<<grid, kCtaThreads, 0, dev->stream>>>((const __half*)x->data, (const __half*)scale->data, (const __half*)bp, (__half*)dst->data, (int)x->shape[1], (int)x->shape[2], (int)groups, eps); break;
+            case RCU_F32: rcu_launch(dev, group_norm_kernel<float>, grid, kCtaThreads, 0, (const float*)x->data, (const float*)scale->data, (const float*)bp, (float*)dst->data, (int)x->shape[1], (int)x->shape[2], (int)groups, eps); break;
+            case RCU_F16: rcu_launch(dev, group_norm_kernel<__half>, grid, kCtaThreads, 0, (const __half*)x->data, (const __half*)scale->data, (const __half*)bp, (__half*)dst->data, (int)x->shape[1], (int)x->shape[2], (int)groups, eps); break;
             default: return rcu_fail(dev, RCU_ERR_UNSUPPORTED, "group_norm: dtype %d", x->dt);
         }
         RCU_LAUNCH_CHECK(dev);
@@ -513,8 +517,8 @@ rcu_status rcu_reduce(rcu_device* dev, int kind, const rcu_tensor* x, rcu_tensor
     const int grid = (int)std::min<size_t>((rows + 7) / 8, (size_t)dev->sm_count * 8);
     const bool vec = N % 8 == 0 && (reinterpret_cast<uintptr_t>(x->data) & 15) == 0;   // 16-byte loads for 2- and 4-byte types
 #define RCU_RED(T, K)                                                                                                        \
-    if (vec) reduce_rows_kernel<T, K, 16 / sizeof(T)><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (T*)dst->data, rows, (int)N); \
-    else reduce_rows_kernel<T, K, 1><<<grid, 256, 0, dev->stream>>>((const T*)x->data, (T*)dst->data, rows, (int)N)
+    if (vec) rcu_launch(dev, reduce_rows_kernel<T, K, 16 / sizeof(T)>, grid, 256, 0, (const T*)x->data, (T*)dst->data, rows, (int)N); \
+    else rcu_launch(dev, reduce_rows_kernel<T, K, 1>, grid, 256, 0, (const T*)x->data, (T*)dst->data, rows, (int)N)
 #define RCU_RED_T(T)                                       \
     switch (kind) {                                        \
         case RCU_REDUCE_SUM: RCU_RED(T, RCU_REDUCE_SUM); break; \
