@@ -57,13 +57,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
         : "memory");
 }
 
-template <int BN, int STAGES>
+// TMR = token rows of a tile, 128 or 64.  With 64 the accumulator rows sit in the first 16 lanes of each 32-lane
+// quarter of tensor memory (row r in lane 32 (r / 16) + r % 16); a tile costs half the shared-memory traffic on the
+// activation side, which is what small M (Phi-2's 64 rows) and grids that do not fill the SMs want.
+template <int BN, int STAGES, int TMR>
 __global__ void __launch_bounds__(kThreadsF32, 1)
 gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ bias,
                    const float* __restrict__ bias_rows,
                    float* __restrict__ out, int M, int N, int K, int kb_per_split, int* status) {
     rcu_kernel_entry();
-    constexpr int A_BYTES = TM * TK32 * 4;        // 16 KiB
+    constexpr int A_BYTES = TMR * TK32 * 4;       // 16 or 8 KiB
     constexpr int B_BYTES = BN * TK32 * 4;
     constexpr int RAW = A_BYTES + B_BYTES;        // hi tiles (A then B); the lo tiles follow in the same order
     constexpr int STAGE = 2 * RAW;
@@ -77,7 +80,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * TMR, n0 = blockIdx.x * BN;
     // blockIdx.z is either the problem of a batch (attention heads: third coordinate of both maps) or, when
     // kb_per_split > 0, the slice of K this CTA sums: slice z covers k-blocks [z * kb_per_split, ...) of the
     // one problem and writes its partial result to slab z of `out`.
@@ -119,7 +122,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_tf32(TM, BN);
+            constexpr uint32_t idesc = umma_idesc_tf32(TMR, BN);
             for (int it = 0; it < nk; ++it) {
                 const int s = it % STAGES;
                 if (!mbar_wait_spin(&full[s], (it / STAGES) & 1, abort_flag, status)) break;
@@ -145,7 +148,7 @@ gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
         const int q = warp & 3;
         const bool ok = mbar_wait(accum_bar, 0, abort_flag, status);
         tc_fence_after();
-        const int row = m0 + q * 32 + lane;
+        const int row = TMR == 128 ? m0 + q * 32 + lane : (lane < 16 ? m0 + q * 16 + lane : M);   // 64-row tiles: 16 rows per quarter
         if (ok) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
@@ -245,18 +248,27 @@ sum_splits_kernel(const float4* __restrict__ part, int splits, size_t slab4, con
     }
 }
 
-template <int BN>
+template <int BN, int TMR>
 rcu_status launch_f32(rcu_device* dev, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, const void* bias_rows, void* out,
                       int M, int N, int K, int batches, int kb_per_split) {
-    constexpr int STAGE = 2 * (TM * TK32 * 4 + BN * TK32 * 4);
-    constexpr int STAGES = (192 * 1024) / STAGE;
+    constexpr int STAGE = 2 * (TMR * TK32 * 4 + BN * TK32 * 4);
+    constexpr int STAGES = (192 * 1024) / STAGE > 8 ? 8 : (192 * 1024) / STAGE;
     const size_t smem = (size_t)STAGES * STAGE + 1024 + 512;
-    auto kern = gemm_tc_f32_kernel<BN, STAGES>;
+    auto kern = gemm_tc_f32_kernel<BN, STAGES, TMR>;
     RCU_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((N + BN - 1) / BN, (M + TM - 1) / TM, batches);
+    dim3 grid((N + BN - 1) / BN, (M + TMR - 1) / TMR, batches);
     rcu_launch(dev, kern, grid, kThreadsF32, smem, xmap, wmap, (const float*)bias, (const float*)bias_rows, (float*)out, M, N, K, kb_per_split, dev->d_status);
     RCU_LAUNCH_CHECK(dev);
     return RCU_OK;
+}
+
+rcu_status launch_f32_any(rcu_device* dev, int bn, int tmr, const CUtensorMap& xmap, const CUtensorMap& wmap, const void* bias, const void* bias_rows,
+                          void* out, int M, int N, int K, int batches, int kb_per_split) {
+    if (tmr == 64)
+        return bn == 128 ? launch_f32<128, 64>(dev, xmap, wmap, bias, bias_rows, out, M, N, K, batches, kb_per_split)
+                         : launch_f32<64, 64>(dev, xmap, wmap, bias, bias_rows, out, M, N, K, batches, kb_per_split);
+    return bn == 128 ? launch_f32<128, 128>(dev, xmap, wmap, bias, bias_rows, out, M, N, K, batches, kb_per_split)
+                     : launch_f32<64, 128>(dev, xmap, wmap, bias, bias_rows, out, M, N, K, batches, kb_per_split);
 }
 
 // [batches, rows, K] f32 row-major, box = 1 x box_rows x 32 elements, 128-byte swizzle
@@ -289,14 +301,19 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
     // tensor-map strides are multiples of 16 bytes; the grid's z extent is limited
     if (batches < 1 || batches > 65535 || (batches > 1 && ((M * K) % 4 != 0 || (N * K) % 4 != 0 || (M * N) % 4 != 0 || bias || bias_rows))) return RCU_ERR_UNSUPPORTED;
     DevGuard g(dev->ordinal);
-    // Tile width by whole waves over the SMs (one CTA per SM): a k-block of the 128-wide tile moves 1.35x
-    // the shared-memory bytes of the 64-wide one (the kernel's bound) for twice the columns.
-    const uint64_t mt = (M + TM - 1) / TM, sms = (uint64_t)dev->sm_count;
+    // Tile height: 64 token rows when M fits one such tile (half of a 128-row tile would be padding).  Cutting larger
+    // M into 64-row tiles to put a CTA on every SM was measured and is slower (Whisper-tiny's 1500 x 384 x 384
+    // Linear and the unfolded conv1d): the weight side of a tile costs the same and is then paid twice as often.
+    const uint64_t sms = (uint64_t)dev->sm_count;
+    const int tmr = M <= 64 ? 64 : 128;
+    // Tile width by whole waves over the SMs (one CTA per SM): a k-block of the 128-wide tile moves 1.35x (1.5x with
+    // 64-row tiles) the shared-memory bytes of the 64-wide one (the kernel's bound) for twice the columns.
+    const uint64_t mt = (M + tmr - 1) / tmr;
     const uint64_t waves128 = (mt * ((N + 127) / 128) * batches + sms - 1) / sms;
     const uint64_t waves64 = (mt * ((N + 63) / 64) * batches + sms - 1) / sms;
-    const int bn = (double)waves128 * 1.35 < (double)waves64 ? 128 : 64;
+    const int bn = (double)waves128 * (tmr == 64 ? 1.5 : 1.35) < (double)waves64 ? 128 : 64;
     CUtensorMap xmap, wmap;
-    if (!make_map_f32_sw128(&xmap, x, batches, M, K, TM) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
+    if (!make_map_f32_sw128(&xmap, x, batches, M, K, (uint32_t)tmr) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
         return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu x%llu)", (unsigned long long)M,
                         (unsigned long long)N, (unsigned long long)K, (unsigned long long)batches);
     // A grid that fills less than half of the SMs with a long K splits K over blockIdx.z: every slice
@@ -311,8 +328,7 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
         void* part = nullptr;
         rcu_status st = rcu_alloc(dev, splits * M * N * 4, &part);
         if (st != RCU_OK) return st;
-        st = bn == 128 ? launch_f32<128>(dev, xmap, wmap, nullptr, nullptr, part, (int)M, (int)N, (int)K, (int)splits, (int)kbps)
-                       : launch_f32<64>(dev, xmap, wmap, nullptr, nullptr, part, (int)M, (int)N, (int)K, (int)splits, (int)kbps);
+        st = launch_f32_any(dev, bn, tmr, xmap, wmap, nullptr, nullptr, part, (int)M, (int)N, (int)K, (int)splits, (int)kbps);
         if (st == RCU_OK) {
             const size_t slab4 = (size_t)(M * N / 4);
             const int grid = (int)std::min<size_t>((slab4 + 255) / 256, (size_t)dev->sm_count * 8);
@@ -323,6 +339,5 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
         rcu_free(dev, part);      // the pool reuses blocks in stream order
         return st;
     }
-    return bn == 128 ? launch_f32<128>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches, 0)
-                     : launch_f32<64>(dev, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches, 0);
+    return launch_f32_any(dev, bn, tmr, xmap, wmap, bias, bias_rows, y, (int)M, (int)N, (int)K, (int)batches, 0);
 }
