@@ -306,22 +306,27 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
     // Linear and the unfolded conv1d): the weight side of a tile costs the same and is then paid twice as often.
     const uint64_t sms = (uint64_t)dev->sm_count;
     const int tmr = M <= 64 ? 64 : 128;
-    // Tile width by whole waves over the SMs (one CTA per SM): a k-block of the 128-wide tile moves 1.35x (1.5x with
-    // 64-row tiles) the shared-memory bytes of the 64-wide one (the kernel's bound) for twice the columns.
-    const uint64_t mt = (M + tmr - 1) / tmr;
-    const uint64_t waves128 = (mt * ((N + 127) / 128) * batches + sms - 1) / sms;
-    const uint64_t waves64 = (mt * ((N + 63) / 64) * batches + sms - 1) / sms;
-    const int bn = (double)waves128 * (tmr == 64 ? 1.5 : 1.35) < (double)waves64 ? 128 : 64;
+    // Tile width and K slices together: the kernel is bound by shared-memory traffic, which per k-block is
+    // proportional to (tile rows + tile columns); a grid that fills less than half of the SMs with a long K splits K
+    // over blockIdx.z (every slice writes a partial result to pooled scratch and one pass sums the slices in order:
+    // deterministic).  Of the two widths take the one with the smaller rounds x k-blocks x (rows + columns).
+    const uint64_t mt = (M + tmr - 1) / tmr, nk = (K + TK32 - 1) / TK32;
+    constexpr uint64_t kMinBlocksPerSplit = 24;
+    int bn = 64;
+    uint64_t splits = 1, best = ~0ull;
+    for (int cand : {64, 128}) {
+        const uint64_t tiles_c = mt * ((N + cand - 1) / cand);
+        uint64_t sp = 1;
+        if (batches == 1 && tiles_c * 2 <= sms && M * N % 4 == 0) sp = std::max<uint64_t>(1, std::min<uint64_t>(sms / tiles_c, nk / kMinBlocksPerSplit));
+        const uint64_t kbps_c = (nk + sp - 1) / sp;
+        const uint64_t rounds = (tiles_c * sp * batches + sms - 1) / sms;
+        const uint64_t cost = rounds * kbps_c * (uint64_t)(tmr + cand);
+        if (cost < best) { best = cost; bn = cand; splits = sp; }
+    }
     CUtensorMap xmap, wmap;
     if (!make_map_f32_sw128(&xmap, x, batches, M, K, (uint32_t)tmr) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
         return rcu_fail(dev, RCU_ERR_CUDA, "gemm_tc_f32: cuTensorMapEncodeTiled failed (M=%llu N=%llu K=%llu x%llu)", (unsigned long long)M,
                         (unsigned long long)N, (unsigned long long)K, (unsigned long long)batches);
-    // A grid that fills less than half of the SMs with a long K splits K over blockIdx.z: every slice
-    // writes a partial result to pooled scratch and one pass sums the slices in order (deterministic).
-    const uint64_t tiles = mt * ((N + bn - 1) / bn), nk = (K + TK32 - 1) / TK32;
-    constexpr uint64_t kMinBlocksPerSplit = 24;
-    uint64_t splits = 1;
-    if (batches == 1 && tiles * 2 <= sms) splits = std::min<uint64_t>(sms / tiles, nk / kMinBlocksPerSplit);
     if (splits > 1 && M * N % 4 == 0) {
         const uint64_t kbps = (nk + splits - 1) / splits;
         splits = (nk + kbps - 1) / kbps;
