@@ -115,7 +115,9 @@ def test_config3_q4k_prefill_shape(dev, config3_weight, M):
 # f32 Linear on the tensor cores (split TF32): the f32 bar, 1e-4 of the result's scale
 F32_SHAPES = [(64, 10240, 2560), (128, 256, 256), (100, 200, 136), (37, 64, 36), (1500, 384, 384), (1500, 1536, 384), (300, 2560, 10240),
               # grids that fill under half of the SMs with a long K: K is split over CTAs and the slices summed in order
-              (64, 2560, 10240), (100, 192, 2000), (1500, 384, 1536)]
+              (64, 2560, 10240), (100, 192, 2000), (1500, 384, 1536),
+              # grids of one and two rounds of CTAs with either tile width
+              (300, 4800, 256), (200, 6912, 128)]
 
 
 @pytest.mark.parametrize("M,N,K", F32_SHAPES)
