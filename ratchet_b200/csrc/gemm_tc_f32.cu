@@ -306,22 +306,25 @@ rcu_status rcu_gemm_tc_f32_dispatch(rcu_device* dev, const void* w, const void* 
     // Linear and the unfolded conv1d): the weight side of a tile costs the same and is then paid twice as often.
     const uint64_t sms = (uint64_t)dev->sm_count;
     const int tmr = M <= 64 ? 64 : 128;
-    // Tile width and K slices together: the kernel is bound by shared-memory traffic, which per k-block is
-    // proportional to (tile rows + tile columns); a grid that fills less than half of the SMs with a long K splits K
-    // over blockIdx.z (every slice writes a partial result to pooled scratch and one pass sums the slices in order:
-    // deterministic).  Of the two widths take the one with the smaller rounds x k-blocks x (rows + columns).
+    // Tile width and K slices together.  A CTA spends about 0.7 us per 32-wide k-block almost regardless of the tile's
+    // width (twelve small MMAs issued by one thread, the lo pass, the barrier hops between them), so what counts is
+    // how many k-blocks a CTA runs one after the other and how many rounds of CTAs the grid needs; the width adds a
+    // little through shared-memory traffic.  Slices of K (blockIdx.z; every slice writes a partial result to pooled
+    // scratch and one pass sums the slices in order: deterministic) are taken whenever they shorten that chain, with a
+    // charge for the summing pass.
     const uint64_t mt = (M + tmr - 1) / tmr, nk = (K + TK32 - 1) / TK32;
-    constexpr uint64_t kMinBlocksPerSplit = 24;
+    constexpr uint64_t kMinBlocksPerSplit = 24, kFixed = 600, kSumCharge = 4;
     int bn = 64;
     uint64_t splits = 1, best = ~0ull;
     for (int cand : {64, 128}) {
         const uint64_t tiles_c = mt * ((N + cand - 1) / cand);
-        uint64_t sp = 1;
-        if (batches == 1 && tiles_c * 2 <= sms && M * N % 4 == 0) sp = std::max<uint64_t>(1, std::min<uint64_t>(sms / tiles_c, nk / kMinBlocksPerSplit));
-        const uint64_t kbps_c = (nk + sp - 1) / sp;
-        const uint64_t rounds = (tiles_c * sp * batches + sms - 1) / sms;
-        const uint64_t cost = rounds * kbps_c * (uint64_t)(tmr + cand);
-        if (cost < best) { best = cost; bn = cand; splits = sp; }
+        const uint64_t sp_max = (batches == 1 && M * N % 4 == 0) ? std::max<uint64_t>(1, std::min<uint64_t>(8, nk / kMinBlocksPerSplit)) : 1;
+        for (uint64_t sp = 1; sp <= sp_max; ++sp) {
+            const uint64_t kbps_c = (nk + sp - 1) / sp;
+            const uint64_t rounds = (tiles_c * sp * batches + sms - 1) / sms;
+            const uint64_t cost = (rounds * kbps_c + (sp > 1 ? kSumCharge : 0)) * (kFixed + (uint64_t)(tmr + cand));
+            if (cost < best) { best = cost; bn = cand; splits = sp; }
+        }
     }
     CUtensorMap xmap, wmap;
     if (!make_map_f32_sw128(&xmap, x, batches, M, K, (uint32_t)tmr) || !make_map_f32_sw128(&wmap, w, batches, N, K, (uint32_t)bn))
