@@ -82,6 +82,11 @@ __device__ __forceinline__ void rcu_kernel_entry() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// The entry of kernels that fill an SM on their own (the tensor-core GEMMs: one or two CTAs hold all of its shared
+// memory): they wait, but leave the trigger to their completion, so that the next kernel's blocks do not move in while
+// this one still wants every resource.
+__device__ __forceinline__ void rcu_kernel_entry_wait_only() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // kern<<<grid, block, smem, dev->stream>>>(args...) as a programmatic dependent of the kernel before it
 // (RCU_NO_PDL in the environment launches it plainly).  The kernel must call rcu_kernel_entry() first.
 template <class... P, class... A>

@@ -59,7 +59,7 @@ template <int BN, int WK, int STAGES>
 __global__ void __launch_bounds__(WK == WK_F16 ? kThreadsTc : kThreadsTc + conv_warps(BN) * 32, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QuantArgs qa,
                const __half* __restrict__ bias, __half* __restrict__ out, int M, int N, int K, int* status, int splits, float* __restrict__ partial) {
-    rcu_kernel_entry();
+    rcu_kernel_entry_wait_only();
     constexpr int A_BYTES = TM * TK * 2;          // 16 KiB
     constexpr int B_BYTES = BN * TK * 2;
     constexpr int STAGE = A_BYTES + B_BYTES;

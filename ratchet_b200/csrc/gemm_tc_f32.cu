@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kThreadsF32, 1)
 gemm_tc_f32_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const float* __restrict__ bias,
                    const float* __restrict__ bias_rows,
                    float* __restrict__ out, int M, int N, int K, int kb_per_split, int* status) {
-    rcu_kernel_entry();
+    rcu_kernel_entry_wait_only();
     constexpr int A_BYTES = TMR * TK32 * 4;       // 16 or 8 KiB
     constexpr int B_BYTES = BN * TK32 * 4;
     constexpr int RAW = A_BYTES + B_BYTES;        // hi tiles (A then B); the lo tiles follow in the same order
